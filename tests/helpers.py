@@ -1,0 +1,98 @@
+"""Tiny configurations and helpers shared by the tests.
+
+Two configurations of the architecture that differ in every size and option:
+
+            layers hidden heads kv  head_dim inter vocab theta  eps   head    bias  window      page
+  tiny_a      2     64     4    2     16     128   256   1e4    1e-6  tied    no    none          4
+  tiny_b      3     96     8    2     32     160   384   1e6    1e-5  untied  yes   20 (layers    8
+                                                                                    1 and 2)
+"""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+TINY = {
+    "tiny_a": dict(
+        seed=0, page_size=4,
+        config=dict(vocab_size=256, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                    num_attention_heads=4, head_dim=16, attention_bias=False, num_key_value_heads=2,
+                    max_position_embeddings=512, tie_word_embeddings=True, rope_theta=10000.0,
+                    rms_norm_eps=1e-6, hidden_act="silu")),
+    "tiny_b": dict(
+        seed=1, page_size=8,
+        config=dict(vocab_size=384, hidden_size=96, intermediate_size=160, num_hidden_layers=3,
+                    num_attention_heads=8, head_dim=32, attention_bias=True, num_key_value_heads=2,
+                    max_position_embeddings=1024, tie_word_embeddings=False, rope_theta=1000000.0,
+                    rms_norm_eps=1e-5, hidden_act="silu", use_sliding_window=True, sliding_window=20,
+                    max_window_layers=1)),
+}
+
+FP32_ATOL = 1e-4
+# bfloat16: the bound the reference's kernel tests use, atol + rtol * |x|
+# (tests/metal_decode_parity.rs:131-136)
+BF16_ATOL, BF16_RTOL = 3e-2, 3e-2
+
+
+def tiny_config(name):
+    from velox_b200.config import Qwen3Config
+    return Qwen3Config.from_dict(TINY[name]["config"])
+
+
+def write_tiny(name, folder, dtype="bfloat16"):
+    from velox_b200.weights import write_random_model
+    return write_random_model(folder, tiny_config(name), TINY[name]["seed"], dtype=dtype)
+
+
+def random_tokens(vocab, length, seed):
+    return [int(t) for t in np.random.default_rng(seed).integers(0, vocab, size=length)]
+
+
+def assert_close(got, want, dtype, what=""):
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    assert got.shape == want.shape, "%s: shape %s vs %s" % (what, got.shape, want.shape)
+    assert np.isfinite(got).all(), "%s: non-finite values in the engine's output" % what
+    err = np.abs(got - want)
+    if dtype == "float32":
+        bound = np.full_like(err, FP32_ATOL)
+    else:
+        bound = BF16_ATOL + BF16_RTOL * np.abs(want)
+    bad = err > bound
+    if bad.any():
+        idx = np.unravel_index(np.argmax(err - bound), err.shape)
+        rows = np.unique(np.nonzero(bad)[0])
+        raise AssertionError("%s: %d values beyond tolerance (%s); worst at %s: got %.6g want %.6g; first wrong row %d, wrong rows %s"
+                             % (what, int(bad.sum()), dtype, idx, got[idx], want[idx], rows[0], rows[:20].tolist()))
+
+
+def run_trace(model_dir, dtype, steps, max_tokens, out_dir, page_size=16, poison=True, timeout=600):
+    """Runs bin/trace_run as a user would: steps on stdin one at a time, waiting
+    for `done <step>` after each.  Returns {step: float32 array [wanted, vocab]}."""
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype,
+           "--out", out_dir, "--max-tokens", str(max_tokens), "--page-size", str(page_size)]
+    if poison:
+        cmd.append("--poison-cache")
+    proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, bufsize=1)
+    try:
+        for rec in steps:
+            proc.stdin.write(json.dumps(rec) + "\n")
+            proc.stdin.flush()
+            line = proc.stdout.readline()
+            assert line.strip() == "done %s" % rec["step"], "trace_run answered %r to step %r" % (line, rec["step"])
+        proc.stdin.close()
+        assert proc.wait(timeout=timeout) == 0
+    finally:
+        if proc.poll() is None:
+            proc.kill()
+    with open(os.path.join(model_dir, "config.json")) as f:
+        vocab = json.load(f)["vocab_size"]
+    out = {}
+    for rec in steps:
+        p = os.path.join(out_dir, "%s.f32" % rec["step"])
+        if os.path.exists(p):
+            out[rec["step"]] = np.fromfile(p, dtype="<f4").reshape(-1, vocab)
+    return out

@@ -1,0 +1,90 @@
+// Shared helpers of the kernels: element types, conversions, warp and block
+// reductions, the error convention of the C entry points.
+//
+// Every entry point is `extern "C"`, takes raw device pointers and a stream,
+// launches on that stream and returns 0 or a negative code (VX_ERR_*) for a
+// refused size, or the positive cudaError_t of a failed launch.  Nothing here
+// allocates device memory.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define VX_OK 0
+#define VX_ERR_SHAPE (-1)    // a size the kernel does not take
+#define VX_ERR_DTYPE (-2)    // an element type code the kernel does not know
+#define VX_ERR_ALIGN (-3)    // a pointer or stride that is not aligned as needed
+#define VX_ERR_LIMIT (-4)    // beyond a stated maximum
+
+#define VX_F32 0
+#define VX_BF16 1
+
+#define VX_LAUNCH_CHECK()                          \
+    do {                                           \
+        cudaError_t e__ = cudaGetLastError();      \
+        if (e__ != cudaSuccess) return (int)e__;   \
+    } while (0)
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_f32(float x) { return x; }
+__device__ __forceinline__ float to_f32(bf16 x) { return __bfloat162float(x); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float x);
+template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float x) { return __float2bfloat16_rn(x); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; `scratch` holds 32 floats.  Every
+// thread gets the result.  The order of the additions is fixed by the block
+// size alone.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = (lane < nwarps) ? scratch[lane] : 0.f;
+    r = warp_sum(r);
+    return r;
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = (lane < nwarps) ? scratch[lane] : -INFINITY;
+    r = warp_max(r);
+    return r;
+}
+
+// Activation functions of gated feed-forwards, by code.
+#define VX_ACT_SILU 0
+#define VX_ACT_GELU 1
+#define VX_ACT_GELU_TANH 2
+#define VX_ACT_RELU 3
+
+__device__ __forceinline__ float activation(float z, int act) {
+    switch (act) {
+        case VX_ACT_SILU: return z / (1.f + expf(-z));
+        case VX_ACT_GELU: return 0.5f * z * (1.f + erff(z * 0.70710678118654752f));
+        case VX_ACT_GELU_TANH: {
+            const float c = 0.7978845608028654f;
+            return 0.5f * z * (1.f + tanhf(c * (z + 0.044715f * z * z * z)));
+        }
+        default: return fmaxf(z, 0.f);
+    }
+}

@@ -1,0 +1,252 @@
+"""Python face of the kernel library: one function per C entry point.
+
+The library is compiled on first use (`build.build`) and loaded with ctypes.
+There is no other implementation behind these functions: if the library cannot
+be built or loaded, or a kernel refuses a size, the call raises.  Every function
+launches on torch's current CUDA stream and takes torch tensors only as holders
+of device memory.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+from typing import Optional
+
+import torch
+
+from . import build as _build
+
+_LIB = None
+
+VX_F32, VX_BF16 = 0, 1
+ACTIVATIONS = {"silu": 0, "gelu": 1, "gelu_pytorch_tanh": 2, "relu": 3}
+_ERRORS = {
+    -1: "a size the kernel does not take",
+    -2: "an element type the kernel does not know",
+    -3: "a pointer or stride that is not aligned as the kernel needs",
+    -4: "a size beyond the kernel's stated maximum",
+    -5: "the device or driver lacks what the kernel needs",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def library():
+    """The loaded kernel library; built first if needed.  Raises if it cannot be had."""
+    global _LIB
+    if _LIB is None:
+        path = _build.build()
+        try:
+            _LIB = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelError("the kernel library %s could not be loaded: %s" % (path, e))
+        _declare(_LIB)
+    return _LIB
+
+
+def is_loaded() -> bool:
+    return _LIB is not None
+
+
+def _declare(lib) -> None:
+    P, I, F = c_void_p, c_int, c_float
+    sigs = {
+        "vx_embedding": [P, P, P, I, I, I, I, P],
+        "vx_add_rmsnorm": [P, P, P, P, P, P, I, I, F, I, P],
+        "vx_rmsnorm": [P, P, P, I, I, F, I, P],
+        "vx_gated_act": [P, P, I, I, I, I, P],
+        "vx_qk_norm_rope_kv": [P, I, P, P, F, P, I, P, P, P, P, I, I, I, I, I, I, P],
+        "vx_paged_attention_generic": [P, I, P, P, P, I, P, P, P, I, F, I, I, I, I, I, I, I, P],
+        "vx_gemm_nt_simt": [P, P, P, P, I, I, I, I, I, I, I, I, P],
+        "vx_sample": [P, I, I, I, P, P, P, P, P],
+    }
+    for name, args in sigs.items():
+        fn = getattr(lib, name)
+        fn.argtypes = args
+        fn.restype = c_int
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code < 0:
+        raise KernelError("%s refused: %s (code %d)" % (what, _ERRORS.get(code, "unknown"), code))
+    raise KernelError("%s: CUDA error %d at launch" % (what, code))
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return VX_F32
+    if dtype == torch.bfloat16:
+        return VX_BF16
+    raise KernelError("element type %s has no kernels (float32 and bfloat16 have)" % dtype)
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def _dev(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernels take CUDA tensors; got one on %s" % t.device)
+
+
+# ----------------------------------------------------------------------------
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """float32 rows of `table` [V,E] at int32 `ids` [T]."""
+    _dev(ids, table)
+    _need(ids.dtype == torch.int32 and ids.is_contiguous() and table.is_contiguous(), "embedding: int32 ids, contiguous")
+    t, (v, e) = ids.numel(), table.shape
+    if out is None:
+        out = torch.empty((t, e), dtype=torch.float32, device=table.device)
+    _check(library().vx_embedding(_ptr(ids), _ptr(table), _ptr(out), t, e, v, dtype_code(table.dtype), _stream()),
+           "embedding")
+    return out
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None,
+                residual_out: Optional[torch.Tensor] = None, update_residual: bool = True) -> torch.Tensor:
+    """normed = rmsnorm(residual (+ delta)) rounded to `out_dtype`.
+
+    Without `rows` the sum is written back into `residual` (if there is a delta
+    and `update_residual`).  With `rows` (int32 indices) only those rows are
+    read, and the sums go to `residual_out` if given."""
+    _dev(residual, delta, weight, rows)
+    _need(residual.dtype == torch.float32 and residual.is_contiguous(), "add_rmsnorm: float32 contiguous residual")
+    _need(weight.dtype == torch.float32, "add_rmsnorm: float32 weight")
+    width = residual.shape[-1]
+    _need(weight.numel() == width, "add_rmsnorm: weight has %d elements, rows %d" % (weight.numel(), width))
+    if delta is not None:
+        _need(delta.dtype == out_dtype and delta.is_contiguous() and delta.shape == residual.shape,
+              "add_rmsnorm: delta must match the residual's shape and the output's element type")
+    n = residual.shape[0] if rows is None else rows.numel()
+    out = torch.empty((n, width), dtype=out_dtype, device=residual.device)
+    if rows is None:
+        res_out = residual if (delta is not None and update_residual) else None
+    else:
+        _need(rows.dtype == torch.int32, "add_rmsnorm: int32 rows")
+        res_out = residual_out
+    _check(library().vx_add_rmsnorm(_ptr(residual), _ptr(delta), _ptr(rows), _ptr(res_out), _ptr(weight), _ptr(out),
+                                    n, width, float(eps), dtype_code(out_dtype), _stream()), "add_rmsnorm")
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    _dev(x, weight)
+    _need(x.is_contiguous() and weight.dtype == torch.float32, "rmsnorm: contiguous input, float32 weight")
+    width = x.shape[-1]
+    _need(weight.numel() == width, "rmsnorm: weight has %d elements, rows %d" % (weight.numel(), width))
+    out = torch.empty_like(x)
+    _check(library().vx_rmsnorm(_ptr(x), _ptr(weight), _ptr(out), x.numel() // width, width, float(eps),
+                                dtype_code(x.dtype), _stream()), "rmsnorm")
+    return out
+
+
+def gated_act(gate_up: torch.Tensor, activation: str) -> torch.Tensor:
+    """act(gate) * up for rows [gate | up]."""
+    _dev(gate_up)
+    _need(gate_up.is_contiguous() and gate_up.shape[-1] % 2 == 0, "gated_act: contiguous rows of even width")
+    _need(activation in ACTIVATIONS, "gated_act: activation %r is not one of %s" % (activation, sorted(ACTIVATIONS)))
+    rows, inner = gate_up.shape[0], gate_up.shape[-1] // 2
+    out = torch.empty((rows, inner), dtype=gate_up.dtype, device=gate_up.device)
+    _check(library().vx_gated_act(_ptr(gate_up), _ptr(out), rows, inner, ACTIVATIONS[activation],
+                                  dtype_code(gate_up.dtype), _stream()), "gated_act")
+    return out
+
+
+def qk_norm_rope_kv(qkv: torch.Tensor, q_weight, k_weight, eps: float, inv_freq, rot_dim: int,
+                    positions: torch.Tensor, slot_mapping, k_pool, v_pool, num_heads: int, num_kv_heads: int,
+                    head_dim: int) -> None:
+    """In place on the packed projections `qkv` [T, (H+2Hk)D]; writes new keys
+    and values into the pools [pages, Hk, S, D] when a slot mapping is given."""
+    _dev(qkv, q_weight, k_weight, inv_freq, positions, slot_mapping, k_pool, v_pool)
+    _need(qkv.is_contiguous() and positions.dtype == torch.int32, "qk_norm_rope_kv: contiguous qkv, int32 positions")
+    page_size = 1
+    if slot_mapping is not None:
+        _need(k_pool is not None and v_pool is not None and k_pool.dtype == qkv.dtype and k_pool.is_contiguous()
+              and v_pool.is_contiguous(), "qk_norm_rope_kv: pools of the activations' element type")
+        _need(tuple(k_pool.shape[1:]) == (num_kv_heads, k_pool.shape[2], head_dim), "qk_norm_rope_kv: pool shape")
+        page_size = k_pool.shape[2]
+    if inv_freq is not None:
+        _need(inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == rot_dim, "qk_norm_rope_kv: inv_freq size")
+    for w in (q_weight, k_weight):
+        if w is not None:
+            _need(w.dtype == torch.float32 and w.numel() == head_dim, "qk_norm_rope_kv: norm weight size")
+    _check(library().vx_qk_norm_rope_kv(
+        _ptr(qkv), qkv.shape[-1], _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(inv_freq), int(rot_dim),
+        _ptr(positions), _ptr(slot_mapping), _ptr(k_pool), _ptr(v_pool), qkv.shape[0], num_heads, num_kv_heads,
+        head_dim, page_size, dtype_code(qkv.dtype), _stream()), "qk_norm_rope_kv")
+
+
+def paged_attention_generic(q: torch.Tensor, q_row_stride: int, k_pool, v_pool, block_table: torch.Tensor,
+                            seq_of_token, positions, scale: float, window: int, num_heads: int,
+                            num_kv_heads: int, head_dim: int, tokens: int) -> torch.Tensor:
+    _dev(q, k_pool, v_pool, block_table, seq_of_token, positions)
+    _need(block_table.dtype == torch.int32 and block_table.is_contiguous() and block_table.dim() == 2,
+          "paged_attention: int32 block table [requests, blocks]")
+    _need(k_pool.dtype == q.dtype and v_pool.dtype == q.dtype, "paged_attention: pools of the queries' element type")
+    out = torch.empty((tokens, num_heads * head_dim), dtype=q.dtype, device=q.device)
+    _check(library().vx_paged_attention_generic(
+        _ptr(q), q_row_stride, _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1],
+        _ptr(seq_of_token), _ptr(positions), _ptr(out), num_heads * head_dim, float(scale), int(window), tokens,
+        num_heads, num_kv_heads, head_dim, k_pool.shape[2], dtype_code(q.dtype), _stream()), "paged_attention_generic")
+    return out
+
+
+def gemm_nt_simt(a: torch.Tensor, w: torch.Tensor, bias=None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """a [M,K] times w [N,K] transposed, float32 multiply-adds on the CUDA cores."""
+    _dev(a, w, bias)
+    _need(a.dim() == 2 and w.dim() == 2 and a.shape[1] == w.shape[1], "gemm: a [M,K], w [N,K]")
+    _need(a.stride(1) == 1 and w.stride(1) == 1 and a.dtype == w.dtype, "gemm: rows contiguous, one element type")
+    out_dtype = out_dtype or a.dtype
+    m, k = a.shape
+    n = w.shape[0]
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == n, "gemm: float32 bias of N elements")
+    out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    _check(library().vx_gemm_nt_simt(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), m, n, k, a.stride(0), w.stride(0), n,
+                                     dtype_code(a.dtype), dtype_code(out_dtype), _stream()), "gemm_nt_simt")
+    return out
+
+
+def gemm_bf16(a: torch.Tensor, w: torch.Tensor, bias=None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """a [M,K] times w [N,K] transposed on the tensor cores, float32 accumulation."""
+    _dev(a, w, bias)
+    _need(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "gemm_bf16: bfloat16 operands")
+    out_dtype = out_dtype or torch.bfloat16
+    # library product (cuBLAS through torch); reductions stay in float32
+    torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+    if out_dtype == torch.float32:
+        out = torch.mm(a, w.t(), out_dtype=torch.float32)
+    else:
+        out = torch.mm(a, w.t())
+    if bias is not None:
+        out = (out.float() + bias).to(out_dtype)
+    return out
+
+
+def sample(logits: torch.Tensor, temperature=None, top_p=None, uniform=None) -> torch.Tensor:
+    """int32 token per row of float32 `logits` [R,V]; all greedy without `temperature`."""
+    _dev(logits, temperature, top_p, uniform)
+    _need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1, "sample: float32 logits [R,V]")
+    r, v = logits.shape
+    for t in (temperature, top_p, uniform):
+        if t is not None:
+            _need(t.dtype == torch.float32 and t.numel() == r, "sample: float32 per-row parameters")
+    out = torch.empty((r,), dtype=torch.int32, device=logits.device)
+    _check(library().vx_sample(_ptr(logits), logits.stride(0), r, v, _ptr(temperature), _ptr(top_p), _ptr(uniform),
+                               _ptr(out), _stream()), "sample")
+    return out

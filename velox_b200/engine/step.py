@@ -1,0 +1,65 @@
+"""The step function: a batch of (request, its next tokens) in, logits at the
+wanted places out.
+
+It runs only the tokens it is given, as one batch, against the cache that earlier
+steps left: portions of prompts beside single decoded tokens, cut anywhere.  The
+reference's counterpart is `PagedQwen3::forward` under `BatchScheduler::step`
+(src/paged/qwen3.rs:994-1017; src/paged/scheduler.rs:299-375), which returns the
+last row of every request; here the caller names the rows, and a portion that
+does not end a prompt asks for none (the reference computes and discards them,
+src/paged/scheduler.rs:416-418).
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+from ..cache.manager import CacheManager, OutOfPages
+from .batch import StepContext, StepEntry, build_step_context
+
+
+class ModelRunner:
+    """Owns a model and its cache on one device and steps them."""
+
+    def __init__(self, model, cache: CacheManager, device, vocab_size: int):
+        self.model, self.cache, self.device, self.vocab_size = model, cache, torch.device(device), int(vocab_size)
+        self.steps = 0
+
+    def validate(self, entries: Sequence[StepEntry]) -> None:
+        seen = set()
+        for e in entries:
+            if e.request_id in seen:
+                raise ValueError("request %r appears twice in one step" % (e.request_id,))
+            seen.add(e.request_id)
+            if len(e.tokens) == 0:
+                raise ValueError("request %r brings no tokens" % (e.request_id,))
+            if not self.cache.has_request(e.request_id):
+                raise KeyError("request %r holds no cache; add it first" % (e.request_id,))
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Runs one batch.  Returns float32 logits [wanted, vocab] on the device
+        in the order of the entries and of their `want`, or None if nothing is
+        wanted.  Raises `OutOfPages` (and changes nothing) if the cache cannot
+        hold the new positions."""
+        self.validate(entries)
+        taken: List[StepEntry] = []
+        for e in entries:
+            if not self.cache.reserve(e.request_id, len(e.tokens)):
+                # give back nothing: pages already reserved stay with their
+                # requests (they are theirs to use in a later step)
+                raise OutOfPages("no pages left for request %r (%d new tokens); free pages per group: %s"
+                                 % (e.request_id, len(e.tokens), self.cache.free_pages()))
+            taken.append(e)
+        ctx = build_step_context(entries, self.cache, self.device, self.vocab_size)
+        logits = self.run(ctx)
+        for e in entries:
+            self.cache.commit(e.request_id, len(e.tokens))
+        self.steps += 1
+        return logits
+
+    def run(self, ctx: StepContext) -> Optional[torch.Tensor]:
+        residual, delta = self.model.forward_hidden(ctx, self.cache)
+        if ctx.wanted_rows.numel() == 0:
+            return None
+        return self.model.logits(residual, delta, ctx.wanted_rows)

@@ -1,0 +1,73 @@
+"""A decoder put together from a `ModelPlan`: embedding, blocks in the plan's
+running order, final norm, output head.  Which architecture the plan came from
+is not known here.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..parts.base import Part, Runtime, TensorSpec
+from ..parts.plan import ModelPlan
+from ..parts.registry import build_part, part_class
+
+
+class DecoderModel:
+    def __init__(self, plan: ModelPlan):
+        plan.validate()
+        self.plan = plan
+        self.embedding = build_part("embedding", plan.embedding)
+        self.blocks = []
+        for spec in plan.layers:
+            block_cls = part_class("block", spec.block)
+            self.blocks.append(block_cls(
+                build_part("mixer", spec.mixer), build_part("feed_forward", spec.feed_forward),
+                build_part("norm", spec.mixer_norm), build_part("norm", spec.feed_forward_norm)))
+        self.final_norm = build_part("norm", plan.final_norm)
+        self.head = build_part("head", plan.head)
+        self.order = plan.running_order()
+        self.runtime: Optional[Runtime] = None
+
+    # -- weights -------------------------------------------------------------
+    def parts(self) -> List[Part]:
+        out: List[Part] = [self.embedding]
+        for b in self.blocks:
+            out.extend(b.parts())
+        out.extend([self.final_norm, self.head])
+        return out
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return [s for p in self.parts() for s in p.tensor_specs()]
+
+    def ignored_tensors(self) -> List[str]:
+        return [n for p in self.parts() for n in p.ignored_tensors()]
+
+    def bind(self, tensors: Dict[str, torch.Tensor], runtime: Runtime) -> None:
+        self.runtime = runtime
+        for p in self.parts():
+            p.bind(tensors, runtime)
+        if getattr(self.head, "tied", False):
+            self.head.tie(self.embedding.weight)
+
+    # -- cache ---------------------------------------------------------------
+    def cache_specs(self) -> list:
+        """Per layer: the mixer's cache need, or None for a layer that has no
+        cache of its own (none at all, or another layer's: `plan.layers[i].cache_of`)."""
+        return [None if spec.cache_of is not None else block.mixer.cache_spec()
+                for spec, block in zip(self.plan.layers, self.blocks)]
+
+    # -- step ----------------------------------------------------------------
+    def forward_hidden(self, ctx, cache):
+        """Runs the step's tokens through every layer; returns (residual, delta),
+        whose sum is the last layer's output [tokens, hidden]."""
+        residual = self.embedding.forward(ctx.token_ids)
+        delta = None
+        for i in self.order:
+            residual, delta = self.blocks[i].forward(residual, delta, ctx, cache.layer(i))
+        return residual, delta
+
+    def logits(self, residual, delta, rows: torch.Tensor) -> torch.Tensor:
+        """float32 logits [len(rows), vocab] at the given token rows (int32)."""
+        h = self.final_norm.add_norm(residual, delta, rows=rows)
+        return self.head.forward(h)

@@ -1,0 +1,111 @@
+"""Attention over a paged cache of keys and values: the mixer of Qwen3.
+
+In the reference's order (src/paged/qwen3.rs:428-448, 584-642):
+q/k/v projections -> RMSNorm of each q and k head over head_dim (before the
+rotation, not on v) -> rotation at position kv_offset + t -> new k (normed,
+rotated) and v (raw) written into the pages -> causal attention over the
+request's pages, scale 1/sqrt(head_dim), grouped heads -> output projection
+whose input width is heads * head_dim.  The three projections are one matrix
+here ([Wq; Wk; Wv], rows in that order), which the reference keeps apart
+(src/paged/qwen3.rs:428-430).
+
+Everything is a parameter: head counts, head size, whether q/k are normed,
+whether projections are biased, the window (0: all keys), the scale, and the
+position encoding (a `PartSpec` of category "position").
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional
+
+import torch
+
+from ..csrc import ops
+from .base import Mixer, PagedKV, Runtime, TensorSpec
+from .linear import Linear
+from .plan import PartSpec
+from .registry import build_part
+
+
+class PagedAttention(Mixer):
+    def __init__(self, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 bias: bool = False, qk_norm: bool = True, eps: float = 1e-6, window: int = 0,
+                 position: Optional[PartSpec] = None, scale: Optional[float] = None):
+        super().__init__(prefix)
+        if num_heads % num_kv_heads:
+            raise ValueError("num_heads %d is not a multiple of num_kv_heads %d" % (num_heads, num_kv_heads))
+        self.hidden_size, self.num_heads, self.num_kv_heads = int(hidden_size), int(num_heads), int(num_kv_heads)
+        self.head_dim, self.bias, self.qk_norm = int(head_dim), bool(bias), bool(qk_norm)
+        self.eps, self.window = float(eps), int(window)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
+        self.position = build_part("position", position) if position is not None else None
+        self.qkv: Optional[Linear] = None
+        self.out: Optional[Linear] = None
+        self.q_norm_weight = self.k_norm_weight = None
+
+    # -- weights -------------------------------------------------------------
+    def _proj_rows(self):
+        d = self.head_dim
+        return {"q_proj": self.num_heads * d, "k_proj": self.num_kv_heads * d, "v_proj": self.num_kv_heads * d}
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        p, specs = self.prefix, []
+        for name, rows in self._proj_rows().items():
+            specs.append(TensorSpec(p + name + ".weight", (rows, self.hidden_size), "matrix"))
+            if self.bias:
+                specs.append(TensorSpec(p + name + ".bias", (rows,), "bias"))
+        specs.append(TensorSpec(p + "o_proj.weight", (self.hidden_size, self.num_heads * self.head_dim), "matrix"))
+        if self.bias:
+            specs.append(TensorSpec(p + "o_proj.bias", (self.hidden_size,), "bias"))
+        if self.qk_norm:
+            specs.append(TensorSpec(p + "q_norm.weight", (self.head_dim,), "norm"))
+            specs.append(TensorSpec(p + "k_norm.weight", (self.head_dim,), "norm"))
+        return specs
+
+    def bind(self, tensors: Dict[str, torch.Tensor], runtime: Runtime) -> None:
+        super().bind(tensors, runtime)
+        p = self.prefix
+        w = torch.cat([tensors[p + n + ".weight"] for n in ("q_proj", "k_proj", "v_proj")], dim=0).contiguous()
+        b = torch.cat([tensors[p + n + ".bias"] for n in ("q_proj", "k_proj", "v_proj")]).contiguous() if self.bias else None
+        self.qkv = Linear(w, b)
+        self.out = Linear(tensors[p + "o_proj.weight"], tensors[p + "o_proj.bias"] if self.bias else None)
+        if self.qk_norm:
+            self.q_norm_weight, self.k_norm_weight = tensors[p + "q_norm.weight"], tensors[p + "k_norm.weight"]
+
+    # -- cache ---------------------------------------------------------------
+    def cache_spec(self):
+        return PagedKV(self.num_kv_heads, self.head_dim, self.window)
+
+    # -- step ----------------------------------------------------------------
+    def forward(self, h: torch.Tensor, ctx, cache) -> torch.Tensor:
+        H, Hk, D = self.num_heads, self.num_kv_heads, self.head_dim
+        group = ctx.groups[cache.group]
+        qkv = self.qkv(h)
+        slots = group.slot_mapping if cache.writes else None
+        rotary = self.position.rotary_table(h.device) if self.position is not None else None
+        qw, kw = self.q_norm_weight, self.k_norm_weight
+        if self.position is None or rotary is not None:
+            inv_freq, rot = rotary if rotary is not None else (None, 0)
+            ops.qk_norm_rope_kv(qkv, qw, kw, self.eps, inv_freq, rot, ctx.positions, slots,
+                                cache.k_pool, cache.v_pool, H, Hk, D)
+        else:
+            # An encoding the fused kernel does not know: norm in place, let the
+            # part encode q and k in place, then write the cache.
+            t = qkv.shape[0]
+            ops.qk_norm_rope_kv(qkv, qw, kw, self.eps, None, 0, ctx.positions, None, None, None, H, Hk, D)
+            q, k = qkv[:, : H * D].view(t, H, D), qkv[:, H * D : (H + Hk) * D].view(t, Hk, D)
+            q2, k2 = self.position.apply(q, k, ctx.positions)
+            if q2 is not q:
+                q.copy_(q2)
+            if k2 is not k:
+                k.copy_(k2)
+            ops.qk_norm_rope_kv(qkv, None, None, self.eps, None, 0, ctx.positions, slots,
+                                cache.k_pool, cache.v_pool, H, Hk, D)
+        attn = self._attend(qkv, ctx, cache, group)
+        return self.out(attn)
+
+    def _attend(self, qkv, ctx, cache, group) -> torch.Tensor:
+        H, Hk, D = self.num_heads, self.num_kv_heads, self.head_dim
+        return ops.paged_attention_generic(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
+                                           ctx.seq_of_token, ctx.positions, self.scale, self.window, H, Hk, D,
+                                           qkv.shape[0])

@@ -1,0 +1,127 @@
+"""Interfaces of the parts a layer is put together from.
+
+A part is built from a `PartSpec`: its kind picks the class, `prefix` is where
+its tensors live in the weight file, `params` are its sizes and constants.  No
+part knows which model it is in.
+
+    Part          tensor_specs() -> what it wants from the weight file
+                  bind(tensors, runtime) -> takes them (already on the device)
+    Norm          forward(x) ; add_norm(residual, delta) -> normed
+    Position      an encoding of positions that a mixer applies to q and k
+    Mixer         cache_spec() -> PagedKV | FixedState | None
+                  forward(h, ctx, cache) -> y          h, y: [tokens, hidden]
+    FeedForward   forward(h, ctx) -> y
+    Block         forward(residual, delta, ctx, cache) -> (residual, delta)
+
+`h` and `y` have the engine's element type; the residual stream is float32.
+`ctx` is the step's `StepContext` (engine/batch.py): positions, which request
+each token belongs to, block tables and slot mappings per cache group, state
+slots.  `cache` is the layer's `LayerCache` (cache/manager.py).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+
+@dataclass(frozen=True)
+class TensorSpec:
+    """A tensor a part wants.  `role` decides how random weights are drawn and
+    in which element type the tensor is held:
+      matrix, table: N(0, 0.02); held in the engine's element type
+      norm:          1 + N(0, 0.05); held in float32 (an exact widening)
+      bias:          N(0, 0.02); held in float32
+      int_table:     integers; held as int32"""
+    name: str
+    shape: Tuple[int, ...]
+    role: str = "matrix"
+
+
+@dataclass(frozen=True)
+class Runtime:
+    dtype: torch.dtype
+    device: torch.device
+
+
+@dataclass(frozen=True)
+class PagedKV:
+    """Keys and values of every position in pages; with a window only the last
+    `window` positions are ever read, and older pages are given back."""
+    num_kv_heads: int
+    head_dim: int
+    window: int = 0
+
+
+@dataclass(frozen=True)
+class FixedState:
+    """State of fixed size per request, in a slot that lives as long as the
+    request; zeroed when the slot is handed out."""
+    shape: Tuple[int, ...]
+    dtype: str = "float32"
+
+
+class Part:
+    def __init__(self, prefix: str = ""):
+        self.prefix = prefix
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return []
+
+    def ignored_tensors(self) -> List[str]:
+        """Names that may be in the file and are not an error to find there."""
+        return []
+
+    def bind(self, tensors: Dict[str, torch.Tensor], runtime: Runtime) -> None:
+        self.runtime = runtime
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+    def add_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor],
+                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """residual (float32, updated in place when `rows` is None) += delta;
+        returns the normed sum in the engine's element type.  With `rows` only
+        those rows are normed and `residual` is left as it is."""
+        raise NotImplementedError
+
+
+class Position(Part):
+    """A position encoding applied to queries and keys inside a mixer."""
+
+    def rotary_table(self, device) -> Optional[Tuple[torch.Tensor, int]]:
+        """(float32 inverse frequencies [rot/2], rot) if the encoding is a
+        half-split rotation that the fused kernel can apply; else None."""
+        return None
+
+    def apply(self, q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor):
+        """For encodings the fused kernel does not know: returns (q, k)."""
+        return q, k
+
+
+class Mixer(Part):
+    def cache_spec(self):
+        return None
+
+    def forward(self, h: torch.Tensor, ctx, cache) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block:
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm):
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+
+    def parts(self) -> List[Part]:
+        return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+
+    def forward(self, residual, delta, ctx, cache):
+        raise NotImplementedError
