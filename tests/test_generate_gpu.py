@@ -1,0 +1,97 @@
+"""Generation through the Python entry point against the plain implementation."""
+import numpy as np
+import pytest
+
+import plain_qwen3 as P
+from helpers import BF16_ATOL, BF16_RTOL, TINY, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+
+def engine(folder, name, dtype, **kw):
+    from velox_b200 import Engine, EngineConfig
+    return Engine(folder, EngineConfig(dtype=dtype, page_size=TINY[name]["page_size"], max_model_len=256, **kw),
+                  poison_cache=True)
+
+
+def check_greedy_path(cfg, w, prompt, generated, dtype):
+    """Every generated token is the plain implementation's argmax given the
+    engine's own path so far; in bfloat16, within the rounding bound of it."""
+    logits = P.forward_logits(cfg, w, list(prompt) + list(generated))
+    for n, tok in enumerate(generated):
+        row = logits[len(prompt) - 1 + n]
+        best = int(np.argmax(row))
+        if dtype == "float32":
+            assert tok == best, "token %d: engine %d, plain %d" % (n, tok, best)
+        else:
+            slack = 2 * (BF16_ATOL + BF16_RTOL * abs(row[best]))
+            assert row[best] - row[tok] <= slack, "token %d: engine %d is %.3g below plain's %d" % (
+                n, tok, row[best] - row[tok], best)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_tiny_a(model_folders, dtype):
+    from velox_b200 import SamplingParams
+    cfg, w = P.load_model_folder(model_folders["tiny_a"])
+    prompts = [random_tokens(cfg["vocab_size"], n, 40 + n) for n in (5, 11, 17)]
+    e = engine(model_folders["tiny_a"], "tiny_a", dtype, num_pages=64)
+    outs = e.generate(prompts, SamplingParams(max_tokens=8))
+    assert [len(o) for o in outs] == [8, 8, 8]
+    for p, o in zip(prompts, outs):
+        check_greedy_path(cfg, w, p, o, dtype)
+    if dtype == "float32":
+        assert outs == [P.greedy_generate(cfg, w, p, 8) for p in prompts]
+    assert e.cache.free_pages() == [64] and e.stats()["requests_completed"] == 3
+    e.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_chunked_prefill_mixed_with_decode_and_temperature_tiny_b(model_folders, dtype):
+    """Prompts 1, 9, 23, 40 cut into portions of 7 beside decoding requests;
+    temperature 0.8 with a fixed seed, 6 new tokens."""
+    from velox_b200 import SamplingParams
+    from velox_b200.sampling.rng import uniform
+    cfg, w = P.load_model_folder(model_folders["tiny_b"])
+    prompts = [random_tokens(cfg["vocab_size"], n, 60 + n) for n in (1, 9, 23, 40)]
+    e = engine(model_folders["tiny_b"], "tiny_b", dtype, num_pages=40, chunk_size=7, max_batch_tokens=16)
+    params = [SamplingParams(max_tokens=6, temperature=0.8, seed=1000 + i) for i in range(4)]
+    outs = e.generate(prompts, params)
+    assert [len(o) for o in outs] == [6] * 4
+    again = engine(model_folders["tiny_b"], "tiny_b", dtype, num_pages=40, chunk_size=3, max_batch_tokens=64)
+    assert again.generate(prompts, params) == outs  # the cutting does not change the tokens
+    if dtype == "float32":
+        for i, (p, o) in enumerate(zip(prompts, outs)):
+            logits = P.forward_logits(cfg, w, p + o)
+            for n, tok in enumerate(o):
+                probs = P.probabilities(logits[len(p) - 1 + n], 0.8)
+                assert tok == P.sample_from(probs, uniform(1000 + i, 0, n)), (i, n)
+    assert e.stats()["preemptions"] == 0 and e.cache.free_pages() == [40, 40]
+
+
+def test_pages_run_out_preempted_request_generates_the_same(model_folders):
+    from velox_b200 import SamplingParams
+    cfg, w = P.load_model_folder(model_folders["tiny_a"])
+    prompts = [random_tokens(cfg["vocab_size"], 8, 80 + n) for n in range(3)]
+    roomy = engine(model_folders["tiny_a"], "tiny_a", "float32", num_pages=64)
+    want = roomy.generate(prompts, SamplingParams(max_tokens=16))
+    tight = engine(model_folders["tiny_a"], "tiny_a", "float32", num_pages=12)  # 3 x 24 positions need 18 pages of 4
+    got = tight.generate(prompts, SamplingParams(max_tokens=16))
+    assert tight.stats()["preemptions"] > 0
+    assert got == want
+    assert tight.cache.free_pages() == [12]
+    tight.cache.check()
+
+
+def test_eos_and_refusal(model_folders):
+    from velox_b200 import SamplingParams
+    from velox_b200.engine import RequestRefused
+    cfg, w = P.load_model_folder(model_folders["tiny_a"])
+    prompt = random_tokens(cfg["vocab_size"], 6, 90)
+    e = engine(model_folders["tiny_a"], "tiny_a", "float32", num_pages=64)
+    free_run = e.generate([prompt], SamplingParams(max_tokens=8))[0]
+    stopped = e.generate([prompt], SamplingParams(max_tokens=8, eos_token_ids=[free_run[2]]))[0]
+    assert stopped == free_run[:free_run.index(free_run[2]) + 1]
+    with pytest.raises(RequestRefused):
+        e.add_request(prompt, SamplingParams(max_tokens=1000))
+    with pytest.raises(ValueError):
+        e.add_request([cfg["vocab_size"]], SamplingParams(max_tokens=2))

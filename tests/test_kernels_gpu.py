@@ -1,0 +1,287 @@
+"""Each kernel alone against its plain reference, at sizes other than the models'."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as P
+from helpers import BF16_ATOL, BF16_RTOL
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def ops():
+    from velox_b200.csrc import ops as o
+    return o
+
+
+def close(got, want, dtype, atol32=2e-5, what=""):
+    got = got.detach().double().cpu().numpy()
+    want = np.asarray(want, np.float64)
+    assert got.shape == want.shape, (got.shape, want.shape)
+    assert np.isfinite(got).all(), what + ": non-finite output"
+    err = np.abs(got - want)
+    bound = atol32 + 1e-5 * np.abs(want) if dtype == torch.float32 else BF16_ATOL + BF16_RTOL * np.abs(want)
+    assert (err <= bound).all(), "%s: max err %.3g at %s" % (what, err.max(), np.unravel_index(err.argmax(), err.shape))
+
+
+def rnd(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def f64(t):
+    return t.detach().double().cpu().numpy()
+
+
+# ----------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding(dtype):
+    table = rnd((37, 50), dtype, 0)
+    ids = torch.tensor([0, 36, 5, 5, 17], dtype=torch.int32, device=DEV)
+    out = ops().embedding(ids, table)
+    assert out.dtype == torch.float32
+    assert torch.equal(out, table.float()[ids.long()])
+    bad = ops().embedding(torch.tensor([3, 37], dtype=torch.int32, device=DEV), table)
+    assert torch.isnan(bad[1]).all() and torch.equal(bad[0], table.float()[3])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [48, 1000, 4100])
+def test_add_rmsnorm(dtype, width):
+    rows, eps = 7, 1e-5
+    res = rnd((rows, width), torch.float32, 1)
+    delta = rnd((rows, width), dtype, 2)
+    w = (1 + 0.05 * torch.randn(width)).to(DEV)
+    want_sum = f64(res) + f64(delta)
+    want = P.rms_norm(want_sum, f64(w), eps)
+    r = res.clone()
+    out = ops().add_rmsnorm(r, delta, w, eps, dtype)
+    close(out, want, dtype, what="normed")
+    assert np.allclose(f64(r), want_sum, atol=1e-6)  # the residual holds the float32 sum
+    # no delta: residual untouched
+    r2 = res.clone()
+    out2 = ops().add_rmsnorm(r2, None, w, eps, dtype)
+    close(out2, P.rms_norm(f64(res), f64(w), eps), dtype)
+    assert torch.equal(r2, res)
+    # gathered rows: only those are normed, the residual stays
+    idx = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    r3 = res.clone()
+    out3 = ops().add_rmsnorm(r3, delta, w, eps, dtype, rows=idx)
+    close(out3, want[[6, 0, 3]], dtype)
+    assert torch.equal(r3, res)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_rmsnorm_rows(dtype):
+    x = rnd((11, 80), dtype, 3)
+    w = (1 + 0.05 * torch.randn(80)).to(DEV)
+    close(ops().rmsnorm(x, w, 1e-6), P.rms_norm(f64(x), f64(w), 1e-6), dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("act", ["silu", "gelu", "gelu_pytorch_tanh", "relu"])
+def test_gated_act(dtype, act):
+    x = rnd((9, 2 * 75), dtype, 4, 2.0)
+    g, u = f64(x)[:, :75], f64(x)[:, 75:]
+    if act == "silu":
+        a = P.silu(g)
+    elif act == "gelu":
+        a = 0.5 * g * (1 + np.vectorize(math.erf)(g / math.sqrt(2)))
+    elif act == "gelu_pytorch_tanh":
+        a = 0.5 * g * (1 + np.tanh(math.sqrt(2 / math.pi) * (g + 0.044715 * g ** 3)))
+    else:
+        a = np.maximum(g, 0)
+    close(ops().gated_act(x, act), a * u, dtype)
+
+
+# ----------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,Hk,D,rot,S", [(6, 3, 48, 48, 8), (5, 1, 16, 8, 4), (8, 2, 128, 128, 16), (2, 2, 80, 0, 2)])
+def test_qk_norm_rope_kv(dtype, H, Hk, D, rot, S):
+    T, pages, eps, theta = 13, 9, 1e-5, 1e6
+    qkv = rnd((T, (H + 2 * Hk) * D), dtype, 5)
+    qw = (1 + 0.05 * torch.randn(D)).to(DEV)
+    kw = (1 + 0.05 * torch.randn(D)).to(DEV)
+    positions = torch.tensor([0, 1, 2, 77, 78, 5000, 5001, 31, 32, 33, 3, 40000, 9], dtype=torch.int32, device=DEV)
+    slots = torch.randperm(pages * S)[:T].to(torch.int32).to(DEV)
+    k_pool = torch.full((pages, Hk, S, D), float("nan"), dtype=dtype, device=DEV)
+    v_pool = torch.full((pages, Hk, S, D), float("nan"), dtype=dtype, device=DEV)
+    inv = None
+    if rot:
+        inv = torch.tensor([np.float32(1.0) / np.float32(theta ** (i / rot)) for i in range(0, rot, 2)],
+                           dtype=torch.float32, device=DEV)
+    x = f64(qkv)
+    q = x[:, : H * D].reshape(T, H, D)
+    k = x[:, H * D : (H + Hk) * D].reshape(T, Hk, D)
+    v = x[:, (H + Hk) * D :].reshape(T, Hk, D)
+    qn, kn = P.rms_norm(q, f64(qw), eps), P.rms_norm(k, f64(kw), eps)
+    if rot:
+        pos = positions.cpu().numpy()
+        qn = np.concatenate([P.rope(qn[..., :rot], pos, theta), qn[..., rot:]], -1)
+        kn = np.concatenate([P.rope(kn[..., :rot], pos, theta), kn[..., rot:]], -1)
+    work = qkv.clone()
+    ops().qk_norm_rope_kv(work, qw, kw, eps, inv, rot, positions, slots, k_pool, v_pool, H, Hk, D)
+    close(work[:, : H * D].reshape(T, H, D), qn, dtype, what="q")
+    sl = slots.cpu().numpy()
+    got_k = k_pool[sl // S, :, sl % S, :]
+    got_v = v_pool[sl // S, :, sl % S, :]
+    close(got_k, kn, dtype, what="k in the pool")
+    assert torch.equal(got_v, qkv[:, (H + Hk) * D :].reshape(T, Hk, D))  # values are copied bit for bit
+    untouched = torch.ones(pages * S, dtype=torch.bool)
+    untouched[sl] = False
+    assert torch.isnan(k_pool.reshape(pages, Hk, S, D).permute(0, 2, 1, 3).reshape(pages * S, -1)[untouched]).all()
+    # without a slot mapping nothing is written and keys are treated in place
+    work2 = qkv.clone()
+    ops().qk_norm_rope_kv(work2, qw, kw, eps, inv, rot, positions, None, None, None, H, Hk, D)
+    close(work2[:, H * D : (H + Hk) * D].reshape(T, Hk, D), kn, dtype, what="k in place")
+    assert torch.equal(work2[:, (H + Hk) * D :], qkv[:, (H + Hk) * D :])
+
+
+# ----------------------------------------------------------------------------
+def paged_case(dtype, seqs, H, Hk, D, S, window, seed, spike=None):
+    """seqs: list of (kv_offset, new_tokens).  Builds whole sequences, scatters
+    keys/values into scattered pages, and returns kernel inputs + the plain answer."""
+    rng = np.random.default_rng(seed)
+    total_pages = sum(-(-(o + n) // S) for o, n in seqs) + 5
+    perm = rng.permutation(total_pages)
+    k_pool = torch.full((total_pages, Hk, S, D), float("nan"), dtype=dtype, device=DEV)
+    v_pool = torch.full((total_pages, Hk, S, D), float("nan"), dtype=dtype, device=DEV)
+    max_blocks = max(-(-(o + n) // S) for o, n in seqs) + 2
+    bt = np.full((len(seqs), max_blocks), -1, np.int32)
+    qs, pos, sot, want = [], [], [], []
+    used = 0
+    for i, (off, n) in enumerate(seqs):
+        L = off + n
+        q = torch.randn(L, H, D, generator=torch.Generator().manual_seed(seed * 100 + i)).to(dtype)
+        k = torch.randn(L, Hk, D, generator=torch.Generator().manual_seed(seed * 100 + 50 + i)).to(dtype)
+        v = torch.randn(L, Hk, D, generator=torch.Generator().manual_seed(seed * 100 + 70 + i)).to(dtype)
+        if spike is not None and L > spike:
+            # one far key that every late query of head 0 must find: its score
+            # towers over the others, so the output is that key's value
+            j = spike
+            q[-1, 0] = 0; q[-1, 0, 0] = 12.0
+            k[j, 0] = 0; k[j, 0, 0] = 12.0
+        npg = -(-L // S)
+        pages = perm[used:used + npg]
+        used += npg
+        bt[i, :npg] = pages
+        for p in range(L):
+            k_pool[pages[p // S], :, p % S] = k[p].to(DEV)
+            v_pool[pages[p // S], :, p % S] = v[p].to(DEV)
+        ref = P.causal_attention(f64(q), f64(k), f64(v), window)
+        qs.append(q[off:])
+        want.append(ref[off:])
+        pos += list(range(off, L))
+        sot += [i] * n
+    q_all = torch.cat(qs).reshape(-1, H * D).contiguous().to(DEV)
+    return (q_all, k_pool, v_pool, torch.from_numpy(bt).to(DEV), torch.tensor(sot, dtype=torch.int32, device=DEV),
+            torch.tensor(pos, dtype=torch.int32, device=DEV), np.concatenate(want).reshape(-1, H * D))
+
+
+ATT_CASES = [
+    # (seqs, H, Hk, D, S, window)
+    ([(0, 1)], 4, 2, 16, 4, 0),                              # a sequence's first token
+    ([(0, 3), (0, 2), (0, 1)], 4, 4, 32, 8, 0),              # first tokens, no grouping
+    ([(0, 8), (20, 4), (10, 1)], 8, 2, 64, 4, 0),            # the reference's mixed batch: cold 8, warm 4 @20, decode 1 @10
+    ([(239, 1)] * 8, 8, 2, 128, 16, 0),                      # 8 decodes over 240 keys
+    ([(0, 37)], 6, 3, 48, 8, 0),                             # head size 48, 3 groups, a partial last page
+    ([(0, 50), (45, 5), (63, 1)], 4, 1, 80, 16, 13),         # a window that is no multiple of the page
+    ([(300, 2)], 2, 1, 256, 16, 0),                          # the largest head size
+    ([(31, 1), (32, 1), (33, 1)], 4, 2, 16, 16, 0),          # around a page's edge
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", range(len(ATT_CASES)))
+def test_paged_attention_generic(dtype, case):
+    seqs, H, Hk, D, S, window = ATT_CASES[case]
+    q, kp, vp, bt, sot, pos, want = paged_case(dtype, seqs, H, Hk, D, S, window, seed=case)
+    out = ops().paged_attention_generic(q, H * D, kp, vp, bt, sot, pos, 1 / math.sqrt(D), window, H, Hk, D, q.shape[0])
+    close(out, want, dtype, atol32=1e-5, what="attention case %d" % case)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("far", [0, 3, 250, 511])
+def test_attention_finds_one_far_key_among_hundreds(dtype, far):
+    H, Hk, D, S = 4, 2, 64, 16
+    q, kp, vp, bt, sot, pos, want = paged_case(dtype, [(599, 1)], H, Hk, D, S, 0, seed=11, spike=far)
+    out = ops().paged_attention_generic(q, H * D, kp, vp, bt, sot, pos, 1 / math.sqrt(D), 0, H, Hk, D, 1)
+    close(out, want, dtype, atol32=1e-5)
+    # the spike dominates: head 0's output is (nearly) the far key's value
+    page, off = int(bt[0, far // S]), far % S
+    assert torch.allclose(out[0, :D].float(), vp[page, 0, off].float(), atol=5e-2)
+
+
+# ----------------------------------------------------------------------------
+@pytest.mark.parametrize("M,N,K", [(1, 53, 71), (37, 64, 16), (130, 129, 100), (5, 384, 96)])
+def test_gemm_simt_fp32(M, N, K):
+    a, w = rnd((M, K), torch.float32, 6), rnd((N, K), torch.float32, 7)
+    bias = rnd((N,), torch.float32, 8)
+    close(ops().gemm_nt_simt(a, w), f64(a) @ f64(w).T, torch.float32)
+    close(ops().gemm_nt_simt(a, w, bias), f64(a) @ f64(w).T + f64(bias), torch.float32)
+    # a row's result does not depend on the rows beside it: bit-identical
+    alone = ops().gemm_nt_simt(a[M - 1 :].contiguous(), w)
+    assert torch.equal(alone[0], ops().gemm_nt_simt(a, w)[M - 1])
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(1, 53, 72), (37, 64, 16), (130, 136, 104), (64, 384, 96), (8, 4096, 4096)])
+def test_gemm_bf16(M, N, K, out_dtype):
+    a, w = rnd((M, K), torch.bfloat16, 6), rnd((N, K), torch.bfloat16, 7, 0.05)
+    want = f64(a) @ f64(w).T
+    close(ops().gemm_bf16(a, w, None, out_dtype), want, torch.bfloat16)
+    close(ops().gemm_nt_simt(a, w, None, out_dtype), want, torch.bfloat16)  # the plain product takes bfloat16 too
+    bias = rnd((N,), torch.float32, 8)
+    close(ops().gemm_bf16(a, w, bias, out_dtype), want + f64(bias), torch.bfloat16)
+
+
+# ----------------------------------------------------------------------------
+def test_sample_greedy_ties_and_rows():
+    x = torch.randn(5, 1000, generator=torch.Generator().manual_seed(0)).to(DEV)
+    x[2, 77] = x[2, 400] = 9.0  # the first maximum wins
+    got = ops().sample(x).tolist()
+    assert got == [P.greedy(r) for r in f64(x)] and got[2] == 77
+    wide = torch.randn(3, 151936, generator=torch.Generator().manual_seed(1)).to(DEV)
+    assert ops().sample(wide).tolist() == wide.argmax(-1).tolist()
+
+
+@pytest.mark.parametrize("vocab", [384, 5000, 151936])
+def test_sample_temperature_and_top_p(vocab):
+    from velox_b200.sampling.rng import uniform
+    rows = 12
+    x = (torch.randn(rows, vocab, generator=torch.Generator().manual_seed(2)) * 2.0).to(DEV)
+    temps = [0.0, 0.8, 1.0, 0.5, 1.3, 0.8, 0.8, 1.0, 0.0, 0.7, 2.0, 0.8]
+    tops = [1.0, 1.0, 0.9, 0.5, 1.0, 0.3, 0.95, 0.0, 0.5, 0.999, 0.8, 1.0]
+    us = [uniform(5, 0, i) for i in range(rows)]
+    t = lambda v: torch.tensor(v, dtype=torch.float32, device=DEV)
+    got = ops().sample(x, t(temps), t(tops), t(us)).tolist()
+    xs = f64(x)
+    for r in range(rows):
+        if temps[r] <= 1e-7:
+            assert got[r] == P.greedy(xs[r])
+            continue
+        p = P.probabilities(xs[r], temps[r], tops[r])
+        want = P.sample_from(p, us[r])
+        if got[r] != want:
+            # float32 against float64 may disagree only where u falls on a boundary of the
+            # cumulative distribution, or where the nucleus' edge is a near-tie
+            c = np.cumsum(p)
+            lo, hi = sorted((got[r], want))
+            assert p[got[r]] > 0 and abs(c[lo] - us[r]) < 1e-5 * max(1, hi - lo), (r, got[r], want)
+    # the same inputs give the same tokens
+    assert ops().sample(x, t(temps), t(tops), t(us)).tolist() == got
+
+
+def test_sample_top_p_keeps_only_the_nucleus():
+    x = torch.full((1, 300), -5.0, device=DEV)
+    x[0, [10, 20, 30]] = torch.tensor([3.0, 2.0, 1.0], device=DEV)
+    t = lambda v: torch.tensor([v], dtype=torch.float32, device=DEV)
+    seen = set()
+    for i in range(64):
+        seen.add(ops().sample(x, t(1.0), t(0.85), t(i / 64.0)).item())
+    assert seen == {10, 20}  # p = .66, .24, .09: the first two reach 0.85
+    assert {ops().sample(x, t(1.0), t(0.5), t(i / 64.0)).item() for i in range(64)} == {10}

@@ -1,0 +1,133 @@
+"""Trace replay through bin/trace_run against the plain implementation: the same
+requests whole, with the last 32 tokens one by one, in portions of changing size,
+and mixed with other requests in a pool so small that pages are used again; in
+32-bit and in bfloat16.  The cache pool is filled with NaN first, so a read of a
+slot that was never written (or written by somebody else and not yet
+overwritten) cannot pass unnoticed."""
+import numpy as np
+import pytest
+
+import plain_qwen3 as P
+from helpers import TINY, assert_close, random_tokens, run_trace
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"tiny_a": [70, 45, 33, 90, 1, 2, 3, 64], "tiny_b": [81, 40, 57, 96, 1, 2, 3, 48]}
+
+
+class Trace:
+    def __init__(self):
+        self.steps, self.expect = [], {}
+
+    def add(self, entries, end=(), plain=None):
+        """entries: [(request id, tokens, want, first position)]"""
+        n = len(self.steps)
+        self.steps.append({"step": n, "entries": [{"id": i, "tokens": t, "want": w} for i, t, w, _ in entries],
+                           "end": list(end)})
+        rows = [plain[i][pos + w_] for i, t, w, pos in entries for w_ in w]
+        if rows:
+            self.expect[n] = np.stack(rows)
+
+
+def cut(tokens, sizes):
+    out, at, k = [], 0, 0
+    while at < len(tokens):
+        s = sizes[k % len(sizes)]
+        out.append((at, tokens[at:at + s]))
+        at += s
+        k += 1
+    return out
+
+
+def build_trace(seqs, plain):
+    """seqs: {id: tokens}; plain: {id: logits [T, V]} -> Trace with all four ways of cutting."""
+    tr = Trace()
+    ids = list(seqs)
+    # 1. each request alone and whole
+    for i in ids:
+        t = seqs[i]
+        tr.add([(i, t, list(range(len(t))), 0)], end=[i], plain=plain)
+    # 2. most of it in one step, the last 32 tokens one by one
+    for i in ids:
+        t = seqs[i]
+        head = max(len(t) - 32, 0)
+        if head:
+            tr.add([(i, t[:head], list(range(head)), 0)], plain=plain)
+        for p in range(head, len(t)):
+            tr.add([(i, [t[p]], [0], p)], end=[i] if p == len(t) - 1 else [], plain=plain)
+    # 3. portions of changing size, down to two tokens
+    for i in ids:
+        t = seqs[i]
+        parts = cut(t, [7, 5, 3, 2, 2, 11, 2, 1, 16])
+        for n, (at, toks) in enumerate(parts):
+            tr.add([(i, toks, list(range(len(toks))), at)], end=[i] if n == len(parts) - 1 else [], plain=plain)
+    # 4. mixed: up to four live, portions of some beside decoded tokens of others;
+    #    later requests start when earlier ones end, in the pages those gave back
+    waiting = list(ids)
+    live = {}  # id -> position reached
+    sizes = {}
+    k = 0
+    while waiting or live:
+        while waiting and len(live) < 4:
+            i = waiting.pop(0)
+            live[i] = 0
+            # some requests go in portions then token by token, some token by token early
+            sizes[i] = [[9, 4, 2], [13], [2, 3], [6, 1, 1]][k % 4]
+            k += 1
+        entries, end = [], []
+        for n, i in enumerate(list(live)):
+            t, at = seqs[i], live[i]
+            left = len(t) - at
+            s = 1 if left <= 12 + 5 * (n % 2) else sizes[i][(at + n) % len(sizes[i])]
+            s = min(s, left)
+            if (len(tr.steps) + n) % 5 == 4 and len(live) > 1:
+                continue  # a request may sit out a step and go on later
+            entries.append((i, t[at:at + s], list(range(s)), at))
+            live[i] = at + s
+            if live[i] == len(t):
+                end.append(i)
+                del live[i]
+        if entries:
+            tr.add(entries, end=end, plain=plain)
+    return tr
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_replay_every_way_of_cutting(model_folders, tmp_path, name, dtype):
+    folder = model_folders[name]
+    cfg, w = P.load_model_folder(folder)
+    seqs = {"r%d" % n: random_tokens(cfg["vocab_size"], L, 100 + n) for n, L in enumerate(LENGTHS[name])}
+    plain = {i: P.forward_logits(cfg, w, t) for i, t in seqs.items()}
+    tr = build_trace(seqs, plain)
+    # the four longest live at once, each rounded up to 64: nothing to spare, so pages are used again
+    pool = sum(-(-L // 64) * 64 for L in sorted(LENGTHS[name])[-4:])
+    got = run_trace(folder, dtype, tr.steps, pool, str(tmp_path / "out"), page_size=TINY[name]["page_size"])
+    assert sorted(got) == sorted(tr.expect)
+    for n in sorted(tr.expect):
+        assert_close(got[n], tr.expect[n], dtype, "%s %s step %d %s" % (name, dtype, n, [
+            (e["id"], len(e["tokens"])) for e in tr.steps[n]["entries"]]))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(model_folders, tmp_path, dtype):
+    """Several hundred tokens one by one, two requests side by side."""
+    folder = model_folders["tiny_b"]
+    cfg, w = P.load_model_folder(folder)
+    seqs = {"x": random_tokens(cfg["vocab_size"], 420, 7), "y": random_tokens(cfg["vocab_size"], 333, 8)}
+    plain = {i: P.forward_logits(cfg, w, t) for i, t in seqs.items()}
+    tr = Trace()
+    tr.add([("x", seqs["x"][:20], [19], 0), ("y", seqs["y"][:5], [4], 0)], plain=plain)
+    at = {"x": 20, "y": 5}
+    while at:
+        entries, end = [], []
+        for i in list(at):
+            entries.append((i, [seqs[i][at[i]]], [0], at[i]))
+            at[i] += 1
+            if at[i] == len(seqs[i]):
+                end.append(i)
+                del at[i]
+        tr.add(entries, end=end, plain=plain)
+    got = run_trace(folder, dtype, tr.steps, 448 + 384, str(tmp_path / "out"), page_size=16)
+    for n in sorted(tr.expect):
+        assert_close(got[n], tr.expect[n], dtype, "long decode step %d" % n)

@@ -1,8 +1,10 @@
 """The cache manager: pages of keys and values with a block table per request,
 in groups of layers with the same needs, and slots for fixed-size state.
 
-Layers whose mixers ask for the same `PagedKV` (kv heads, head size, window)
-form a group.  A group has its own page pool, storage
+The manager is told, for every place of the model's running order, what the
+mixer there needs (a layer that runs twice has two places and two caches).
+Places that ask for the same `PagedKV` (kv heads, head size, window) form a
+group.  A group has its own page pool, storage
 [layer, K|V, page, kv head, offset in page, head_dim] (the reference keeps a K
 and a V pool [page, kv head, offset, head_dim] per layer,
 src/paged/pages.rs:62-74, 101-109), and its own block table per request: entry i

@@ -90,7 +90,7 @@ class Engine:
         max_blocks = -(-self.max_model_len // S)
         specs = self.model.cache_specs()
         num_pages = self._pool_pages(specs, max_blocks)
-        self.cache = CacheManager(specs, [l.cache_of for l in self.plan.layers], S, num_pages,
+        self.cache = CacheManager(specs, self.model.cache_sources(), S, num_pages,
                                   cfg.max_running_requests, max_blocks, self.runtime.dtype, self.device,
                                   poison=poison_cache)
         self.runner = ModelRunner(self.model, self.cache, self.device, self.plan.vocab_size)

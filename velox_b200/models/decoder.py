@@ -51,11 +51,30 @@ class DecoderModel:
             self.head.tie(self.embedding.weight)
 
     # -- cache ---------------------------------------------------------------
+    # Caches belong to the places of the running order, not to layers: a layer
+    # that the order names twice shares its weights between the two places, but
+    # each place keeps keys, values or state of its own, so that a position's
+    # result does not depend on how the tokens were cut into steps.
     def cache_specs(self) -> list:
-        """Per layer: the mixer's cache need, or None for a layer that has no
-        cache of its own (none at all, or another layer's: `plan.layers[i].cache_of`)."""
-        return [None if spec.cache_of is not None else block.mixer.cache_spec()
-                for spec, block in zip(self.plan.layers, self.blocks)]
+        """Per place of the running order: the mixer's cache need, or None for a
+        place without a cache of its own (none at all, or another's)."""
+        return [None if self.plan.layers[i].cache_of is not None else self.blocks[i].mixer.cache_spec()
+                for i in self.order]
+
+    def cache_sources(self) -> list:
+        """Per place of the running order: None, or the earlier place whose cache
+        it reads (the latest earlier run of layer `cache_of`)."""
+        out = []
+        for k, i in enumerate(self.order):
+            j = self.plan.layers[i].cache_of
+            if j is None:
+                out.append(None)
+                continue
+            earlier = [m for m in range(k) if self.order[m] == j]
+            if not earlier:
+                raise ValueError("layer %d reads the cache of layer %d, which has not run before it" % (i, j))
+            out.append(earlier[-1])
+        return out
 
     # -- step ----------------------------------------------------------------
     def forward_hidden(self, ctx, cache):
@@ -63,8 +82,8 @@ class DecoderModel:
         whose sum is the last layer's output [tokens, hidden]."""
         residual = self.embedding.forward(ctx.token_ids)
         delta = None
-        for i in self.order:
-            residual, delta = self.blocks[i].forward(residual, delta, ctx, cache.layer(i))
+        for place, i in enumerate(self.order):
+            residual, delta = self.blocks[i].forward(residual, delta, ctx, cache.layer(place))
         return residual, delta
 
     def logits(self, residual, delta, rows: torch.Tensor) -> torch.Tensor:

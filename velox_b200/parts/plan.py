@@ -5,9 +5,10 @@ A `ModelPlan` is what an architecture's plan function makes out of its typed
 configuration.  It names parts by kind (looked up in `parts.registry`) and gives
 each its sizes and constants as parameters, layer by layer, so that one model
 can have different mixers and feed-forwards in different layers.  `order` is the
-list of layer indices in running order; it may name a layer twice.  A layer with
-`cache_of = j` keeps no cache of its own and reads (and does not write) the
-cache of layer j.
+list of layer indices in running order; it may name a layer twice: the two runs
+share the layer's weights, and each has a cache of its own.  A layer with
+`cache_of = j` keeps no cache and reads (and does not write) the cache that the
+latest earlier run of layer j filled.
 """
 from __future__ import annotations
 
