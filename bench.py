@@ -1,0 +1,238 @@
+#!/usr/bin/env python3
+"""Benchmark of velox_b200: decode tokens per second of a Qwen3-8B-shaped model
+with random weights on one B200, plus prefill, batch-1 and batch-64 points and
+roofline fractions.  Prints ONE JSON line.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+
+A "step" is one decode step of the whole batch.  The timed decode steps are the
+last K before the requests reach the context length, so the cache they read is
+as long as it gets.  Weights (15 GB) and cache are far larger than L2, so every
+step reads them from memory; nothing is flushed between steps.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# Qwen3-8B shape: the benchmark configuration (36 layers, hidden 4096, 32 query
+# heads, 8 kv heads of 128, intermediate 12288, vocabulary 151936, untied head).
+MODEL = dict(vocab_size=151936, hidden_size=4096, intermediate_size=12288, num_hidden_layers=36,
+             num_attention_heads=32, head_dim=128, attention_bias=False, num_key_value_heads=8,
+             max_position_embeddings=40960, tie_word_embeddings=False, rope_theta=1000000.0,
+             rms_norm_eps=1e-6, hidden_act="silu")
+CONTEXT, PROMPT, PAGE, BATCH, SEED = 4096, 2048, 16, 8, 2
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(p):
+        try:
+            with open(p) as f:
+                raw = json.load(f)
+            out = dict(FALLBACK_PEAKS)
+            for k in out:
+                if isinstance(raw.get(k), (int, float)):
+                    out[k] = float(raw[k])
+            out["source"] = "measured"
+            return out
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.QUERY,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        mhz = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(mhz)}
+
+
+def decode_bytes(cfg, layers, batch, kv_len, elt=2):
+    """Bytes a decode step has to read: every weight once, and the live requests' cache."""
+    E, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    H, Hk, D = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer = ((H + 2 * Hk) * D * E + E * H * D + 3 * I * E) * elt
+    weights = layers * per_layer + V * E * elt  # head; the embedding rows read are negligible
+    kv = layers * 2 * Hk * D * elt * batch * kv_len
+    return weights + kv
+
+
+def prefill_flops(cfg, layers, tokens):
+    E, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    H, Hk, D = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    linear = 2 * tokens * layers * ((H + 2 * Hk) * D * E + E * H * D + 3 * I * E)
+    attn = layers * H * 2 * D * tokens * tokens  # causal: half of 4 D T^2
+    return linear + attn + 2 * V * E
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (recorded in config)")
+    ap.add_argument("--batch", type=int, default=BATCH)
+    ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64 and prefill")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a Rust project whose GPU path is Apple Metal: pip finds neither setup.py "
+                          "nor pyproject.toml, there is no Rust toolchain, and no Metal device on this box"}))
+        return 0
+    if args.gpus != 1:
+        print("bench.py: this engine runs on one GPU; --gpus %d is not supported" % args.gpus)
+        return 2
+    K, W = max(1, args.steps), max(3, args.warmup)
+
+    import torch
+    from velox_b200 import Engine, EngineConfig, Qwen3Config, SamplingParams
+    from velox_b200.csrc import ops
+    from velox_b200.engine import StepEntry
+
+    layers = args.layers or MODEL["num_hidden_layers"]
+    raw = dict(MODEL, num_hidden_layers=layers)
+    cfg = Qwen3Config.from_dict(raw)
+    pk = peaks()
+    max_batch = 64 if not args.skip_points else args.batch
+    engine = Engine(model_config=cfg, random_seed=SEED, config=EngineConfig(
+        dtype="bfloat16", page_size=PAGE, num_pages=max_batch * (CONTEXT // PAGE + 1) + 8,
+        max_running_requests=max_batch, max_batch_tokens=2048, max_model_len=CONTEXT + PAGE))
+    gen = torch.Generator().manual_seed(SEED)
+
+    def prompts(n, length):
+        return torch.randint(0, cfg.vocab_size, (n, length), generator=gen).tolist()
+
+    def timed(fn, steps):
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / steps
+
+    def decode_run(batch, steps, warmup):
+        """`batch` requests prefilled so that the timed steps end at the context
+        length.  Times `steps` steps through the public entry point (host ids in,
+        sampled ids out, every step), then `steps` steps of the step function and
+        sampler alone (ids stay on the device).  Returns (ms end to end, ms on the
+        device, kernel launches per device step, mean cache length of the device steps)."""
+        start = CONTEXT - 2 * steps - warmup - 1
+        sp = SamplingParams(max_tokens=2 * steps + warmup + 1, ignore_eos=True)
+        for p in prompts(batch, start):
+            engine.add_request(p, SamplingParams(**vars(sp)))
+        while any(engine.cache.length(r) < start for r in engine.scheduler.running) or engine.scheduler.waiting:
+            engine.step()
+        for _ in range(warmup):
+            engine.step()
+        e2e_ms = timed(engine.step, steps)
+        assert len(engine.scheduler.running) == batch
+        entries = [StepEntry(r.request_id, [r.generated[-1]], [0]) for r in engine.scheduler.running.values()]
+
+        def device_step():
+            ops.sample(engine.run_step(entries))
+        n0 = ops.launch_count()
+        dev_ms = timed(device_step, steps)
+        launches = (ops.launch_count() - n0) // steps
+        for r in list(engine.scheduler.running.values()):
+            engine.scheduler._finish(r, "length")
+        return e2e_ms, dev_ms, launches, CONTEXT - steps // 2
+
+    out = {"metric": "decode tok/s @ batch %d, Qwen3-8B bf16, context %d" % (args.batch, CONTEXT),
+           "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "higher_is_better": True, "scaling": "weak",
+           "vs_baseline": None, "dtype": "bf16", "data": "synthetic: random weights N(0,0.02) seed 2, uniform random token ids"}
+
+    with ClockSampler() as clocks:
+        e2e_ms, ms, launches, kv_mid = decode_run(args.batch, K, W)
+    out["clocks"] = clocks.summary()
+    out.update({"value": round(args.batch * 1000.0 / ms, 1), "ms_per_step": round(ms, 4),
+                "gpu_launches": int(launches * K)})
+    # per step through the entry point: the step's description (token ids, positions,
+    # block tables, slot mapping) goes up in one pinned copy, the sampled ids come back
+    h2d = 4 * (args.batch * 6 + 1 + args.batch * (engine.cache.max_blocks + 1))
+    out["e2e"] = {"value": round(args.batch * 1000.0 / e2e_ms, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+                  "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch}
+    nbytes = decode_bytes(raw, layers, args.batch, kv_mid)
+    ach = nbytes / (ms * 1e-3) / 1e9
+    out["roofline"] = {"bound": "hbm", "achieved": round(ach, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                       "frac": round(ach / pk["hbm_gbs"], 4), "peak_source": pk["source"]}
+
+    if not args.skip_points:
+        # prefill: one prompt of 2,048 tokens in one step
+        toks = prompts(1, PROMPT)[0]
+
+        def one_prefill():
+            engine.cache.add_request("prefill")
+            engine.run_step([StepEntry("prefill", toks, [PROMPT - 1])])
+            engine.cache.release("prefill")
+        for _ in range(3):
+            one_prefill()
+        pms = timed(one_prefill, 5)
+        fl = prefill_flops(raw, layers, PROMPT)
+        out["prefill"] = {"value": round(PROMPT * 1000.0 / pms, 1), "tokens": PROMPT, "ms": round(pms, 3),
+                          "frac": round(fl / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+        pts = {}
+        for b in (1, 64):
+            steps = min(K, 32)
+            _, m, _, _ = decode_run(b, steps, 4)
+            pts["decode_b%d" % b] = round(b * 1000.0 / m, 1)
+        out["points"] = pts
+
+    out["config"] = {"model": "Qwen3-8B shape", "layers": layers, "layers_full": MODEL["num_hidden_layers"],
+                     "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                     "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                     "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT, "page_size": PAGE,
+                     "parallelism": "single GPU", "l2": "inputs larger than L2 (weights 15 GB)",
+                     "peaks": pk["source"]}
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -68,7 +68,17 @@ def _declare(lib) -> None:
         fn.restype = c_int
 
 
+_LAUNCHES = 0
+
+
+def launch_count() -> int:
+    """Calls of this library's kernels so far (library matrix products are not counted)."""
+    return _LAUNCHES
+
+
 def _check(code: int, what: str) -> None:
+    global _LAUNCHES
+    _LAUNCHES += 1
     if code == 0:
         return
     if code < 0:

@@ -56,11 +56,12 @@ def _eos_ids(folder: Optional[str], raw: Dict) -> List[int]:
 class Engine:
     def __init__(self, model_dir: Optional[str] = None, config: Optional[EngineConfig] = None, *,
                  model_config: Optional[ModelConfig] = None, random_seed: Optional[int] = None,
-                 poison_cache: bool = False):
+                 poison_cache: bool = False, cache_memory_limit: Optional[int] = None):
         """Loads `model_dir` (config.json + safetensors).  Without a folder, a
         typed `model_config` and a `random_seed` give a model with random
         weights made on the device."""
         self.config = config or EngineConfig()
+        self.cache_memory_limit = cache_memory_limit
         if not torch.cuda.is_available():
             raise RuntimeError("velox_b200 runs on a CUDA device (sm_100a); none is visible")
         self.device = torch.device(self.config.device)
@@ -111,7 +112,10 @@ class Engine:
         if per_page == 0:
             return max(1, min(wanted, 1024))
         free, _ = torch.cuda.mem_get_info(self.device)
-        return max(1, min(wanted, int(free * 0.85) // per_page))
+        room = int(free * 0.85)
+        if self.cache_memory_limit is not None:
+            room = min(room, int(self.cache_memory_limit))
+        return max(1, min(wanted, room // per_page))
 
     # -- requests ---------------------------------------------------------------
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> int:
