@@ -1,11 +1,12 @@
 """Tiny configurations and helpers shared by the tests.
 
-Two configurations of the architecture that differ in every size and option:
+Configurations of the architecture that differ in every size and option:
 
             layers hidden heads kv  head_dim inter vocab theta  eps   head    bias  window      page
   tiny_a      2     64     4    2     16     128   256   1e4    1e-6  tied    no    none          4
   tiny_b      3     96     8    2     32     160   384   1e6    1e-5  untied  yes   20 (layers    8
                                                                                     1 and 2)
+  tiny_c      2     128    4    2     64     192   300   5e5    1e-6  untied  no    40 (layer 1)  16
 """
 import json
 import os
@@ -29,6 +30,14 @@ TINY = {
                     num_attention_heads=8, head_dim=32, attention_bias=True, num_key_value_heads=2,
                     max_position_embeddings=1024, tie_word_embeddings=False, rope_theta=1000000.0,
                     rms_norm_eps=1e-5, hidden_act="silu", use_sliding_window=True, sliding_window=20,
+                    max_window_layers=1)),
+    # head size 64 and pages of 16: the sizes the tensor-core attention kernels take
+    "tiny_c": dict(
+        seed=2, page_size=16,
+        config=dict(vocab_size=300, hidden_size=128, intermediate_size=192, num_hidden_layers=2,
+                    num_attention_heads=4, head_dim=64, attention_bias=False, num_key_value_heads=2,
+                    max_position_embeddings=2048, tie_word_embeddings=False, rope_theta=500000.0,
+                    rms_norm_eps=1e-6, hidden_act="silu", use_sliding_window=True, sliding_window=40,
                     max_window_layers=1)),
 }
 

@@ -285,3 +285,66 @@ def test_sample_top_p_keeps_only_the_nucleus():
         seen.add(ops().sample(x, t(1.0), t(0.85), t(i / 64.0)).item())
     assert seen == {10, 20}  # p = .66, .24, .09: the first two reach 0.85
     assert {ops().sample(x, t(1.0), t(0.5), t(i / 64.0)).item() for i in range(64)} == {10}
+
+
+# ----------------------------------------------------------------------------
+DECODE_CASES = [
+    # (kv lengths, H, Hk, D, S, window)
+    ([1, 2, 15, 16, 17], 8, 2, 128, 16, 0),          # first tokens, around a page's edge
+    ([255, 256, 257, 600, 1000], 8, 2, 128, 16, 0),  # around the split boundary (256 keys), several pieces
+    ([700, 33, 300], 6, 6, 64, 32, 0),               # no grouping, head size 64, pages of 32
+    ([900, 64, 257], 16, 1, 64, 16, 0),              # 16 query heads share one kv head
+    ([700, 40, 290, 5], 4, 2, 128, 16, 270),         # a window that crosses split boundaries
+    ([3000], 32, 8, 128, 16, 0),                     # the flagship's head layout, 12 pieces
+]
+
+
+@pytest.mark.parametrize("case", range(len(DECODE_CASES)))
+def test_paged_decode_attention(case):
+    lens, H, Hk, D, S, window = DECODE_CASES[case]
+    seqs = [(n - 1, 1) for n in lens]
+    q, kp, vp, bt, sot, pos, want = paged_case(torch.bfloat16, seqs, H, Hk, D, S, window, seed=40 + case)
+    out = ops().paged_decode_attention(q, H * D, kp, vp, bt, sot, pos, 1 / math.sqrt(D), window, H, Hk, D,
+                                       len(lens), max(lens))
+    close(out, want, torch.bfloat16, what="decode attention case %d" % case)
+    # and it agrees with the general kernel far more closely than with the bound
+    gen = ops().paged_attention_generic(q, H * D, kp, vp, bt, sot, pos, 1 / math.sqrt(D), window, H, Hk, D, len(lens))
+    assert (out.float() - gen.float()).abs().max() < 2e-2
+
+
+@pytest.mark.parametrize("far", [0, 17, 255, 256, 700, 1023])
+def test_decode_attention_finds_one_far_key(far):
+    H, Hk, D, S = 8, 2, 128, 16
+    q, kp, vp, bt, sot, pos, want = paged_case(torch.bfloat16, [(1099, 1)], H, Hk, D, S, 0, seed=12, spike=far)
+    out = ops().paged_decode_attention(q, H * D, kp, vp, bt, sot, pos, 1 / math.sqrt(D), 0, H, Hk, D, 1, 1100)
+    close(out, want, torch.bfloat16)
+    page, off = int(bt[0, far // S]), far % S
+    assert torch.allclose(out[0, :D].float(), vp[page, 0, off].float(), atol=5e-2)
+
+
+def test_decode_attention_token_rows_and_batch_independence():
+    """Requests picked out of a larger batch by row; a request's output does not
+    depend on which others are beside it."""
+    H, Hk, D, S = 8, 2, 128, 16
+    seqs = [(0, 5), (499, 1), (0, 3), (299, 1), (1200, 1)]
+    q, kp, vp, bt, sot, pos, want = paged_case(torch.bfloat16, seqs, H, Hk, D, S, 0, seed=13)
+    rows = torch.tensor([5, 9, 10], dtype=torch.int32, device=DEV)  # the three single-token requests
+    out = torch.zeros((11, H * D), dtype=torch.bfloat16, device=DEV)
+    ops().paged_decode_attention(q, H * D, kp, vp, bt, sot, pos, 1 / math.sqrt(D), 0, H, Hk, D, 3, 1201,
+                                 token_rows=rows, out=out)
+    close(out[rows.long()], want[[5, 9, 10]], torch.bfloat16)
+    assert (out[:5] == 0).all()
+    alone = torch.zeros_like(out)
+    ops().paged_decode_attention(q, H * D, kp, vp, bt, sot, pos, 1 / math.sqrt(D), 0, H, Hk, D, 1, 500,
+                                 token_rows=rows[:1], out=alone)
+    assert torch.equal(alone[5], out[5])  # bit-identical alone and in company
+
+
+def test_decode_attention_refuses_what_it_cannot_do():
+    from velox_b200.csrc.ops import KernelError
+    q, kp, vp, bt, sot, pos, _ = paged_case(torch.bfloat16, [(9, 1)], 4, 2, 48, 16, 0, seed=14)
+    with pytest.raises(KernelError, match="size"):
+        ops().paged_decode_attention(q, 4 * 48, kp, vp, bt, sot, pos, 0.1, 0, 4, 2, 48, 1, 10)
+    assert not ops().decode_attention_supported(torch.bfloat16, 48, 16, 2)
+    assert not ops().decode_attention_supported(torch.bfloat16, 128, 8, 2)
+    assert not ops().decode_attention_supported(torch.float32, 128, 16, 2)

@@ -12,7 +12,8 @@ from helpers import TINY, assert_close, random_tokens, run_trace
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"tiny_a": [70, 45, 33, 90, 1, 2, 3, 64], "tiny_b": [81, 40, 57, 96, 1, 2, 3, 48]}
+LENGTHS = {"tiny_a": [70, 45, 33, 90, 1, 2, 3, 64], "tiny_b": [81, 40, 57, 96, 1, 2, 3, 48],
+           "tiny_c": [300, 45, 129, 77, 1, 2, 17, 64]}
 
 
 class Trace:
@@ -93,7 +94,7 @@ def build_trace(seqs, plain):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c"])
 def test_replay_every_way_of_cutting(model_folders, tmp_path, name, dtype):
     folder = model_folders[name]
     cfg, w = P.load_model_folder(folder)
@@ -112,7 +113,7 @@ def test_replay_every_way_of_cutting(model_folders, tmp_path, name, dtype):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding(model_folders, tmp_path, dtype):
     """Several hundred tokens one by one, two requests side by side."""
-    folder = model_folders["tiny_b"]
+    folder = model_folders["tiny_c"]
     cfg, w = P.load_model_folder(folder)
     seqs = {"x": random_tokens(cfg["vocab_size"], 420, 7), "y": random_tokens(cfg["vocab_size"], 333, 8)}
     plain = {i: P.forward_logits(cfg, w, t) for i, t in seqs.items()}

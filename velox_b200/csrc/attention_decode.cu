@@ -1,0 +1,371 @@
+// Paged attention for decoded tokens (one query per request), bfloat16, with the
+// key/value range of a request split over several blocks and a second pass that
+// joins the pieces.
+//
+// grid (split, kv head, request); 4 warps.  A block takes `chunk_tiles` tiles of
+// 16 keys of one kv head of one request and ALL the query heads of that kv head
+// (the group), so every key and value is read from memory once; the group's
+// queries fill the rows of one 16-row tensor-core tile.  Each warp streams its
+// own tiles (tile t goes to warp t mod 4) through a 3-stage cp.async pipeline
+// of its own in shared memory, computes S = Q K^T and O += P V with
+// mma.sync.m16n8k16 (bf16 in, float32 out) and keeps a running maximum, sum and
+// accumulator per query row in float32 (online softmax, base 2).  The four
+// warps' states are merged in shared memory.  A request whose whole range fits
+// one block writes its output at once; otherwise the block writes its
+// unnormalised accumulator and (max, sum) to scratch, and `combine` joins them.
+//
+// Split boundaries depend only on the request's own key range (fixed number of
+// keys per block), never on the batch, so a request's output does not depend on
+// what else is in the step.
+//
+// Sizes: head size 64 or 128; page size a multiple of 16; group size up to 16;
+// any number of heads; an optional window.  Other sizes are refused (the caller
+// then uses the general kernel).
+#include "common.cuh"
+
+#define DEC_WARPS 4
+#define DEC_STAGES 3
+#define LOG2E 1.4426950408889634f
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+// Shared memory of a block: per warp, DEC_STAGES stages of a K tile and a V tile
+// [16 keys][D] bf16, 16-byte chunks of a row XOR-swizzled with the row index so
+// that ldmatrix reads hit distinct banks.  After the main loop the same memory
+// holds the warps' states for the merge.
+template <int D>
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+paged_decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __restrict__ k_pool,
+                              const bf16* __restrict__ v_pool, const int* __restrict__ block_table,
+                              int max_blocks, const int* __restrict__ token_rows,
+                              const int* __restrict__ seq_of_token, const int* __restrict__ positions,
+                              float* __restrict__ part_o, float* __restrict__ part_ml, int max_splits,
+                              bf16* __restrict__ out, int out_row_stride, float scale_log2, int window,
+                              int H, int Hk, int S, int chunk_tiles) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    constexpr int TILE_BYTES = 16 * D * 2;
+    constexpr int CHUNKS_PER_ROW = D / 8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+    const int G = H / Hk;
+    const int row_tok = token_rows ? token_rows[b] : b;
+    const int seq = seq_of_token[row_tok];
+    const int kv_len = positions[row_tok] + 1;
+    const int start = (window > 0 && kv_len > window) ? kv_len - window : 0;
+    const int tile_first = start >> 4;
+    const int tile_last = (kv_len + 15) >> 4;  // exclusive
+    const int nsplits = (tile_last - tile_first + chunk_tiles - 1) / chunk_tiles;
+    if (split >= nsplits) return;
+    const int tile_begin = tile_first + split * chunk_tiles;
+    const int tile_end = min(tile_begin + chunk_tiles, tile_last);
+    const int* bt = block_table + (size_t)seq * max_blocks;
+
+    unsigned char* my_smem = smem_raw + (size_t)warp * DEC_STAGES * 2 * TILE_BYTES;
+
+    // queries of the group: rows of the A operand, kept in registers
+    unsigned qf[D / 16][4];
+    {
+        const int r0 = lane >> 2, r1 = r0 + 8;
+        const bf16* q0 = q + (size_t)row_tok * q_row_stride + (size_t)(hk * G + r0) * D;
+        const bf16* q1 = q + (size_t)row_tok * q_row_stride + (size_t)(hk * G + r1) * D;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+            const int c = kk * 16 + (lane & 3) * 2;
+            qf[kk][0] = r0 < G ? *reinterpret_cast<const unsigned*>(q0 + c) : 0u;
+            qf[kk][1] = r1 < G ? *reinterpret_cast<const unsigned*>(q1 + c) : 0u;
+            qf[kk][2] = r0 < G ? *reinterpret_cast<const unsigned*>(q0 + c + 8) : 0u;
+            qf[kk][3] = r1 < G ? *reinterpret_cast<const unsigned*>(q1 + c + 8) : 0u;
+        }
+    }
+
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    const int first = tile_begin + warp;
+    const int count = first < tile_end ? (tile_end - first + DEC_WARPS - 1) / DEC_WARPS : 0;
+
+    auto issue = [&](int j) {
+        const int key0 = (first + j * DEC_WARPS) << 4;
+        const int page = bt[key0 / S];
+        const size_t base = (((size_t)page * Hk + hk) * S + (key0 % S)) * D;
+        unsigned char* ks = my_smem + (size_t)(j % DEC_STAGES) * 2 * TILE_BYTES;
+        unsigned char* vs = ks + TILE_BYTES;
+        const unsigned char* kg = reinterpret_cast<const unsigned char*>(k_pool + base);
+        const unsigned char* vg = reinterpret_cast<const unsigned char*>(v_pool + base);
+#pragma unroll
+        for (int i = 0; i < (16 * CHUNKS_PER_ROW) / 32; ++i) {
+            const int c = lane + 32 * i;
+            const int r = c / CHUNKS_PER_ROW, cc = c % CHUNKS_PER_ROW;
+            const int dst = r * (D * 2) + ((cc ^ (r & 7)) << 4);
+            cp_async16(ks + dst, kg + (size_t)c * 16);
+            cp_async16(vs + dst, vg + (size_t)c * 16);
+        }
+    };
+
+#pragma unroll
+    for (int s = 0; s < DEC_STAGES - 1; ++s) {
+        if (s < count) issue(s);
+        cp_async_commit();
+    }
+
+    for (int i = 0; i < count; ++i) {
+        if (i + DEC_STAGES - 1 < count) issue(i + DEC_STAGES - 1);
+        cp_async_commit();
+        cp_async_wait<DEC_STAGES - 1>();
+        __syncwarp();
+        const int key0 = (first + i * DEC_WARPS) << 4;
+        unsigned char* ks = my_smem + (size_t)(i % DEC_STAGES) * 2 * TILE_BYTES;
+        unsigned char* vs = ks + TILE_BYTES;
+        if (key0 + 16 > kv_len) {
+            // Rows past the last key were never written (they may hold anything,
+            // NaN included): their probabilities are zero, but 0 * NaN is NaN in
+            // the tensor core, so the value rows are cleared.
+            for (int c = lane; c < 16 * CHUNKS_PER_ROW; c += 32) {
+                const int r = c / CHUNKS_PER_ROW;
+                if (key0 + r >= kv_len) *reinterpret_cast<uint4*>(vs + (size_t)c * 16) = make_uint4(0, 0, 0, 0);
+            }
+            __syncwarp();
+        }
+
+        // S = Q K^T for 16 keys: two n-tiles of 8 keys
+        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+            const int mi = lane >> 3;
+            const int r = ((mi >> 1) << 3) + (lane & 7);
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+                const int cc = 2 * kk + (mi & 1);
+                unsigned b00, b01, b10, b11;
+                ldmatrix_x4(b00, b01, b10, b11, ks + r * (D * 2) + ((cc ^ (r & 7)) << 4));
+                mma_bf16(s0, qf[kk], b00, b01);
+                mma_bf16(s1, qf[kk], b10, b11);
+            }
+        }
+        // scale, mask, online softmax (base 2).  Thread holds rows lane/4 and
+        // lane/4 + 8, key columns (lane%4)*2 + {0,1} of each n-tile.
+        const int kc = key0 + ((lane & 3) << 1);
+        float sv[2][4];  // [row half][n-tile 0: 2 cols, n-tile 1: 2 cols]
+        sv[0][0] = s0[0]; sv[0][1] = s0[1]; sv[0][2] = s1[0]; sv[0][3] = s1[1];
+        sv[1][0] = s0[2]; sv[1][1] = s0[3]; sv[1][2] = s1[2]; sv[1][3] = s1[3];
+        unsigned pa[4];
+#pragma unroll
+        for (int hrow = 0; hrow < 2; ++hrow) {
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int key = kc + (c & 1) + ((c >> 1) << 3);
+                const bool ok = key >= start && key < kv_len;
+                sv[hrow][c] = ok ? sv[hrow][c] * scale_log2 : -INFINITY;
+                mx = fmaxf(mx, sv[hrow][c]);
+            }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m[hrow], mx);
+            // a row with no visible key so far keeps m = -inf; exp2f(-inf - (-inf)) must not be formed
+            const float alpha = (m_new == -INFINITY) ? 1.f : exp2f(m[hrow] - m_new);
+            float ps = 0.f;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const float p = (m_new == -INFINITY) ? 0.f : exp2f(sv[hrow][c] - m_new);
+                sv[hrow][c] = p;
+                ps += p;
+            }
+            l[hrow] = l[hrow] * alpha + ps;
+            m[hrow] = m_new;
+#pragma unroll
+            for (int i2 = 0; i2 < D / 8; ++i2) {
+                o[i2][2 * hrow] *= alpha;
+                o[i2][2 * hrow + 1] *= alpha;
+            }
+        }
+        pa[0] = pack_bf16(sv[0][0], sv[0][1]);
+        pa[1] = pack_bf16(sv[1][0], sv[1][1]);
+        pa[2] = pack_bf16(sv[0][2], sv[0][3]);
+        pa[3] = pack_bf16(sv[1][2], sv[1][3]);
+        // O += P V
+        {
+            const int mi = lane >> 3;
+            const int r = ((mi & 1) << 3) + (lane & 7);
+#pragma unroll
+            for (int nt = 0; nt < D / 8; nt += 2) {
+                const int cc = nt + (mi >> 1);
+                unsigned v00, v01, v10, v11;
+                ldmatrix_x4_trans(v00, v01, v10, v11, vs + r * (D * 2) + ((cc ^ (r & 7)) << 4));
+                mma_bf16(o[nt], pa, v00, v01);
+                mma_bf16(o[nt + 1], pa, v10, v11);
+            }
+        }
+        __syncwarp();
+    }
+    cp_async_wait<0>();
+
+    // row sums: add the four threads of a quad
+#pragma unroll
+    for (int hrow = 0; hrow < 2; ++hrow) {
+        l[hrow] += __shfl_xor_sync(0xffffffffu, l[hrow], 1);
+        l[hrow] += __shfl_xor_sync(0xffffffffu, l[hrow], 2);
+    }
+    __syncthreads();  // every warp is done with its stages: reuse the memory
+    float* om = reinterpret_cast<float*>(smem_raw);                 // [warps][16][D]
+    float* mls = om + DEC_WARPS * 16 * D;                            // [warps][16][2]
+#pragma unroll
+    for (int hrow = 0; hrow < 2; ++hrow) {
+        const int r = (lane >> 2) + 8 * hrow;
+        if (r < G) {
+            float* dst = om + ((size_t)warp * 16 + r) * D;
+#pragma unroll
+            for (int nt = 0; nt < D / 8; ++nt) {
+                const int d = nt * 8 + ((lane & 3) << 1);
+                dst[d] = o[nt][2 * hrow];
+                dst[d + 1] = o[nt][2 * hrow + 1];
+            }
+            if ((lane & 3) == 0) {
+                mls[((size_t)warp * 16 + r) * 2] = m[hrow];
+                mls[((size_t)warp * 16 + r) * 2 + 1] = l[hrow];
+            }
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * D; idx += DEC_WARPS * 32) {
+        const int g = idx / D, d = idx % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, mls[((size_t)w * 16 + g) * 2]);
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) {
+            const float mw = mls[((size_t)w * 16 + g) * 2];
+            const float wgt = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+            L += wgt * mls[((size_t)w * 16 + g) * 2 + 1];
+            O += wgt * om[((size_t)w * 16 + g) * D + d];
+        }
+        const int h = hk * G + g;
+        if (nsplits == 1) {
+            out[(size_t)row_tok * out_row_stride + (size_t)h * D + d] = __float2bfloat16_rn(O / L);
+        } else {
+            const size_t p = ((size_t)b * H + h) * max_splits + split;
+            part_o[p * D + d] = O;
+            if (d == 0) { part_ml[p * 2] = M; part_ml[p * 2 + 1] = L; }
+        }
+    }
+}
+
+// Joins the pieces of requests that were split: one block per (request, head).
+template <int D>
+__global__ void paged_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                            int max_splits, const int* __restrict__ token_rows,
+                                            const int* __restrict__ positions, bf16* __restrict__ out,
+                                            int out_row_stride, int window, int H, int chunk_tiles) {
+    const int b = blockIdx.x, h = blockIdx.y;
+    const int row_tok = token_rows ? token_rows[b] : b;
+    const int kv_len = positions[row_tok] + 1;
+    const int start = (window > 0 && kv_len > window) ? kv_len - window : 0;
+    const int ntiles = ((kv_len + 15) >> 4) - (start >> 4);
+    const int nsplits = (ntiles + chunk_tiles - 1) / chunk_tiles;
+    if (nsplits <= 1) return;  // written by the first pass
+    const size_t p0 = ((size_t)b * H + h) * max_splits;
+    float M = -INFINITY;
+    for (int s = 0; s < nsplits; ++s) M = fmaxf(M, part_ml[(p0 + s) * 2]);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float L = 0.f, O = 0.f;
+        for (int s = 0; s < nsplits; ++s) {
+            const float ms = part_ml[(p0 + s) * 2];
+            const float wgt = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
+            L += wgt * part_ml[(p0 + s) * 2 + 1];
+            O += wgt * part_o[(p0 + s) * D + d];
+        }
+        out[(size_t)row_tok * out_row_stride + (size_t)h * D + d] = __float2bfloat16_rn(O / L);
+    }
+}
+
+// Scratch the two passes need, in floats: accumulators [requests, H, max_splits, D]
+// then (max, sum) [requests, H, max_splits, 2].
+extern "C" long long vx_paged_decode_scratch_floats(int requests, int H, int D, int max_splits) {
+    return (long long)requests * H * max_splits * (D + 2);
+}
+
+template <int D>
+static int launch_decode(const bf16* q, int q_row_stride, const bf16* k_pool, const bf16* v_pool,
+                         const int* block_table, int max_blocks, const int* token_rows,
+                         const int* seq_of_token, const int* positions, float* scratch, int max_splits,
+                         bf16* out, int out_row_stride, float scale, int window, int requests, int H, int Hk,
+                         int S, int chunk_tiles, cudaStream_t stream) {
+    const size_t smem = (size_t)DEC_WARPS * DEC_STAGES * 2 * 16 * D * 2;
+    static bool configured = false;  // per process and instantiation; the attribute is per device function
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(paged_decode_attention_kernel<D>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    float* part_o = scratch;
+    float* part_ml = scratch ? scratch + (size_t)requests * H * max_splits * D : nullptr;
+    dim3 grid(max_splits, Hk, requests);
+    paged_decode_attention_kernel<D><<<grid, DEC_WARPS * 32, smem, stream>>>(
+        q, q_row_stride, k_pool, v_pool, block_table, max_blocks, token_rows, seq_of_token, positions, part_o,
+        part_ml, max_splits, out, out_row_stride, scale * LOG2E, window, H, Hk, S, chunk_tiles);
+    VX_LAUNCH_CHECK();
+    if (max_splits > 1) {
+        dim3 cgrid(requests, H);
+        paged_decode_combine_kernel<D><<<cgrid, D <= 64 ? 64 : 128, 0, stream>>>(
+            part_o, part_ml, max_splits, token_rows, positions, out, out_row_stride, window, H, chunk_tiles);
+        VX_LAUNCH_CHECK();
+    }
+    return VX_OK;
+}
+
+// One query token per request.  `token_rows[i]` is the token row (in q, out,
+// seq_of_token, positions) of request i, or null when request i is row i.
+// `max_splits` bounds the pieces of any request: ceil(ceil(max keys / 16) / chunk_tiles);
+// `scratch` holds vx_paged_decode_scratch_floats(...) floats (may be null when max_splits is 1).
+extern "C" int vx_paged_decode_attention(const void* q, int q_row_stride, const void* k_pool,
+                                         const void* v_pool, const int* block_table, int max_blocks,
+                                         const int* token_rows, const int* seq_of_token,
+                                         const int* positions, float* scratch, int max_splits, void* out,
+                                         int out_row_stride, float scale, int window, int requests, int H,
+                                         int Hk, int D, int S, int chunk_tiles, cudaStream_t stream) {
+    if (requests <= 0) return VX_OK;
+    if (H <= 0 || Hk <= 0 || H % Hk || H / Hk > 16 || S <= 0 || S % 16 || window < 0) return VX_ERR_SHAPE;
+    if (chunk_tiles <= 0 || max_splits <= 0 || (max_splits > 1 && !scratch)) return VX_ERR_SHAPE;
+    if (Hk > 65535 || requests > 65535) return VX_ERR_LIMIT;
+    if ((q_row_stride & 1) || (((uintptr_t)q) & 3)) return VX_ERR_ALIGN;
+    if (D == 128)
+        return launch_decode<128>((const bf16*)q, q_row_stride, (const bf16*)k_pool, (const bf16*)v_pool,
+                                  block_table, max_blocks, token_rows, seq_of_token, positions, scratch,
+                                  max_splits, (bf16*)out, out_row_stride, scale, window, requests, H, Hk, S,
+                                  chunk_tiles, stream);
+    if (D == 64)
+        return launch_decode<64>((const bf16*)q, q_row_stride, (const bf16*)k_pool, (const bf16*)v_pool,
+                                 block_table, max_blocks, token_rows, seq_of_token, positions, scratch,
+                                 max_splits, (bf16*)out, out_row_stride, scale, window, requests, H, Hk, S,
+                                 chunk_tiles, stream);
+    return VX_ERR_SHAPE;
+}

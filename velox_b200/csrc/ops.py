@@ -60,6 +60,7 @@ def _declare(lib) -> None:
         "vx_qk_norm_rope_kv": [P, I, P, P, F, P, I, P, P, P, P, I, I, I, I, I, I, P],
         "vx_paged_attention_generic": [P, I, P, P, P, I, P, P, P, I, F, I, I, I, I, I, I, I, P],
         "vx_gemm_nt_simt": [P, P, P, P, I, I, I, I, I, I, I, I, P],
+        "vx_paged_decode_attention": [P, I, P, P, P, I, P, P, P, P, I, P, I, F, I, I, I, I, I, I, I, P],
         "vx_sample": [P, I, I, I, P, P, P, P, P],
     }
     for name, args in sigs.items():
@@ -213,6 +214,52 @@ def paged_attention_generic(q: torch.Tensor, q_row_stride: int, k_pool, v_pool, 
         _ptr(q), q_row_stride, _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1],
         _ptr(seq_of_token), _ptr(positions), _ptr(out), num_heads * head_dim, float(scale), int(window), tokens,
         num_heads, num_kv_heads, head_dim, k_pool.shape[2], dtype_code(q.dtype), _stream()), "paged_attention_generic")
+    return out
+
+
+DECODE_CHUNK_TILES = 16  # keys per block of the split decode kernel: 16 tiles of 16
+_WORKSPACE = {}
+
+
+def workspace(device, nfloats: int) -> torch.Tensor:
+    """A float32 scratch buffer of at least `nfloats` on `device`, kept between calls."""
+    key = str(device)
+    buf = _WORKSPACE.get(key)
+    if buf is None or buf.numel() < nfloats:
+        buf = torch.empty(max(nfloats, 1 << 16), dtype=torch.float32, device=device)
+        _WORKSPACE[key] = buf
+    return buf
+
+
+def decode_attention_supported(dtype, head_dim: int, page_size: int, group: int) -> bool:
+    return dtype == torch.bfloat16 and head_dim in (64, 128) and page_size % 16 == 0 and group <= 16
+
+
+def paged_decode_attention(q: torch.Tensor, q_row_stride: int, k_pool, v_pool, block_table: torch.Tensor,
+                           seq_of_token, positions, scale: float, window: int, num_heads: int, num_kv_heads: int,
+                           head_dim: int, requests: int, max_kv: int, token_rows=None,
+                           out: Optional[torch.Tensor] = None, out_rows: Optional[int] = None) -> torch.Tensor:
+    """Attention of one query token per request over its pages (bfloat16), the
+    key range split over blocks of DECODE_CHUNK_TILES * 16 keys.  `max_kv` bounds
+    every request's number of keys (it sizes the grid and the scratch)."""
+    _dev(q, k_pool, v_pool, block_table, seq_of_token, positions, token_rows)
+    _need(q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and v_pool.dtype == torch.bfloat16,
+          "paged_decode_attention: bfloat16 only")
+    _need(block_table.dtype == torch.int32 and block_table.is_contiguous() and block_table.dim() == 2,
+          "paged_decode_attention: int32 block table [requests, blocks]")
+    if out is None:
+        out = torch.empty((out_rows if out_rows is not None else requests, num_heads * head_dim),
+                          dtype=q.dtype, device=q.device)
+    keys = max_kv if window <= 0 else min(max_kv, window + 15)
+    max_splits = max(1, -(-(-(-keys // 16) + (1 if window > 0 else 0)) // DECODE_CHUNK_TILES))
+    scratch = None
+    if max_splits > 1:
+        scratch = workspace(q.device, requests * num_heads * max_splits * (head_dim + 2))
+    _check(library().vx_paged_decode_attention(
+        _ptr(q), q_row_stride, _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1],
+        _ptr(token_rows), _ptr(seq_of_token), _ptr(positions), _ptr(scratch), max_splits, _ptr(out),
+        num_heads * head_dim, float(scale), int(window), requests, num_heads, num_kv_heads, head_dim,
+        k_pool.shape[2], DECODE_CHUNK_TILES, _stream()), "paged_decode_attention")
     return out
 
 

@@ -106,6 +106,11 @@ class PagedAttention(Mixer):
 
     def _attend(self, qkv, ctx, cache, group) -> torch.Tensor:
         H, Hk, D = self.num_heads, self.num_kv_heads, self.head_dim
+        if ctx.decode_only and ops.decode_attention_supported(qkv.dtype, D, cache.k_pool.shape[2], H // Hk):
+            # one token per request: token row i is request i
+            return ops.paged_decode_attention(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
+                                              ctx.seq_of_token, ctx.positions, self.scale, self.window, H, Hk, D,
+                                              ctx.n_seqs, ctx.max_kv)
         return ops.paged_attention_generic(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
                                            ctx.seq_of_token, ctx.positions, self.scale, self.window, H, Hk, D,
                                            qkv.shape[0])
