@@ -369,3 +369,45 @@ extern "C" int vx_paged_decode_attention(const void* q, int q_row_stride, const 
                                  chunk_tiles, stream);
     return VX_ERR_SHAPE;
 }
+
+// ----------------------------------------------------------------------------
+// The variant that allocates nothing (declared and described in no_alloc.h).
+#include "no_alloc.h"
+
+// The scratch itself.  In host code this name is only a handle for the runtime's
+// symbol lookup, never a device address: the address comes from
+// cudaGetSymbolAddress below.
+static __device__ __align__(256) float g_decode_static_scratch[VX_DECODE_STATIC_SCRATCH_FLOATS];
+
+#define VX_STATIC_MAX_DEVICES 64
+static float* g_decode_static_ptr[VX_STATIC_MAX_DEVICES];  // device address of the array, per device
+
+extern "C" long long vx_paged_decode_static_max_floats(void) { return VX_DECODE_STATIC_SCRATCH_FLOATS; }
+
+extern "C" int vx_paged_decode_attention_static(const void* q, int q_row_stride, const void* k_pool,
+                                                const void* v_pool, const int* block_table, int max_blocks,
+                                                const int* token_rows, const int* seq_of_token,
+                                                const int* positions, int max_splits, void* out,
+                                                int out_row_stride, float scale, int window, int requests,
+                                                int H, int Hk, int D, int S, int chunk_tiles,
+                                                cudaStream_t stream) {
+    if (requests <= 0) return VX_OK;
+    if (H <= 0 || D <= 0 || max_splits <= 0) return VX_ERR_SHAPE;
+    if (vx_paged_decode_scratch_floats(requests, H, D, max_splits) > (long long)VX_DECODE_STATIC_SCRATCH_FLOATS)
+        return VX_ERR_LIMIT;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= VX_STATIC_MAX_DEVICES) return VX_ERR_LIMIT;
+    if (!g_decode_static_ptr[dev]) {
+        // set-up, once per device, with that device current
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, g_decode_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        if (!p) return VX_ERR_ALIGN;
+        g_decode_static_ptr[dev] = p;
+    }
+    return vx_paged_decode_attention(q, q_row_stride, k_pool, v_pool, block_table, max_blocks, token_rows,
+                                     seq_of_token, positions, g_decode_static_ptr[dev], max_splits, out,
+                                     out_row_stride, scale, window, requests, H, Hk, D, S, chunk_tiles, stream);
+}
