@@ -175,8 +175,10 @@ def main() -> int:
         assert len(engine.scheduler.running) == batch
         entries = [StepEntry(r.request_id, [r.generated[-1]], [0]) for r in engine.scheduler.running.values()]
 
+        zeros, ones = [0.0] * batch, [1.0] * batch
+
         def device_step():
-            ops.sample(engine.run_step(entries))
+            engine.runner.step_and_sample(entries, zeros, ones, zeros)
         n0 = ops.launch_count()
         dev_ms = timed(device_step, steps)
         launches = (ops.launch_count() - n0) // steps

@@ -96,6 +96,9 @@ def test_gated_act(dtype, act):
     else:
         a = np.maximum(g, 0)
     close(ops().gated_act(x, act), a * u, dtype)
+    # the same values laid out in tiles of 5 gates followed by their 5 ups
+    tiled = torch.stack([x[:, :75].reshape(9, 15, 5), x[:, 75:].reshape(9, 15, 5)], 2).reshape(9, 150).contiguous()
+    assert torch.equal(ops().gated_act(tiled, act, block=5), ops().gated_act(x, act))
 
 
 # ----------------------------------------------------------------------------
@@ -291,10 +294,10 @@ def test_sample_top_p_keeps_only_the_nucleus():
 DECODE_CASES = [
     # (kv lengths, H, Hk, D, S, window)
     ([1, 2, 15, 16, 17], 8, 2, 128, 16, 0),          # first tokens, around a page's edge
-    ([255, 256, 257, 600, 1000], 8, 2, 128, 16, 0),  # around the split boundary (256 keys), several pieces
+    ([255, 256, 257, 600, 1600], 8, 2, 128, 16, 0),   # around a piece's edge (256 keys), several pieces
     ([700, 33, 300], 6, 6, 64, 32, 0),               # no grouping, head size 64, pages of 32
     ([900, 64, 257], 16, 1, 64, 16, 0),              # 16 query heads share one kv head
-    ([700, 40, 290, 5], 4, 2, 128, 16, 270),         # a window that crosses split boundaries
+    ([1300, 40, 590, 5], 4, 2, 128, 16, 540),        # a window that crosses split boundaries
     ([3000], 32, 8, 128, 16, 0),                     # the flagship's head layout, 12 pieces
 ]
 
@@ -348,3 +351,43 @@ def test_decode_attention_refuses_what_it_cannot_do():
     assert not ops().decode_attention_supported(torch.bfloat16, 48, 16, 2)
     assert not ops().decode_attention_supported(torch.bfloat16, 128, 8, 2)
     assert not ops().decode_attention_supported(torch.float32, 128, 16, 2)
+
+
+# ----------------------------------------------------------------------------
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(1, 48, 64), (3, 50, 96), (8, 4096, 4096), (7, 136, 160), (8, 333, 1024), (5, 16, 12288)])
+def test_gemm_skinny(M, N, K, out_dtype):
+    a, w = rnd((M, K), torch.bfloat16, 20), rnd((N, K), torch.bfloat16, 21, 0.05)
+    bias = rnd((N,), torch.float32, 22)
+    want = f64(a) @ f64(w).T
+    close(ops().gemm_skinny(a, w, None, out_dtype), want, torch.bfloat16, what="skinny")
+    close(ops().gemm_skinny(a, w, bias, out_dtype), want + f64(bias), torch.bfloat16, what="skinny + bias")
+    # against the plain product on the same bfloat16 inputs: only the order of additions differs
+    ref = ops().gemm_nt_simt(a, w, None, torch.float32)
+    got = ops().gemm_skinny(a, w, None, torch.float32)
+    assert (got - ref).abs().max() <= 1e-3 * max(1.0, float(ref.abs().max()))
+    # a row alone gives the same bits as in company
+    alone = ops().gemm_skinny(a[:1].contiguous(), w, None, torch.float32)
+    assert torch.equal(alone[0], got[0])
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu_pytorch_tanh"])
+@pytest.mark.parametrize("M,I,K", [(2, 24, 64), (8, 200, 96), (5, 1024, 512)])
+def test_gemm_skinny_gated(M, I, K, act):
+    a = rnd((M, K), torch.bfloat16, 23)
+    wg, wu = rnd((I, K), torch.bfloat16, 24, 0.1), rnd((I, K), torch.bfloat16, 25, 0.1)
+    # tiles of 16 rows: 8 gate rows, then their 8 up rows
+    w = torch.stack([wg.view(I // 8, 8, K), wu.view(I // 8, 8, K)], 1).reshape(2 * I, K).contiguous()
+    g, u = f64(a) @ f64(wg).T, f64(a) @ f64(wu).T
+    av = P.silu(g) if act == "silu" else 0.5 * g * (1 + np.tanh(math.sqrt(2 / math.pi) * (g + 0.044715 * g ** 3)))
+    close(ops().gemm_skinny(a, w, None, torch.bfloat16, gated_activation=act), av * u, torch.bfloat16, what="gated")
+
+
+def test_gemm_skinny_refuses_what_it_cannot_do():
+    from velox_b200.csrc.ops import KernelError
+    a, w = rnd((9, 64), torch.bfloat16, 1), rnd((32, 64), torch.bfloat16, 2)
+    with pytest.raises(KernelError):
+        ops().gemm_skinny(a, w)
+    with pytest.raises(KernelError):
+        ops().gemm_skinny(rnd((4, 40), torch.bfloat16, 1), rnd((32, 40), torch.bfloat16, 2))
+    assert not ops().skinny_supported(4, 40, a, w) and not ops().skinny_supported(9, 64, a, w)

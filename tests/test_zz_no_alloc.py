@@ -44,7 +44,7 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
     fn.restype = I
     lib.vx_paged_decode_static_max_floats.restype = ctypes.c_longlong
     limit = lib.vx_paged_decode_static_max_floats()
-    assert limit == 2 * 1024 * 1024
+    assert limit == 4 * 1024 * 1024
 
     H, Hk, D, S, chunk = 8, 2, 128, 16, ops.DECODE_CHUNK_TILES
     stream = torch.cuda.current_stream().cuda_stream

@@ -1,22 +1,23 @@
 // Paged attention for decoded tokens (one query per request), bfloat16, with the
-// key/value range of a request split over several blocks and a second pass that
-// joins the pieces.
+// key/value range of a request split into pieces of fixed size that are worked on
+// independently and joined by a second, small kernel.
 //
-// grid (split, kv head, request); 4 warps.  A block takes `chunk_tiles` tiles of
-// 16 keys of one kv head of one request and ALL the query heads of that kv head
-// (the group), so every key and value is read from memory once; the group's
-// queries fill the rows of one 16-row tensor-core tile.  Each warp streams its
-// own tiles (tile t goes to warp t mod 4) through a 3-stage cp.async pipeline
-// of its own in shared memory, computes S = Q K^T and O += P V with
-// mma.sync.m16n8k16 (bf16 in, float32 out) and keeps a running maximum, sum and
-// accumulator per query row in float32 (online softmax, base 2).  The four
-// warps' states are merged in shared memory.  A request whose whole range fits
-// one block writes its output at once; otherwise the block writes its
-// unnormalised accumulator and (max, sum) to scratch, and `combine` joins them.
+// The unit of work is a WARP: it takes `piece_tiles` tiles of 16 keys of one kv
+// head of one request and ALL the query heads of that kv head (the group), so
+// every key and value is read from memory once; the group's queries fill the rows
+// of one 16-row tensor-core tile.  The warp streams its tiles through a cp.async
+// pipeline of its own in shared memory (no barrier between warps anywhere in the
+// kernel), computes S = Q K^T and O += P V with mma.sync.m16n8k16 (bf16 in,
+// float32 out) and keeps a running maximum, sum and accumulator per query row in
+// float32 (online softmax, base 2).  A request whose whole range is one piece gets
+// its output written at once; otherwise each warp writes its unnormalised
+// accumulator and (max, sum) to scratch, and the join kernel (one block per
+// request and head) adds the pieces in piece order.
 //
-// Split boundaries depend only on the request's own key range (fixed number of
-// keys per block), never on the batch, so a request's output does not depend on
-// what else is in the step.
+// Piece boundaries depend only on the request's own key range (fixed number of
+// keys per piece), never on the batch, so a request's output does not depend on
+// what else is in the step.  Blocks are four warps = four consecutive pieces;
+// grid (pieces / 4, kv head, request).
 //
 // Sizes: head size 64 or 128; page size a multiple of 16; group size up to 16;
 // any number of heads; an optional window.  Other sizes are refused (the caller
@@ -57,36 +58,65 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 
 // Shared memory of a block: per warp, DEC_STAGES stages of a K tile and a V tile
 // [16 keys][D] bf16, 16-byte chunks of a row XOR-swizzled with the row index so
-// that ldmatrix reads hit distinct banks.  After the main loop the same memory
-// holds the warps' states for the merge.
+// that ldmatrix reads hit distinct banks.
 template <int D>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 paged_decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __restrict__ k_pool,
                               const bf16* __restrict__ v_pool, const int* __restrict__ block_table,
                               int max_blocks, const int* __restrict__ token_rows,
                               const int* __restrict__ seq_of_token, const int* __restrict__ positions,
-                              float* __restrict__ part_o, float* __restrict__ part_ml, int max_splits,
+                              float* __restrict__ part_o, float* __restrict__ part_ml, int max_pieces,
                               bf16* __restrict__ out, int out_row_stride, float scale_log2, int window,
-                              int H, int Hk, int S, int chunk_tiles) {
+                              int H, int Hk, int S, int piece_tiles) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
+    pdl_trigger();
     constexpr int TILE_BYTES = 16 * D * 2;
     constexpr int CHUNKS_PER_ROW = D / 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+    const int piece = blockIdx.x * DEC_WARPS + warp, hk = blockIdx.y, b = blockIdx.z;
     const int G = H / Hk;
+    // The step's description was copied to the device before any kernel of the
+    // step ran, so it may be read before the wait on earlier kernels.
     const int row_tok = token_rows ? token_rows[b] : b;
     const int seq = seq_of_token[row_tok];
     const int kv_len = positions[row_tok] + 1;
     const int start = (window > 0 && kv_len > window) ? kv_len - window : 0;
     const int tile_first = start >> 4;
     const int tile_last = (kv_len + 15) >> 4;  // exclusive
-    const int nsplits = (tile_last - tile_first + chunk_tiles - 1) / chunk_tiles;
-    if (split >= nsplits) return;
-    const int tile_begin = tile_first + split * chunk_tiles;
-    const int tile_end = min(tile_begin + chunk_tiles, tile_last);
+    const int npieces = (tile_last - tile_first + piece_tiles - 1) / piece_tiles;
+    if (piece >= npieces) return;  // (no barrier follows: a warp may leave alone)
+    const int tile_begin = tile_first + piece * piece_tiles;
+    const int count = min(piece_tiles, tile_last - tile_begin);
     const int* bt = block_table + (size_t)seq * max_blocks;
+    // lane j holds the page of the warp's j-th tile
+    int my_page = 0;
+    if (lane < count) my_page = bt[((tile_begin + lane) << 4) / S];
 
     unsigned char* my_smem = smem_raw + (size_t)warp * DEC_STAGES * 2 * TILE_BYTES;
+    pdl_wait();
+
+    auto issue = [&](int j) {
+        const int key0 = (tile_begin + j) << 4;
+        const int page = __shfl_sync(0xffffffffu, my_page, j);
+        const size_t base = (((size_t)page * Hk + hk) * S + (key0 % S)) * D;
+        unsigned char* ks = my_smem + (size_t)(j % DEC_STAGES) * 2 * TILE_BYTES;
+        unsigned char* vs = ks + TILE_BYTES;
+        const unsigned char* kg = reinterpret_cast<const unsigned char*>(k_pool + base);
+        const unsigned char* vg = reinterpret_cast<const unsigned char*>(v_pool + base);
+#pragma unroll
+        for (int i = 0; i < (16 * CHUNKS_PER_ROW) / 32; ++i) {
+            const int c = lane + 32 * i;
+            const int r = c / CHUNKS_PER_ROW, cc = c % CHUNKS_PER_ROW;
+            const int dst = r * (D * 2) + ((cc ^ (r & 7)) << 4);
+            cp_async16(ks + dst, kg + (size_t)c * 16);
+            cp_async16(vs + dst, vg + (size_t)c * 16);
+        }
+    };
+#pragma unroll
+    for (int s = 0; s < DEC_STAGES - 1; ++s) {
+        if (s < count) issue(s);
+        cp_async_commit();
+    }
 
     // queries of the group: rows of the A operand, kept in registers
     unsigned qf[D / 16][4];
@@ -109,39 +139,12 @@ paged_decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, cons
     for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
-    const int first = tile_begin + warp;
-    const int count = first < tile_end ? (tile_end - first + DEC_WARPS - 1) / DEC_WARPS : 0;
-
-    auto issue = [&](int j) {
-        const int key0 = (first + j * DEC_WARPS) << 4;
-        const int page = bt[key0 / S];
-        const size_t base = (((size_t)page * Hk + hk) * S + (key0 % S)) * D;
-        unsigned char* ks = my_smem + (size_t)(j % DEC_STAGES) * 2 * TILE_BYTES;
-        unsigned char* vs = ks + TILE_BYTES;
-        const unsigned char* kg = reinterpret_cast<const unsigned char*>(k_pool + base);
-        const unsigned char* vg = reinterpret_cast<const unsigned char*>(v_pool + base);
-#pragma unroll
-        for (int i = 0; i < (16 * CHUNKS_PER_ROW) / 32; ++i) {
-            const int c = lane + 32 * i;
-            const int r = c / CHUNKS_PER_ROW, cc = c % CHUNKS_PER_ROW;
-            const int dst = r * (D * 2) + ((cc ^ (r & 7)) << 4);
-            cp_async16(ks + dst, kg + (size_t)c * 16);
-            cp_async16(vs + dst, vg + (size_t)c * 16);
-        }
-    };
-
-#pragma unroll
-    for (int s = 0; s < DEC_STAGES - 1; ++s) {
-        if (s < count) issue(s);
-        cp_async_commit();
-    }
-
     for (int i = 0; i < count; ++i) {
         if (i + DEC_STAGES - 1 < count) issue(i + DEC_STAGES - 1);
         cp_async_commit();
         cp_async_wait<DEC_STAGES - 1>();
         __syncwarp();
-        const int key0 = (first + i * DEC_WARPS) << 4;
+        const int key0 = (tile_begin + i) << 4;
         unsigned char* ks = my_smem + (size_t)(i % DEC_STAGES) * 2 * TILE_BYTES;
         unsigned char* vs = ks + TILE_BYTES;
         if (key0 + 16 > kv_len) {
@@ -233,70 +236,52 @@ paged_decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, cons
         l[hrow] += __shfl_xor_sync(0xffffffffu, l[hrow], 1);
         l[hrow] += __shfl_xor_sync(0xffffffffu, l[hrow], 2);
     }
-    __syncthreads();  // every warp is done with its stages: reuse the memory
-    float* om = reinterpret_cast<float*>(smem_raw);                 // [warps][16][D]
-    float* mls = om + DEC_WARPS * 16 * D;                            // [warps][16][2]
+    // thread holds rows lane/4 (+8), columns nt*8 + (lane%4)*2 + {0,1}
 #pragma unroll
     for (int hrow = 0; hrow < 2; ++hrow) {
-        const int r = (lane >> 2) + 8 * hrow;
-        if (r < G) {
-            float* dst = om + ((size_t)warp * 16 + r) * D;
-#pragma unroll
-            for (int nt = 0; nt < D / 8; ++nt) {
-                const int d = nt * 8 + ((lane & 3) << 1);
-                dst[d] = o[nt][2 * hrow];
-                dst[d + 1] = o[nt][2 * hrow + 1];
-            }
-            if ((lane & 3) == 0) {
-                mls[((size_t)warp * 16 + r) * 2] = m[hrow];
-                mls[((size_t)warp * 16 + r) * 2 + 1] = l[hrow];
-            }
-        }
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < G * D; idx += DEC_WARPS * 32) {
-        const int g = idx / D, d = idx % D;
-        float M = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, mls[((size_t)w * 16 + g) * 2]);
-        float L = 0.f, O = 0.f;
-#pragma unroll
-        for (int w = 0; w < DEC_WARPS; ++w) {
-            const float mw = mls[((size_t)w * 16 + g) * 2];
-            const float wgt = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
-            L += wgt * mls[((size_t)w * 16 + g) * 2 + 1];
-            O += wgt * om[((size_t)w * 16 + g) * D + d];
-        }
+        const int g = (lane >> 2) + 8 * hrow;
+        if (g >= G) continue;
         const int h = hk * G + g;
-        if (nsplits == 1) {
-            out[(size_t)row_tok * out_row_stride + (size_t)h * D + d] = __float2bfloat16_rn(O / L);
+        if (npieces == 1) {
+            const float inv = 1.f / l[hrow];
+            bf16* dst = out + (size_t)row_tok * out_row_stride + (size_t)h * D + ((lane & 3) << 1);
+#pragma unroll
+            for (int nt = 0; nt < D / 8; ++nt)
+                *reinterpret_cast<__nv_bfloat162*>(dst + nt * 8) =
+                    __floats2bfloat162_rn(o[nt][2 * hrow] * inv, o[nt][2 * hrow + 1] * inv);
         } else {
-            const size_t p = ((size_t)b * H + h) * max_splits + split;
-            part_o[p * D + d] = O;
-            if (d == 0) { part_ml[p * 2] = M; part_ml[p * 2 + 1] = L; }
+            const size_t p = ((size_t)b * H + h) * max_pieces + piece;
+            float* dst = part_o + p * D + ((lane & 3) << 1);
+#pragma unroll
+            for (int nt = 0; nt < D / 8; ++nt)
+                *reinterpret_cast<float2*>(dst + nt * 8) = make_float2(o[nt][2 * hrow], o[nt][2 * hrow + 1]);
+            if ((lane & 3) == 0) *reinterpret_cast<float2*>(part_ml + p * 2) = make_float2(m[hrow], l[hrow]);
         }
     }
 }
 
-// Joins the pieces of requests that were split: one block per (request, head).
+// Joins the pieces of requests that have several: one block per (request, head),
+// pieces added in piece order.
 template <int D>
-__global__ void paged_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                            int max_splits, const int* __restrict__ token_rows,
-                                            const int* __restrict__ positions, bf16* __restrict__ out,
-                                            int out_row_stride, int window, int H, int chunk_tiles) {
+__global__ void paged_decode_join_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                         int max_pieces, const int* __restrict__ token_rows,
+                                         const int* __restrict__ positions, bf16* __restrict__ out,
+                                         int out_row_stride, int window, int H, int piece_tiles) {
+    pdl_trigger();
     const int b = blockIdx.x, h = blockIdx.y;
     const int row_tok = token_rows ? token_rows[b] : b;
     const int kv_len = positions[row_tok] + 1;
     const int start = (window > 0 && kv_len > window) ? kv_len - window : 0;
     const int ntiles = ((kv_len + 15) >> 4) - (start >> 4);
-    const int nsplits = (ntiles + chunk_tiles - 1) / chunk_tiles;
-    if (nsplits <= 1) return;  // written by the first pass
-    const size_t p0 = ((size_t)b * H + h) * max_splits;
+    const int npieces = (ntiles + piece_tiles - 1) / piece_tiles;
+    if (npieces <= 1) return;  // written by the first pass
+    pdl_wait();
+    const size_t p0 = ((size_t)b * H + h) * max_pieces;
     float M = -INFINITY;
-    for (int s = 0; s < nsplits; ++s) M = fmaxf(M, part_ml[(p0 + s) * 2]);
+    for (int s = 0; s < npieces; ++s) M = fmaxf(M, part_ml[(p0 + s) * 2]);
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float L = 0.f, O = 0.f;
-        for (int s = 0; s < nsplits; ++s) {
+        for (int s = 0; s < npieces; ++s) {
             const float ms = part_ml[(p0 + s) * 2];
             const float wgt = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
             L += wgt * part_ml[(p0 + s) * 2 + 1];
@@ -306,18 +291,19 @@ __global__ void paged_decode_combine_kernel(const float* __restrict__ part_o, co
     }
 }
 
-// Scratch the two passes need, in floats: accumulators [requests, H, max_splits, D]
-// then (max, sum) [requests, H, max_splits, 2].
-extern "C" long long vx_paged_decode_scratch_floats(int requests, int H, int D, int max_splits) {
-    return (long long)requests * H * max_splits * (D + 2);
+// Scratch a launch needs, in floats: accumulators [requests, H, max_pieces, D] then
+// (max, sum) [requests, H, max_pieces, 2].  Every element is written before it is
+// read; nothing needs clearing.
+extern "C" long long vx_paged_decode_scratch_floats(int requests, int H, int D, int max_pieces) {
+    return (long long)requests * H * max_pieces * (D + 2);
 }
 
 template <int D>
 static int launch_decode(const bf16* q, int q_row_stride, const bf16* k_pool, const bf16* v_pool,
                          const int* block_table, int max_blocks, const int* token_rows,
-                         const int* seq_of_token, const int* positions, float* scratch, int max_splits,
+                         const int* seq_of_token, const int* positions, float* scratch, int max_pieces,
                          bf16* out, int out_row_stride, float scale, int window, int requests, int H, int Hk,
-                         int S, int chunk_tiles, cudaStream_t stream) {
+                         int S, int piece_tiles, cudaStream_t stream) {
     const size_t smem = (size_t)DEC_WARPS * DEC_STAGES * 2 * 16 * D * 2;
     static bool configured = false;  // per process and instantiation; the attribute is per device function
     if (!configured) {
@@ -327,16 +313,16 @@ static int launch_decode(const bf16* q, int q_row_stride, const bf16* k_pool, co
         configured = true;
     }
     float* part_o = scratch;
-    float* part_ml = scratch ? scratch + (size_t)requests * H * max_splits * D : nullptr;
-    dim3 grid(max_splits, Hk, requests);
-    paged_decode_attention_kernel<D><<<grid, DEC_WARPS * 32, smem, stream>>>(
-        q, q_row_stride, k_pool, v_pool, block_table, max_blocks, token_rows, seq_of_token, positions, part_o,
-        part_ml, max_splits, out, out_row_stride, scale * LOG2E, window, H, Hk, S, chunk_tiles);
+    float* part_ml = scratch ? scratch + (size_t)requests * H * max_pieces * D : nullptr;
+    dim3 grid((max_pieces + DEC_WARPS - 1) / DEC_WARPS, Hk, requests);
+    VX_LAUNCH_K(VX_K_ATTENTION, (paged_decode_attention_kernel<D>), grid, DEC_WARPS * 32, smem, stream, q, q_row_stride, k_pool,
+              v_pool, block_table, max_blocks, token_rows, seq_of_token, positions, part_o, part_ml, max_pieces,
+              out, out_row_stride, scale * LOG2E, window, H, Hk, S, piece_tiles);
     VX_LAUNCH_CHECK();
-    if (max_splits > 1) {
-        dim3 cgrid(requests, H);
-        paged_decode_combine_kernel<D><<<cgrid, D <= 64 ? 64 : 128, 0, stream>>>(
-            part_o, part_ml, max_splits, token_rows, positions, out, out_row_stride, window, H, chunk_tiles);
+    if (max_pieces > 1) {
+        dim3 jgrid(requests, H);
+        VX_LAUNCH_K(VX_K_JOIN, (paged_decode_join_kernel<D>), jgrid, D <= 64 ? 64 : 128, 0, stream, part_o, part_ml, max_pieces,
+                  token_rows, positions, out, out_row_stride, window, H, piece_tiles);
         VX_LAUNCH_CHECK();
     }
     return VX_OK;
@@ -344,29 +330,30 @@ static int launch_decode(const bf16* q, int q_row_stride, const bf16* k_pool, co
 
 // One query token per request.  `token_rows[i]` is the token row (in q, out,
 // seq_of_token, positions) of request i, or null when request i is row i.
-// `max_splits` bounds the pieces of any request: ceil(ceil(max keys / 16) / chunk_tiles);
-// `scratch` holds vx_paged_decode_scratch_floats(...) floats (may be null when max_splits is 1).
+// `max_pieces` bounds the pieces of any request: ceil(ceil(max keys / 16) / piece_tiles)
+// (one more with a window that does not start on a tile's edge); `scratch` holds
+// vx_paged_decode_scratch_floats(...) floats (may be null when max_pieces is 1).
 extern "C" int vx_paged_decode_attention(const void* q, int q_row_stride, const void* k_pool,
                                          const void* v_pool, const int* block_table, int max_blocks,
                                          const int* token_rows, const int* seq_of_token,
-                                         const int* positions, float* scratch, int max_splits, void* out,
+                                         const int* positions, float* scratch, int max_pieces, void* out,
                                          int out_row_stride, float scale, int window, int requests, int H,
-                                         int Hk, int D, int S, int chunk_tiles, cudaStream_t stream) {
+                                         int Hk, int D, int S, int piece_tiles, cudaStream_t stream) {
     if (requests <= 0) return VX_OK;
     if (H <= 0 || Hk <= 0 || H % Hk || H / Hk > 16 || S <= 0 || S % 16 || window < 0) return VX_ERR_SHAPE;
-    if (chunk_tiles <= 0 || max_splits <= 0 || (max_splits > 1 && !scratch)) return VX_ERR_SHAPE;
+    if (piece_tiles <= 0 || piece_tiles > 32 || max_pieces <= 0 || (max_pieces > 1 && !scratch)) return VX_ERR_SHAPE;
     if (Hk > 65535 || requests > 65535) return VX_ERR_LIMIT;
-    if ((q_row_stride & 1) || (((uintptr_t)q) & 3)) return VX_ERR_ALIGN;
+    if ((q_row_stride & 1) || (((uintptr_t)q) & 3) || (out_row_stride & 1) || (((uintptr_t)out) & 3)) return VX_ERR_ALIGN;
     if (D == 128)
         return launch_decode<128>((const bf16*)q, q_row_stride, (const bf16*)k_pool, (const bf16*)v_pool,
                                   block_table, max_blocks, token_rows, seq_of_token, positions, scratch,
-                                  max_splits, (bf16*)out, out_row_stride, scale, window, requests, H, Hk, S,
-                                  chunk_tiles, stream);
+                                  max_pieces, (bf16*)out, out_row_stride, scale, window, requests, H, Hk, S,
+                                  piece_tiles, stream);
     if (D == 64)
         return launch_decode<64>((const bf16*)q, q_row_stride, (const bf16*)k_pool, (const bf16*)v_pool,
                                  block_table, max_blocks, token_rows, seq_of_token, positions, scratch,
-                                 max_splits, (bf16*)out, out_row_stride, scale, window, requests, H, Hk, S,
-                                 chunk_tiles, stream);
+                                 max_pieces, (bf16*)out, out_row_stride, scale, window, requests, H, Hk, S,
+                                 piece_tiles, stream);
     return VX_ERR_SHAPE;
 }
 

@@ -26,6 +26,8 @@ __global__ void paged_attention_generic_kernel(
     const T* __restrict__ v_pool, const int* __restrict__ block_table, int max_blocks,
     const int* __restrict__ seq_of_token, const int* __restrict__ positions, T* __restrict__ out,
     int out_row_stride, float scale, int window, int H, int Hk, int D, int S) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float q_s[ATT_MAX_D];
     __shared__ float acc_s[ATT_WARPS][ATT_MAX_D];
     __shared__ float m_s[ATT_WARPS], l_s[ATT_WARPS];
@@ -116,12 +118,10 @@ extern "C" int vx_paged_attention_generic(const void* q, int q_row_stride, const
     if (window < 0) return VX_ERR_SHAPE;
     dim3 grid(tokens, H);
     if (dtype == VX_F32)
-        paged_attention_generic_kernel<float><<<grid, ATT_WARPS * 32, 0, stream>>>(
-            (const float*)q, q_row_stride, (const float*)k_pool, (const float*)v_pool, block_table,
+        VX_LAUNCH_K(VX_K_ATTENTION, (paged_attention_generic_kernel<float>), grid, ATT_WARPS * 32, 0, stream, (const float*)q, q_row_stride, (const float*)k_pool, (const float*)v_pool, block_table,
             max_blocks, seq_of_token, positions, (float*)out, out_row_stride, scale, window, H, Hk, D, S);
     else if (dtype == VX_BF16)
-        paged_attention_generic_kernel<bf16><<<grid, ATT_WARPS * 32, 0, stream>>>(
-            (const bf16*)q, q_row_stride, (const bf16*)k_pool, (const bf16*)v_pool, block_table,
+        VX_LAUNCH_K(VX_K_ATTENTION, (paged_attention_generic_kernel<bf16>), grid, ATT_WARPS * 32, 0, stream, (const bf16*)q, q_row_stride, (const bf16*)k_pool, (const bf16*)v_pool, block_table,
             max_blocks, seq_of_token, positions, (bf16*)out, out_row_stride, scale, window, H, Hk, D, S);
     else
         return VX_ERR_DTYPE;

@@ -27,6 +27,73 @@
 
 typedef __nv_bfloat16 bf16;
 
+// Programmatic dependent launch (off unless vx_set_pdl(1)).  With it, kernels of
+// this library are launched so that the next kernel in the stream may become
+// resident while the previous one is still running.  A kernel first calls pdl_trigger() (its dependents may be
+// launched), does whatever needs nothing of earlier kernels (loading weights),
+// and calls pdl_wait() before it reads anything an earlier kernel wrote and
+// before it writes anything at all; pdl_wait() returns when all earlier work in
+// the stream is complete and visible.  Launched without the attribute (or after a
+// kernel of another library) both calls do nothing and the order is the stream's.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+extern "C" int vx_pdl_is_enabled(void);
+extern "C" int vx_pdl_mask(void);
+
+// Kernel classes, for switching programmatic dependent launch on and off per class
+// (vx_set_pdl_mask; bit i = class i).
+#define VX_K_ELEMENTWISE 0
+#define VX_K_ROPE 1
+#define VX_K_ATTENTION 2
+#define VX_K_GEMM 3
+#define VX_K_SAMPLE 4
+#define VX_K_JOIN 5
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t vx_launch_class(int kclass, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                          cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (vx_pdl_is_enabled() && ((vx_pdl_mask() >> kclass) & 1)) ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t vx_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = vx_pdl_is_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+#define VX_LAUNCH_K(kclass, kernel, grid, block, smem, stream, ...)                                       \
+    do {                                                                                                 \
+        cudaError_t e__ = vx_launch_class(kclass, kernel, dim3(grid), dim3(block), smem, stream, __VA_ARGS__); \
+        if (e__ != cudaSuccess) return (int)e__;                                                         \
+    } while (0)
+
+#define VX_LAUNCH(kernel, grid, block, smem, stream, ...)                                          \
+    do {                                                                                           \
+        cudaError_t e__ = vx_launch(kernel, dim3(grid), dim3(block), smem, stream, __VA_ARGS__);   \
+        if (e__ != cudaSuccess) return (int)e__;                                                   \
+    } while (0)
+
 __device__ __forceinline__ float to_f32(float x) { return x; }
 __device__ __forceinline__ float to_f32(bf16 x) { return __bfloat162float(x); }
 

@@ -12,6 +12,8 @@
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ out, int hidden, int vocab) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * hidden;
@@ -29,9 +31,9 @@ extern "C" int vx_embedding(const int* ids, const void* table, float* out, int t
     if (hidden <= 0 || vocab <= 0) return VX_ERR_SHAPE;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (dtype == VX_F32)
-        embedding_kernel<float><<<tokens, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab);
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (embedding_kernel<float>), tokens, threads, 0, stream, ids, (const float*)table, out, hidden, vocab);
     else if (dtype == VX_BF16)
-        embedding_kernel<bf16><<<tokens, threads, 0, stream>>>(ids, (const bf16*)table, out, hidden, vocab);
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (embedding_kernel<bf16>), tokens, threads, 0, stream, ids, (const bf16*)table, out, hidden, vocab);
     else
         return VX_ERR_DTYPE;
     VX_LAUNCH_CHECK();
@@ -47,6 +49,8 @@ __global__ void add_rmsnorm_kernel(const float* __restrict__ residual_in, const 
                                    const int* __restrict__ row_index, float* __restrict__ residual_out,
                                    const float* __restrict__ weight, T* __restrict__ out, int width,
                                    float eps) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float scratch[32];
     const int r = blockIdx.x;
     const int s = row_index ? row_index[r] : r;
@@ -87,11 +91,9 @@ extern "C" int vx_add_rmsnorm(const float* residual_in, const void* delta, const
     if (row_index && residual_out == residual_in) return VX_ERR_SHAPE;
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
     if (dtype == VX_F32)
-        add_rmsnorm_kernel<float><<<rows, threads, 0, stream>>>(
-            residual_in, (const float*)delta, row_index, residual_out, weight, (float*)out, width, eps);
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (add_rmsnorm_kernel<float>), rows, threads, 0, stream, residual_in, (const float*)delta, row_index, residual_out, weight, (float*)out, width, eps);
     else if (dtype == VX_BF16)
-        add_rmsnorm_kernel<bf16><<<rows, threads, 0, stream>>>(
-            residual_in, (const bf16*)delta, row_index, residual_out, weight, (bf16*)out, width, eps);
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (add_rmsnorm_kernel<bf16>), rows, threads, 0, stream, residual_in, (const bf16*)delta, row_index, residual_out, weight, (bf16*)out, width, eps);
     else
         return VX_ERR_DTYPE;
     VX_LAUNCH_CHECK();
@@ -102,6 +104,8 @@ extern "C" int vx_add_rmsnorm(const float* residual_in, const void* delta, const
 template <typename T>
 __global__ void rmsnorm_kernel(const T* __restrict__ x, const float* __restrict__ weight,
                                T* __restrict__ out, int width, float eps) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float scratch[32];
     const T* xin = x + (size_t)blockIdx.x * width;
     T* o = out + (size_t)blockIdx.x * width;
@@ -122,43 +126,47 @@ extern "C" int vx_rmsnorm(const void* x, const float* weight, void* out, int row
     if (width <= 0) return VX_ERR_SHAPE;
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
     if (dtype == VX_F32)
-        rmsnorm_kernel<float><<<rows, threads, 0, stream>>>((const float*)x, weight, (float*)out, width, eps);
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (rmsnorm_kernel<float>), rows, threads, 0, stream, (const float*)x, weight, (float*)out, width, eps);
     else if (dtype == VX_BF16)
-        rmsnorm_kernel<bf16><<<rows, threads, 0, stream>>>((const bf16*)x, weight, (bf16*)out, width, eps);
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (rmsnorm_kernel<bf16>), rows, threads, 0, stream, (const bf16*)x, weight, (bf16*)out, width, eps);
     else
         return VX_ERR_DTYPE;
     VX_LAUNCH_CHECK();
     return VX_OK;
 }
 
-// out[t, i] = act(gate_up[t, i]) * gate_up[t, inner + i]: the gate half of a
-// row is followed by the up half.  Activation and product in float32.
+// out[t, i] = act(gate) * up, activation and product in float32.  Where gate i
+// and up i sit in a row of 2 * inner values: with block == 0 the gate half is
+// followed by the up half; with block > 0 the row is made of tiles of 2 * block
+// values, `block` gates followed by their `block` ups.
 template <typename T>
 __global__ void gated_act_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long total,
-                                 int inner, int act) {
+                                 int inner, int act, int block) {
+    pdl_trigger();
+    pdl_wait();
     for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x) {
         const long long t = idx / inner;
         const int i = (int)(idx - t * inner);
         const T* row = gate_up + t * 2 * inner;
-        const float g = to_f32(row[i]);
-        const float u = to_f32(row[inner + i]);
-        out[idx] = from_f32<T>(activation(g, act) * u);
+        const int gi = block > 0 ? (i / block) * 2 * block + i % block : i;
+        const int ui = block > 0 ? gi + block : inner + i;
+        out[idx] = from_f32<T>(activation(to_f32(row[gi]), act) * to_f32(row[ui]));
     }
 }
 
-extern "C" int vx_gated_act(const void* gate_up, void* out, int rows, int inner, int act, int dtype,
+extern "C" int vx_gated_act(const void* gate_up, void* out, int rows, int inner, int act, int block, int dtype,
                             cudaStream_t stream) {
     if (rows <= 0) return VX_OK;
-    if (inner <= 0 || act < 0 || act > 3) return VX_ERR_SHAPE;
+    if (inner <= 0 || act < 0 || act > 3 || block < 0 || (block > 0 && inner % block)) return VX_ERR_SHAPE;
     const long long total = (long long)rows * inner;
     const int threads = 256;
     long long blocks = (total + threads - 1) / threads;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (dtype == VX_F32)
-        gated_act_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, total, inner, act);
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (gated_act_kernel<float>), (int)blocks, threads, 0, stream, (const float*)gate_up, (float*)out, total, inner, act, block);
     else if (dtype == VX_BF16)
-        gated_act_kernel<bf16><<<(int)blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, total, inner, act);
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (gated_act_kernel<bf16>), (int)blocks, threads, 0, stream, (const bf16*)gate_up, (bf16*)out, total, inner, act, block);
     else
         return VX_ERR_DTYPE;
     VX_LAUNCH_CHECK();

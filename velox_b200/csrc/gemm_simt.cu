@@ -15,6 +15,8 @@ template <typename TA, typename TC>
 __global__ void __launch_bounds__(256)
 gemm_nt_simt_kernel(const TA* __restrict__ A, const TA* __restrict__ W, const float* __restrict__ bias,
                     TC* __restrict__ C, int M, int N, int K, int lda, int ldw, int ldc) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float As[GS_BK][GS_BM + 1];
     __shared__ float Ws[GS_BK][GS_BN + 1];
     const int tid = threadIdx.x;
@@ -76,14 +78,11 @@ extern "C" int vx_gemm_nt_simt(const void* A, const void* W, const float* bias, 
     dim3 grid((N + GS_BN - 1) / GS_BN, (M + GS_BM - 1) / GS_BM);
     if (grid.y > 65535) return VX_ERR_LIMIT;
     if (in_dtype == VX_F32 && out_dtype == VX_F32)
-        gemm_nt_simt_kernel<float, float><<<grid, 256, 0, stream>>>(
-            (const float*)A, (const float*)W, bias, (float*)C, M, N, K, lda, ldw, ldc);
+        VX_LAUNCH_K(VX_K_GEMM, (gemm_nt_simt_kernel<float, float>), grid, 256, 0, stream, (const float*)A, (const float*)W, bias, (float*)C, M, N, K, lda, ldw, ldc);
     else if (in_dtype == VX_BF16 && out_dtype == VX_BF16)
-        gemm_nt_simt_kernel<bf16, bf16><<<grid, 256, 0, stream>>>(
-            (const bf16*)A, (const bf16*)W, bias, (bf16*)C, M, N, K, lda, ldw, ldc);
+        VX_LAUNCH_K(VX_K_GEMM, (gemm_nt_simt_kernel<bf16, bf16>), grid, 256, 0, stream, (const bf16*)A, (const bf16*)W, bias, (bf16*)C, M, N, K, lda, ldw, ldc);
     else if (in_dtype == VX_BF16 && out_dtype == VX_F32)
-        gemm_nt_simt_kernel<bf16, float><<<grid, 256, 0, stream>>>(
-            (const bf16*)A, (const bf16*)W, bias, (float*)C, M, N, K, lda, ldw, ldc);
+        VX_LAUNCH_K(VX_K_GEMM, (gemm_nt_simt_kernel<bf16, float>), grid, 256, 0, stream, (const bf16*)A, (const bf16*)W, bias, (float*)C, M, N, K, lda, ldw, ldc);
     else
         return VX_ERR_DTYPE;
     VX_LAUNCH_CHECK();

@@ -10,7 +10,7 @@
 // vx_paged_decode_attention the scratch buffer it asks for by allocating one at
 // call time.  For them the scratch lives inside the library, in a file-scope
 // device array of fixed size that every GPU loading the library holds until the
-// process exits (VX_DECODE_STATIC_SCRATCH_FLOATS floats = 8 MiB).
+// process exits (VX_DECODE_STATIC_SCRATCH_FLOATS floats = 16 MiB).
 //
 // Contract:
 //   * Same arguments and same results as vx_paged_decode_attention, minus the
@@ -30,7 +30,7 @@
 #pragma once
 #include <cuda_runtime.h>
 
-#define VX_DECODE_STATIC_SCRATCH_FLOATS (2 * 1024 * 1024)
+#define VX_DECODE_STATIC_SCRATCH_FLOATS (4 * 1024 * 1024)
 
 #ifdef __cplusplus
 extern "C" {

@@ -9,6 +9,7 @@ of device memory.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_void_p
 from typing import Optional
 
@@ -43,7 +44,17 @@ def library():
         except OSError as e:
             raise KernelError("the kernel library %s could not be loaded: %s" % (path, e))
         _declare(_LIB)
+        if os.environ.get("VELOX_B200_PDL", "0") == "1":
+            _LIB.vx_set_pdl(1)
+        if os.environ.get("VELOX_B200_PDL_MASK"):
+            _LIB.vx_set_pdl_mask(int(os.environ["VELOX_B200_PDL_MASK"], 0))
     return _LIB
+
+
+def set_pdl(enabled: bool) -> None:
+    """Programmatic dependent launch on or off for kernels launched from now on
+    (off by default; VELOX_B200_PDL=1 in the environment starts with it on)."""
+    library().vx_set_pdl(1 if enabled else 0)
 
 
 def is_loaded() -> bool:
@@ -56,13 +67,18 @@ def _declare(lib) -> None:
         "vx_embedding": [P, P, P, I, I, I, I, P],
         "vx_add_rmsnorm": [P, P, P, P, P, P, I, I, F, I, P],
         "vx_rmsnorm": [P, P, P, I, I, F, I, P],
-        "vx_gated_act": [P, P, I, I, I, I, P],
+        "vx_gated_act": [P, P, I, I, I, I, I, P],
         "vx_qk_norm_rope_kv": [P, I, P, P, F, P, I, P, P, P, P, I, I, I, I, I, I, P],
         "vx_paged_attention_generic": [P, I, P, P, P, I, P, P, P, I, F, I, I, I, I, I, I, I, P],
         "vx_gemm_nt_simt": [P, P, P, P, I, I, I, I, I, I, I, I, P],
+        "vx_gemm_skinny": [P, P, P, P, I, I, I, I, I, I, I, I, I, P],
         "vx_paged_decode_attention": [P, I, P, P, P, I, P, P, P, P, I, P, I, F, I, I, I, I, I, I, I, P],
         "vx_sample": [P, I, I, I, P, P, P, P, P],
     }
+    lib.vx_set_pdl_mask.argtypes = [I]
+    lib.vx_set_pdl_mask.restype = None
+    lib.vx_set_pdl.argtypes = [I]
+    lib.vx_set_pdl.restype = None
     for name, args in sigs.items():
         fn = getattr(lib, name)
         fn.argtypes = args
@@ -75,6 +91,12 @@ _LAUNCHES = 0
 def launch_count() -> int:
     """Calls of this library's kernels so far (library matrix products are not counted)."""
     return _LAUNCHES
+
+
+def add_launches(n: int) -> None:
+    """Kernels launched by replaying a captured graph (counted at capture)."""
+    global _LAUNCHES
+    _LAUNCHES += n
 
 
 def _check(code: int, what: str) -> None:
@@ -166,14 +188,15 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     return out
 
 
-def gated_act(gate_up: torch.Tensor, activation: str) -> torch.Tensor:
-    """act(gate) * up for rows [gate | up]."""
+def gated_act(gate_up: torch.Tensor, activation: str, block: int = 0) -> torch.Tensor:
+    """act(gate) * up.  block == 0: rows are [all gates | all ups]; block > 0: rows
+    are tiles of `block` gates followed by their `block` ups."""
     _dev(gate_up)
     _need(gate_up.is_contiguous() and gate_up.shape[-1] % 2 == 0, "gated_act: contiguous rows of even width")
     _need(activation in ACTIVATIONS, "gated_act: activation %r is not one of %s" % (activation, sorted(ACTIVATIONS)))
     rows, inner = gate_up.shape[0], gate_up.shape[-1] // 2
     out = torch.empty((rows, inner), dtype=gate_up.dtype, device=gate_up.device)
-    _check(library().vx_gated_act(_ptr(gate_up), _ptr(out), rows, inner, ACTIVATIONS[activation],
+    _check(library().vx_gated_act(_ptr(gate_up), _ptr(out), rows, inner, ACTIVATIONS[activation], int(block),
                                   dtype_code(gate_up.dtype), _stream()), "gated_act")
     return out
 
@@ -217,12 +240,15 @@ def paged_attention_generic(q: torch.Tensor, q_row_stride: int, k_pool, v_pool, 
     return out
 
 
-DECODE_CHUNK_TILES = 16  # keys per block of the split decode kernel: 16 tiles of 16
+DECODE_CHUNK_TILES = 16  # keys per piece of the split decode kernel: 16 tiles of 16
 _WORKSPACE = {}
 
 
 def workspace(device, nfloats: int) -> torch.Tensor:
-    """A float32 scratch buffer of at least `nfloats` on `device`, kept between calls."""
+    """A float32 scratch buffer of at least `nfloats` on `device`, kept between calls.
+    While a CUDA graph is being captured the buffer is the graph's own."""
+    if torch.cuda.is_current_stream_capturing():
+        return torch.empty(max(nfloats, 1), dtype=torch.float32, device=device)
     key = str(device)
     buf = _WORKSPACE.get(key)
     if buf is None or buf.numel() < nfloats:
@@ -279,11 +305,42 @@ def gemm_nt_simt(a: torch.Tensor, w: torch.Tensor, bias=None, out_dtype: Optiona
     return out
 
 
+SKINNY_MAX_ROWS = 8
+
+
+def skinny_supported(m: int, k: int, a: torch.Tensor, w: torch.Tensor) -> bool:
+    return (0 < m <= SKINNY_MAX_ROWS and k % 32 == 0 and a.stride(1) == 1 and w.stride(1) == 1
+            and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias=None, out_dtype: Optional[torch.dtype] = None,
+                gated_activation: Optional[str] = None) -> torch.Tensor:
+    """a [M<=8, K] times w [N,K] transposed, W streamed once (bfloat16).  With
+    `gated_activation`, w's rows come in tiles of 8 gate rows followed by their 8 up
+    rows and the result is act(gate) * up, [M, N/2]."""
+    _dev(a, w, bias)
+    _need(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.dim() == 2 and w.dim() == 2
+          and a.shape[1] == w.shape[1], "gemm_skinny: bfloat16 a [M,K], w [N,K]")
+    out_dtype = out_dtype or torch.bfloat16
+    m, k = a.shape
+    n = w.shape[0]
+    cols = n // 2 if gated_activation else n
+    if gated_activation is not None:
+        _need(gated_activation in ACTIVATIONS, "gemm_skinny: unknown activation %r" % gated_activation)
+    out = torch.empty((m, cols), dtype=out_dtype, device=a.device)
+    _check(library().vx_gemm_skinny(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), m, n, k, a.stride(0), w.stride(0), cols,
+                                    1 if gated_activation else 0, ACTIVATIONS.get(gated_activation, 0),
+                                    dtype_code(out_dtype), _stream()), "gemm_skinny")
+    return out
+
+
 def gemm_bf16(a: torch.Tensor, w: torch.Tensor, bias=None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """a [M,K] times w [N,K] transposed on the tensor cores, float32 accumulation."""
     _dev(a, w, bias)
     _need(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "gemm_bf16: bfloat16 operands")
     out_dtype = out_dtype or torch.bfloat16
+    if skinny_supported(a.shape[0], a.shape[1], a, w):
+        return gemm_skinny(a, w, bias, out_dtype)
     # library product (cuBLAS through torch); reductions stay in float32
     torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
     if out_dtype == torch.float32:

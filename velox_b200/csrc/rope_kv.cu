@@ -27,6 +27,8 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, int row_stride,
                                        const int* __restrict__ positions,
                                        const int* __restrict__ slot_mapping, T* __restrict__ k_pool,
                                        T* __restrict__ v_pool, int H, int Hk, int D, int S) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
@@ -93,12 +95,10 @@ extern "C" int vx_qk_norm_rope_kv(void* qkv, int row_stride, const float* q_weig
     dim3 grid(tokens, (H + 2 * Hk + ROPE_WARPS - 1) / ROPE_WARPS);
     const size_t smem = (size_t)ROPE_WARPS * D * sizeof(float);
     if (dtype == VX_F32)
-        qk_norm_rope_kv_kernel<float><<<grid, ROPE_WARPS * 32, smem, stream>>>(
-            (float*)qkv, row_stride, q_weight, k_weight, eps, inv_freq, rot_dim, positions, slot_mapping,
+        VX_LAUNCH_K(VX_K_ROPE, (qk_norm_rope_kv_kernel<float>), grid, ROPE_WARPS * 32, smem, stream, (float*)qkv, row_stride, q_weight, k_weight, eps, inv_freq, rot_dim, positions, slot_mapping,
             (float*)k_pool, (float*)v_pool, H, Hk, D, S);
     else if (dtype == VX_BF16)
-        qk_norm_rope_kv_kernel<bf16><<<grid, ROPE_WARPS * 32, smem, stream>>>(
-            (bf16*)qkv, row_stride, q_weight, k_weight, eps, inv_freq, rot_dim, positions, slot_mapping,
+        VX_LAUNCH_K(VX_K_ROPE, (qk_norm_rope_kv_kernel<bf16>), grid, ROPE_WARPS * 32, smem, stream, (bf16*)qkv, row_stride, q_weight, k_weight, eps, inv_freq, rot_dim, positions, slot_mapping,
             (bf16*)k_pool, (bf16*)v_pool, H, Hk, D, S);
     else
         return VX_ERR_DTYPE;

@@ -54,6 +54,8 @@ __device__ __forceinline__ int block_min_int(int v, int* si) {
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __restrict__ temperature,
               const float* __restrict__ top_p, const float* __restrict__ uniform, int* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float sv[32];
     __shared__ int si[32];
     __shared__ float scan[SAMPLE_THREADS];
@@ -148,7 +150,7 @@ extern "C" int vx_sample(const float* logits, int ld, int rows, int vocab, const
     if (rows <= 0) return VX_OK;
     if (vocab <= 0 || ld < vocab) return VX_ERR_SHAPE;
     if (temperature && !uniform) return VX_ERR_SHAPE;
-    sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, vocab, temperature, top_p, uniform, out);
+    VX_LAUNCH_K(VX_K_SAMPLE, (sample_kernel), rows, SAMPLE_THREADS, 0, stream, logits, ld, vocab, temperature, top_p, uniform, out);
     VX_LAUNCH_CHECK();
     return VX_OK;
 }

@@ -25,6 +25,7 @@ from ..config.registry import load_config, resolve_architecture
 from ..models.decoder import DecoderModel
 from ..parts.base import PagedKV, Runtime
 from ..sampling.params import SamplingParams
+from ..sampling.rng import uniform
 from ..weights.loader import load_weights
 from ..weights.random_init import bind_random_weights
 from .batch import StepEntry
@@ -94,11 +95,10 @@ class Engine:
         self.cache = CacheManager(specs, self.model.cache_sources(), S, num_pages,
                                   cfg.max_running_requests, max_blocks, self.runtime.dtype, self.device,
                                   poison=poison_cache)
-        self.runner = ModelRunner(self.model, self.cache, self.device, self.plan.vocab_size)
+        self.runner = ModelRunner(self.model, self.cache, self.device, self.plan.vocab_size,
+                                  cuda_graphs=cfg.cuda_graphs)
         self.scheduler = Scheduler(self.cache, cfg.max_running_requests, cfg.max_batch_tokens, cfg.chunk_size,
                                    self.max_model_len)
-        from ..sampling.sampler import Sampler
-        self.sampler = Sampler(self.device)
 
     def _pool_pages(self, specs, max_blocks: int) -> int:
         cfg = self.config
@@ -134,13 +134,14 @@ class Engine:
         entries, _ended = self.scheduler.plan()
         if not entries:
             return []
-        logits = self.runner.step(entries)
-        sampled: List[int] = []
-        if logits is not None:
-            reqs = [self.scheduler.running[e.request_id] for e in entries if e.want]
-            seeds = [r.params.seed if r.params.seed is not None
-                     else (self.config.seed * 1000003 + r.request_id) for r in reqs]
-            sampled = self.sampler.sample(logits, [r.params for r in reqs], seeds, [len(r.generated) for r in reqs])
+        reqs = [self.scheduler.running[e.request_id] for e in entries if e.want]
+        temps = [0.0 if r.params.greedy else r.params.temperature for r in reqs]
+        tops = [r.params.top_p if r.params.nucleus else 1.0 for r in reqs]
+        us = [0.0 if r.params.greedy else uniform(
+            r.params.seed if r.params.seed is not None else self.config.seed * 1000003 + r.request_id,
+            0, len(r.generated)) for r in reqs]
+        _logits, ids = self.runner.step_and_sample(entries, temps, tops, us)
+        sampled: List[int] = ids.tolist() if ids is not None else []
         return self.scheduler.update(entries, sampled)
 
     def run_step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:

@@ -1,0 +1,169 @@
+"""Decode steps as CUDA graphs.
+
+A step in which every request brings exactly one token has the same shape of
+work every time, so its ~400 kernel launches are captured once per (batch size,
+key-range bucket) and replayed: the host fills one pinned buffer with the step's
+description (token ids, positions, block tables, slot mapping, sampling
+parameters), copies it into the graph's fixed device buffer, and launches the
+graph; embedding, all layers, the head and the sampling kernel run from there.
+
+Padding: a batch is padded up to its bucket with rows that read page 0 at
+position 0 and write nothing (slot -1); their tokens are dropped.  Models with
+per-request state are never padded (a padded row would touch a real slot), and
+models with a part that is not marked `cuda_graph_safe` (it reads host-side
+fields of the step) do not use graphs at all.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..csrc import ops
+from .batch import GroupContext, StepContext, StepEntry
+
+SPLIT_KEYS = ops.DECODE_CHUNK_TILES * 16
+
+
+def batch_bucket(n: int, exact: bool, cap: int) -> int:
+    if exact or n <= 8:
+        return n
+    return min(cap, -(-n // 8) * 8) if cap >= n else n
+
+
+def keys_bucket(max_kv: int) -> int:
+    """Key-range bucket: the next power of two of the number of 256-key pieces."""
+    pieces = max(1, -(-max_kv // SPLIT_KEYS))
+    b = 1
+    while b < pieces:
+        b *= 2
+    return b * SPLIT_KEYS
+
+
+class _Graph:
+    def __init__(self, runner, bucket: int, max_kv: int):
+        cache, device = runner.cache, runner.device
+        self.bucket, self.max_kv = bucket, max_kv
+        MB, G = cache.max_blocks, len(cache.groups)
+        B = bucket
+        names = ["token_ids", "positions", "seq_of_token", "cu_seqlens", "kv_offsets", "state_slots", "wanted_rows"]
+        sizes = [B, B, B, B + 1, B, B, B]
+        for _ in range(G):
+            sizes += [B * MB, B]
+        sizes += [B, B, B]  # temperature, top_p, uniform (float32 bit patterns)
+        self.starts, cur = [], 0
+        for s in sizes:
+            self.starts.append(cur)
+            cur += (s + 3) // 4 * 4
+        self.sizes = sizes
+        self.host = torch.zeros(cur, dtype=torch.int32, pin_memory=True)
+        self.hv = self.host.numpy()
+        self.dev = torch.zeros(cur, dtype=torch.int32, device=device)
+        v = [self.dev[st:st + s] for st, s in zip(self.starts, sizes)]
+        hvv = [self.hv[st:st + s] for st, s in zip(self.starts, sizes)]
+        self.h = dict(zip(names, hvv[:7]))
+        self.h_groups = [(hvv[7 + 2 * g].reshape(B, MB), hvv[8 + 2 * g]) for g in range(G)]
+        self.h_temp, self.h_top_p, self.h_uniform = (x.view(np.float32) for x in hvv[7 + 2 * G:])
+        groups = [GroupContext(v[7 + 2 * g].view(B, MB), v[8 + 2 * g]) for g in range(G)]
+        f = [x.view(torch.float32) for x in v[7 + 2 * G:]]
+        self.d_temp, self.d_top_p, self.d_uniform = f
+        self.ctx = StepContext(n_tokens=B, n_seqs=B, groups=groups, new_lens=[1] * B, offsets=[0] * B,
+                               slots=[0] * B, max_new=1, max_kv=max_kv, **dict(zip(names, v[:7])))
+        # constant sections
+        self.h["seq_of_token"][:] = np.arange(B)
+        self.h["cu_seqlens"][:] = np.arange(B + 1)
+        self.h["wanted_rows"][:] = np.arange(B)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits = self.ids = None
+        self.launches = 0
+        self.copied: Optional[torch.cuda.Event] = None  # the last copy out of the pinned buffer
+
+    def fill(self, entries: Sequence[StepEntry], cache, sampling) -> None:
+        if self.copied is not None:
+            self.copied.synchronize()  # the pinned buffer is free once its last copy has run
+        n, B, S = len(entries), self.bucket, cache.page_size
+        h = self.h
+        h["token_ids"][n:] = 0
+        h["positions"][n:] = 0
+        h["kv_offsets"][n:] = 0
+        h["state_slots"][n:] = 0
+        for bt, sm in self.h_groups:
+            sm[n:] = -1
+            bt[n:, :] = 0
+        for i, e in enumerate(entries):
+            rc = cache.requests[e.request_id]
+            pos = rc.length
+            h["token_ids"][i] = e.tokens[0]
+            h["positions"][i] = pos
+            h["kv_offsets"][i] = pos
+            h["state_slots"][i] = rc.slot
+            for (bt, sm), table in zip(self.h_groups, rc.tables):
+                k = len(table)
+                bt[i, :k] = table
+                sm[i] = table[pos // S] * S + pos % S
+        if sampling is None:
+            self.h_temp[:] = 0.0
+        else:
+            temps, tops, us = sampling
+            self.h_temp[:n], self.h_top_p[:n], self.h_uniform[:n] = temps, tops, us
+            self.h_temp[n:] = 0.0
+        self.dev.copy_(self.host, non_blocking=True)
+        if self.copied is None:
+            self.copied = torch.cuda.Event()
+        self.copied.record()
+
+    def run_model(self, runner) -> None:
+        residual, delta = runner.model.forward_hidden(self.ctx, runner.cache)
+        self.logits = runner.model.logits(residual, delta, self.ctx.wanted_rows)
+        self.ids = ops.sample(self.logits, self.d_temp, self.d_top_p, self.d_uniform)
+
+
+class DecodeGraphs:
+    def __init__(self, runner):
+        self.runner = runner
+        self.graphs: Dict[Tuple[int, int], _Graph] = {}
+        self.pool = None
+        cache = runner.cache
+        self.has_state = bool(cache._state_layers)
+        self.usable = all(getattr(p, "cuda_graph_safe", False) for p in runner.model.parts())
+        self.cap = cache.slots.num_slots
+
+    def eligible(self, entries: Sequence[StepEntry]) -> bool:
+        return self.usable and len(entries) > 0 and all(len(e.tokens) == 1 for e in entries)
+
+    def step(self, entries: Sequence[StepEntry], sampling=None):
+        """Runs a decode-only step.  Returns (logits [bucket, vocab], ids [bucket]):
+        the first len(entries) rows are the entries'."""
+        cache = self.runner.cache
+        n = len(entries)
+        max_kv = max(cache.requests[e.request_id].length for e in entries) + 1
+        key = (batch_bucket(n, self.has_state, self.cap), keys_bucket(max_kv))
+        g = self.graphs.get(key)
+        if g is None:
+            g = self.graphs[key] = _Graph(self.runner, *key)
+        g.fill(entries, cache, sampling)
+        if g.graph is None:
+            self._capture(g)
+        g.graph.replay()
+        ops.add_launches(g.launches)
+        return g.logits, g.ids
+
+    def _capture(self, g: _Graph) -> None:
+        # once eagerly (first-use set-up of kernels and libraries happens outside the capture) ...
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            g.run_model(self.runner)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        # ... then recorded; the keys and values of this step are simply written twice
+        graph = torch.cuda.CUDAGraph()
+        n0 = ops.launch_count()
+        with torch.cuda.graph(graph, pool=self.pool):
+            g.run_model(self.runner)
+        g.launches = ops.launch_count() - n0
+        if self.pool is None:
+            self.pool = graph.pool()
+        g.graph = graph

@@ -51,7 +51,7 @@ def main(argv: Optional[List[str]] = None) -> int:
 
     pool_tokens = -(-args.max_tokens // 64) * 64
     cfg = EngineConfig(dtype=args.dtype, page_size=args.page_size, max_cache_tokens=pool_tokens,
-                       max_running_requests=args.max_requests, max_model_len=pool_tokens, cuda_graphs=False)
+                       max_running_requests=args.max_requests, max_model_len=pool_tokens)
     engine = Engine(args.model, cfg, poison_cache=args.poison_cache)
     runner, cache = engine.runner, engine.cache
     sys.stderr.write("[velox_b200] trace_run: ready (%s, %d pages of %d tokens per group)\n"

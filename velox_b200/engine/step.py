@@ -16,15 +16,20 @@ from typing import List, Optional, Sequence
 import torch
 
 from ..cache.manager import CacheManager, OutOfPages
+from ..csrc import ops
 from .batch import StepContext, StepEntry, build_step_context
 
 
 class ModelRunner:
     """Owns a model and its cache on one device and steps them."""
 
-    def __init__(self, model, cache: CacheManager, device, vocab_size: int):
+    def __init__(self, model, cache: CacheManager, device, vocab_size: int, cuda_graphs: bool = False):
         self.model, self.cache, self.device, self.vocab_size = model, cache, torch.device(device), int(vocab_size)
         self.steps = 0
+        self.graphs = None
+        if cuda_graphs:
+            from .graphs import DecodeGraphs
+            self.graphs = DecodeGraphs(self)
 
     def validate(self, entries: Sequence[StepEntry]) -> None:
         seen = set()
@@ -42,6 +47,16 @@ class ModelRunner:
         in the order of the entries and of their `want`, or None if nothing is
         wanted.  Raises `OutOfPages` (and changes nothing) if the cache cannot
         hold the new positions."""
+        logits, _ = self._step(entries, None, False)
+        return logits
+
+    def step_and_sample(self, entries: Sequence[StepEntry], temperature, top_p, uniform):
+        """Runs one batch and samples a token at every wanted place (per-row
+        float lists).  Returns (logits [wanted, vocab], int32 ids [wanted]) on
+        the device, or (None, None)."""
+        return self._step(entries, (temperature, top_p, uniform), True)
+
+    def _step(self, entries, sampling, sample: bool):
         self.validate(entries)
         taken: List[StepEntry] = []
         for e in entries:
@@ -51,12 +66,32 @@ class ModelRunner:
                 raise OutOfPages("no pages left for request %r (%d new tokens); free pages per group: %s"
                                  % (e.request_id, len(e.tokens), self.cache.free_pages()))
             taken.append(e)
-        ctx = build_step_context(entries, self.cache, self.device, self.vocab_size)
-        logits = self.run(ctx)
+        ids = None
+        if self.graphs is not None and self.graphs.eligible(entries):
+            for e in entries:
+                if not 0 <= int(e.tokens[0]) < self.vocab_size:
+                    raise ValueError("request %r: token id outside [0, %d)" % (e.request_id, self.vocab_size))
+                if any(w != 0 for w in e.want):
+                    raise ValueError("request %r: wanted place is not among its 1 tokens" % (e.request_id,))
+            all_logits, all_ids = self.graphs.step(entries, sampling if sample else None)
+            rows = [i for i, e in enumerate(entries) for _ in e.want]
+            if not rows:
+                logits = None
+            elif rows == list(range(len(entries))):
+                logits, ids = all_logits[:len(rows)], all_ids[:len(rows)]
+            else:
+                idx = torch.tensor(rows, dtype=torch.long, device=self.device)
+                logits, ids = all_logits[idx], all_ids[idx]
+        else:
+            ctx = build_step_context(entries, self.cache, self.device, self.vocab_size)
+            logits = self.run(ctx)
+            if sample and logits is not None:
+                t = torch.tensor([sampling[0], sampling[1], sampling[2]], dtype=torch.float32).to(self.device, non_blocking=True)
+                ids = ops.sample(logits, t[0], t[1], t[2]) if any(x > 0 for x in sampling[0]) else ops.sample(logits)
         for e in entries:
             self.cache.commit(e.request_id, len(e.tokens))
         self.steps += 1
-        return logits
+        return logits, (ids if sample else None)
 
     def run(self, ctx: StepContext) -> Optional[torch.Tensor]:
         residual, delta = self.model.forward_hidden(ctx, self.cache)

@@ -28,6 +28,8 @@ from .registry import build_part
 
 
 class PagedAttention(Mixer):
+    cuda_graph_safe = True  # reads nothing of a step but device tensors and sizes fixed per graph
+
     def __init__(self, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  bias: bool = False, qk_norm: bool = True, eps: float = 1e-6, window: int = 0,
                  position: Optional[PartSpec] = None, scale: Optional[float] = None):

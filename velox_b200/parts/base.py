@@ -63,6 +63,11 @@ class FixedState:
 
 
 class Part:
+    # True if `forward` reads nothing of a step but device tensors (and sizes that
+    # are fixed for a given batch size): only then may a step be captured in a
+    # CUDA graph.  Parts that look at the step's host-side lists leave it False.
+    cuda_graph_safe = False
+
     def __init__(self, prefix: str = ""):
         self.prefix = prefix
 

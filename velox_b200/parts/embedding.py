@@ -18,6 +18,8 @@ from .linear import matmul
 
 
 class TokenEmbedding(Part):
+    cuda_graph_safe = True  # reads nothing of a step but device tensors and sizes fixed per graph
+
     def __init__(self, prefix: str, vocab_size: int, hidden_size: int):
         super().__init__(prefix)
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
@@ -35,6 +37,8 @@ class TokenEmbedding(Part):
 
 
 class OutputHead(Part):
+    cuda_graph_safe = True  # reads nothing of a step but device tensors and sizes fixed per graph
+
     def __init__(self, prefix: str, vocab_size: int, hidden_size: int, tied: bool = False):
         super().__init__(prefix)
         self.vocab_size, self.hidden_size, self.tied = int(vocab_size), int(hidden_size), bool(tied)

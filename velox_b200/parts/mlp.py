@@ -1,7 +1,11 @@
 """The gated feed-forward of Qwen3: down(act(gate(x)) * up(x)), never biased
-(src/paged/qwen3.rs:313-340).  Gate and up are one matrix here ([Wgate; Wup],
-the gate rows first), which the reference keeps apart (:334-336); activation
-and product are formed in float32.
+(src/paged/qwen3.rs:313-340).  Gate and up are one matrix here, which the
+reference keeps apart (:334-336): its rows come in tiles of 16, 8 gate rows
+followed by the 8 up rows of the same features, so that a matrix-product kernel
+that owns a tile holds gate and up of a feature together and can apply
+act(gate) * up before anything is written (if the intermediate size is no
+multiple of 8, all gate rows are followed by all up rows and the product is taken
+by a kernel of its own).  Activation and product are formed in float32.
 """
 from __future__ import annotations
 
@@ -14,7 +18,12 @@ from .base import FeedForward, Runtime, TensorSpec
 from .linear import Linear
 
 
+GATE_TILE = 8
+
+
 class GatedMLP(FeedForward):
+    cuda_graph_safe = True  # reads nothing of a step but device tensors and sizes fixed per graph
+
     def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, activation: str = "silu"):
         super().__init__(prefix)
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
@@ -33,8 +42,21 @@ class GatedMLP(FeedForward):
     def bind(self, tensors: Dict[str, torch.Tensor], runtime: Runtime) -> None:
         super().bind(tensors, runtime)
         p = self.prefix
-        self.gate_up = Linear(torch.cat([tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]], 0).contiguous())
+        gate, up = tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]
+        i, e = self.intermediate_size, self.hidden_size
+        if i % GATE_TILE == 0:
+            self.tile = GATE_TILE
+            w = torch.stack([gate.view(i // GATE_TILE, GATE_TILE, e), up.view(i // GATE_TILE, GATE_TILE, e)], 1)
+            self.gate_up = Linear(w.reshape(2 * i, e).contiguous())
+        else:
+            self.tile = 0
+            self.gate_up = Linear(torch.cat([gate, up], 0).contiguous())
         self.down = Linear(tensors[p + "down_proj.weight"])
 
     def forward(self, h: torch.Tensor, ctx=None) -> torch.Tensor:
-        return self.down(ops.gated_act(self.gate_up(h), self.activation))
+        w = self.gate_up.weight
+        if self.tile and h.dtype == torch.bfloat16 and ops.skinny_supported(h.shape[0], h.shape[1], h, w):
+            a = ops.gemm_skinny(h, w, None, h.dtype, gated_activation=self.activation)
+        else:
+            a = ops.gated_act(self.gate_up(h), self.activation, self.tile)
+        return self.down(a)

@@ -14,6 +14,8 @@ from .base import Norm, Runtime, TensorSpec
 
 
 class RMSNorm(Norm):
+    cuda_graph_safe = True  # reads nothing of a step but device tensors and sizes fixed per graph
+
     def __init__(self, prefix: str, size: int, eps: float):
         super().__init__(prefix)
         self.size, self.eps = int(size), float(eps)
