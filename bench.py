@@ -162,29 +162,37 @@ def main() -> int:
         length.  Times `steps` steps through the public entry point (host ids in,
         sampled ids out, every step), then `steps` steps of the step function and
         sampler alone (ids stay on the device).  Returns (ms end to end, ms on the
-        device, kernel launches per device step, mean cache length of the device steps)."""
-        start = CONTEXT - 2 * steps - warmup - 1
-        sp = SamplingParams(max_tokens=2 * steps + warmup + 1, ignore_eos=True)
+        device, kernel launches per device step, mean cached tokens per request
+        during the device steps)."""
+        # Requests whose prompts are done start decoding while the others' prompts
+        # are still going in (2,048 new tokens a step), so the first one decodes
+        # `stagger` tokens more than the last; it is the one that ends at CONTEXT.
+        budget = 2 * steps + warmup + 1
+        stagger = -(-batch * CONTEXT // 2048) + 2 if batch > 1 else 0
+        start = CONTEXT - budget - stagger
+        sp = SamplingParams(max_tokens=budget + stagger, ignore_eos=True)
         for p in prompts(batch, start):
             engine.add_request(p, SamplingParams(**vars(sp)))
-        while any(engine.cache.length(r) < start for r in engine.scheduler.running) or engine.scheduler.waiting:
+        while engine.scheduler.waiting or any(engine.cache.length(r) < start for r in engine.scheduler.running):
             engine.step()
+        assert len(engine.scheduler.running) == batch, "a request ended during the prompts"
         for _ in range(warmup):
             engine.step()
         e2e_ms = timed(engine.step, steps)
         assert len(engine.scheduler.running) == batch
         entries = [StepEntry(r.request_id, [r.generated[-1]], [0]) for r in engine.scheduler.running.values()]
-
         zeros, ones = [0.0] * batch, [1.0] * batch
+        held = sum(engine.cache.length(r) for r in engine.scheduler.running) / batch
 
         def device_step():
             engine.runner.step_and_sample(entries, zeros, ones, zeros)
         n0 = ops.launch_count()
         dev_ms = timed(device_step, steps)
         launches = (ops.launch_count() - n0) // steps
+        assert max(engine.cache.length(r) for r in engine.scheduler.running) <= CONTEXT
         for r in list(engine.scheduler.running.values()):
             engine.scheduler._finish(r, "length")
-        return e2e_ms, dev_ms, launches, CONTEXT - steps // 2
+        return e2e_ms, dev_ms, launches, held + steps / 2.0
 
     out = {"metric": "decode tok/s @ batch %d, Qwen3-8B bf16, context %d" % (args.batch, CONTEXT),
            "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "higher_is_better": True, "scaling": "weak",

@@ -391,3 +391,47 @@ def test_gemm_skinny_refuses_what_it_cannot_do():
     with pytest.raises(KernelError):
         ops().gemm_skinny(rnd((4, 40), torch.bfloat16, 1), rnd((32, 40), torch.bfloat16, 2))
     assert not ops().skinny_supported(4, 40, a, w) and not ops().skinny_supported(9, 64, a, w)
+
+
+# ----------------------------------------------------------------------------
+def prefill_inputs(seqs):
+    cu = np.concatenate([[0], np.cumsum([n for _, n in seqs])]).astype(np.int32)
+    offs = np.asarray([o for o, _ in seqs], np.int32)
+    return torch.from_numpy(cu).to(DEV), torch.from_numpy(offs).to(DEV)
+
+
+PREFILL_CASES = [
+    # (seqs (kv_offset, new tokens), H, Hk, D, S, window)
+    ([(0, 1)], 4, 2, 64, 16, 0),                               # a sequence's first token
+    ([(0, 64)], 4, 2, 128, 16, 0),                             # exactly one tile
+    ([(0, 65), (0, 3), (0, 127)], 4, 4, 128, 16, 0),           # one past a tile, a short one, one short of two tiles
+    ([(0, 8), (20, 4), (10, 1)], 8, 2, 64, 16, 0),             # the reference's mixed batch: cold 8, warm 4 @20, decode 1 @10
+    ([(100, 200), (63, 2), (64, 1), (300, 1)], 8, 2, 128, 16, 0),   # portions on top of cached keys, decodes beside them
+    ([(0, 300)], 6, 3, 64, 32, 0),                             # pages of 32, 3 groups
+    ([(0, 200), (150, 90), (400, 1)], 4, 1, 128, 16, 70),      # a window that is no multiple of the tile
+    ([(7, 130)], 32, 8, 128, 16, 0),                           # the flagship's head layout
+]
+
+
+@pytest.mark.parametrize("case", range(len(PREFILL_CASES)))
+def test_paged_prefill_attention(case):
+    seqs, H, Hk, D, S, window = PREFILL_CASES[case]
+    q, kp, vp, bt, sot, pos, want = paged_case(torch.bfloat16, seqs, H, Hk, D, S, window, seed=60 + case)
+    cu, offs = prefill_inputs(seqs)
+    out = ops().paged_prefill_attention(q, H * D, kp, vp, bt, cu, offs, 1 / math.sqrt(D), window, H, Hk, D,
+                                        len(seqs), max(n for _, n in seqs), q.shape[0])
+    close(out, want, torch.bfloat16, what="prefill attention case %d" % case)
+    gen = ops().paged_attention_generic(q, H * D, kp, vp, bt, sot, pos, 1 / math.sqrt(D), window, H, Hk, D, q.shape[0])
+    assert (out.float() - gen.float()).abs().max() < 2e-2
+
+
+@pytest.mark.parametrize("far", [0, 63, 64, 500, 777])
+def test_prefill_attention_finds_one_far_key(far):
+    H, Hk, D, S = 8, 2, 128, 16
+    seqs = [(700, 100)]
+    q, kp, vp, bt, sot, pos, want = paged_case(torch.bfloat16, seqs, H, Hk, D, S, 0, seed=15, spike=far)
+    cu, offs = prefill_inputs(seqs)
+    out = ops().paged_prefill_attention(q, H * D, kp, vp, bt, cu, offs, 1 / math.sqrt(D), 0, H, Hk, D, 1, 100, 100)
+    close(out, want, torch.bfloat16)
+    page, off = int(bt[0, far // S]), far % S
+    assert torch.allclose(out[-1, :D].float(), vp[page, 0, off].float(), atol=5e-2)  # the last query has the spike

@@ -82,6 +82,106 @@ __global__ void add_rmsnorm_kernel(const float* __restrict__ residual_in, const 
     }
 }
 
+// The same with 8 elements per thread and access (width a multiple of 8, at most
+// 8 * 256 * RN_MAX_ITER): the row stays in registers between the two passes.
+#define RN_THREADS 256
+#define RN_MAX_ITER 4
+
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const bf16* p, float (&v)[8]) {
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+}
+__device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void store8(bf16* p, const float (&v)[8]) {
+    uint4 r;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = r;
+}
+
+template <typename T, int ITER>
+__global__ void __launch_bounds__(RN_THREADS)
+add_rmsnorm_vec_kernel(const float* __restrict__ residual_in, const T* __restrict__ delta,
+                       const int* __restrict__ row_index, float* __restrict__ residual_out,
+                       const float* __restrict__ weight, T* __restrict__ out, int width, float eps) {
+    __shared__ float scratch[32];
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const int s = row_index ? row_index[r] : r;
+    const float* xin = residual_in + (size_t)s * width;
+    const T* din = delta ? delta + (size_t)s * width : nullptr;
+    float* xout = residual_out ? residual_out + (size_t)r * width : nullptr;
+    T* o = out + (size_t)r * width;
+    const int chunks = width >> 3;
+    float x[ITER][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < ITER; ++i) {
+        const int c = threadIdx.x + i * RN_THREADS;
+        if (c < chunks) {
+            load8(xin + c * 8, x[i]);
+            if (din) {
+                float d[8];
+                load8(din + c * 8, d);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) x[i][j] += d[j];
+            }
+            if (xout) store8(xout + c * 8, x[i]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss += x[i][j] * x[i][j];
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float rstd = rsqrtf(ss / (float)width + eps);
+#pragma unroll
+    for (int i = 0; i < ITER; ++i) {
+        const int c = threadIdx.x + i * RN_THREADS;
+        if (c < chunks) {
+            float w[8], y[8];
+            load8(weight + c * 8, w);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) y[j] = x[i][j] * rstd * w[j];
+            store8(o + c * 8, y);
+        }
+    }
+}
+
+template <typename T>
+static int launch_add_rmsnorm(const float* residual_in, const T* delta, const int* row_index, float* residual_out,
+                              const float* weight, T* out, int rows, int width, float eps, cudaStream_t stream) {
+    const bool aligned = !((((uintptr_t)residual_in) | ((uintptr_t)delta) | ((uintptr_t)residual_out) |
+                            ((uintptr_t)weight) | ((uintptr_t)out)) & 15);
+    if (width % 8 == 0 && aligned && width <= 8 * RN_THREADS * RN_MAX_ITER) {
+        const int iter = (width / 8 + RN_THREADS - 1) / RN_THREADS;
+        if (iter <= 1)
+            VX_LAUNCH_K(VX_K_ELEMENTWISE, (add_rmsnorm_vec_kernel<T, 1>), rows, RN_THREADS, 0, stream, residual_in,
+                        delta, row_index, residual_out, weight, out, width, eps);
+        else if (iter == 2)
+            VX_LAUNCH_K(VX_K_ELEMENTWISE, (add_rmsnorm_vec_kernel<T, 2>), rows, RN_THREADS, 0, stream, residual_in,
+                        delta, row_index, residual_out, weight, out, width, eps);
+        else
+            VX_LAUNCH_K(VX_K_ELEMENTWISE, (add_rmsnorm_vec_kernel<T, 4>), rows, RN_THREADS, 0, stream, residual_in,
+                        delta, row_index, residual_out, weight, out, width, eps);
+    } else {
+        const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (add_rmsnorm_kernel<T>), rows, threads, 0, stream, residual_in, delta,
+                    row_index, residual_out, weight, out, width, eps);
+    }
+    VX_LAUNCH_CHECK();
+    return VX_OK;
+}
+
 extern "C" int vx_add_rmsnorm(const float* residual_in, const void* delta, const int* row_index,
                               float* residual_out, const float* weight, void* out, int rows,
                               int width, float eps, int dtype, cudaStream_t stream) {
@@ -89,15 +189,13 @@ extern "C" int vx_add_rmsnorm(const float* residual_in, const void* delta, const
     if (width <= 0) return VX_ERR_SHAPE;
     // In place (residual_out == residual_in) is only sound without a gather.
     if (row_index && residual_out == residual_in) return VX_ERR_SHAPE;
-    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
     if (dtype == VX_F32)
-        VX_LAUNCH_K(VX_K_ELEMENTWISE, (add_rmsnorm_kernel<float>), rows, threads, 0, stream, residual_in, (const float*)delta, row_index, residual_out, weight, (float*)out, width, eps);
-    else if (dtype == VX_BF16)
-        VX_LAUNCH_K(VX_K_ELEMENTWISE, (add_rmsnorm_kernel<bf16>), rows, threads, 0, stream, residual_in, (const bf16*)delta, row_index, residual_out, weight, (bf16*)out, width, eps);
-    else
-        return VX_ERR_DTYPE;
-    VX_LAUNCH_CHECK();
-    return VX_OK;
+        return launch_add_rmsnorm<float>(residual_in, (const float*)delta, row_index, residual_out, weight,
+                                         (float*)out, rows, width, eps, stream);
+    if (dtype == VX_BF16)
+        return launch_add_rmsnorm<bf16>(residual_in, (const bf16*)delta, row_index, residual_out, weight,
+                                        (bf16*)out, rows, width, eps, stream);
+    return VX_ERR_DTYPE;
 }
 
 // Plain RMSNorm of rows of element type T (no residual), statistics in float32.
@@ -155,18 +253,60 @@ __global__ void gated_act_kernel(const T* __restrict__ gate_up, T* __restrict__ 
     }
 }
 
+// Eight features per thread: with tiles of 8 (block == 8) the gates of a tile are
+// 16 contiguous bytes (bf16) followed by its ups; with halves (block == 0) eight
+// gates and eight ups are contiguous each.  inner a multiple of 8, 16-byte aligned.
+template <typename T>
+__global__ void gated_act_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long chunks,
+                                     int inner, int act, int block) {
+    pdl_trigger();
+    pdl_wait();
+    const int per_row = inner >> 3;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < chunks;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const long long t = idx / per_row;
+        const int c = (int)(idx - t * per_row);
+        const T* row = gate_up + t * 2 * inner;
+        float g[8], u[8], y[8];
+        if (block == 8) {
+            load8(row + c * 16, g);
+            load8(row + c * 16 + 8, u);
+        } else {
+            load8(row + c * 8, g);
+            load8(row + inner + c * 8, u);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) y[j] = activation(g[j], act) * u[j];
+        store8(out + t * inner + c * 8, y);
+    }
+}
+
 extern "C" int vx_gated_act(const void* gate_up, void* out, int rows, int inner, int act, int block, int dtype,
                             cudaStream_t stream) {
     if (rows <= 0) return VX_OK;
     if (inner <= 0 || act < 0 || act > 3 || block < 0 || (block > 0 && inner % block)) return VX_ERR_SHAPE;
     const long long total = (long long)rows * inner;
     const int threads = 256;
-    long long blocks = (total + threads - 1) / threads;
-    if (blocks > 148 * 16) blocks = 148 * 16;
-    if (dtype == VX_F32)
-        VX_LAUNCH_K(VX_K_ELEMENTWISE, (gated_act_kernel<float>), (int)blocks, threads, 0, stream, (const float*)gate_up, (float*)out, total, inner, act, block);
-    else if (dtype == VX_BF16)
-        VX_LAUNCH_K(VX_K_ELEMENTWISE, (gated_act_kernel<bf16>), (int)blocks, threads, 0, stream, (const bf16*)gate_up, (bf16*)out, total, inner, act, block);
+    const bool vec = inner % 8 == 0 && (block == 0 || block == 8) &&
+                     !((((uintptr_t)gate_up) | ((uintptr_t)out)) & 15);
+    const long long items = vec ? total / 8 : total;
+    long long blocks = (items + threads - 1) / threads;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (dtype == VX_F32) {
+        if (vec)
+            VX_LAUNCH_K(VX_K_ELEMENTWISE, (gated_act_vec_kernel<float>), (int)blocks, threads, 0, stream,
+                        (const float*)gate_up, (float*)out, items, inner, act, block);
+        else
+            VX_LAUNCH_K(VX_K_ELEMENTWISE, (gated_act_kernel<float>), (int)blocks, threads, 0, stream,
+                        (const float*)gate_up, (float*)out, total, inner, act, block);
+    } else if (dtype == VX_BF16) {
+        if (vec)
+            VX_LAUNCH_K(VX_K_ELEMENTWISE, (gated_act_vec_kernel<bf16>), (int)blocks, threads, 0, stream,
+                        (const bf16*)gate_up, (bf16*)out, items, inner, act, block);
+        else
+            VX_LAUNCH_K(VX_K_ELEMENTWISE, (gated_act_kernel<bf16>), (int)blocks, threads, 0, stream,
+                        (const bf16*)gate_up, (bf16*)out, total, inner, act, block);
+    }
     else
         return VX_ERR_DTYPE;
     VX_LAUNCH_CHECK();

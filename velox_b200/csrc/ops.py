@@ -72,6 +72,7 @@ def _declare(lib) -> None:
         "vx_paged_attention_generic": [P, I, P, P, P, I, P, P, P, I, F, I, I, I, I, I, I, I, P],
         "vx_gemm_nt_simt": [P, P, P, P, I, I, I, I, I, I, I, I, P],
         "vx_gemm_skinny": [P, P, P, P, I, I, I, I, I, I, I, I, I, P],
+        "vx_paged_prefill_attention": [P, I, P, P, P, I, P, P, P, I, F, I, I, I, I, I, I, I, P],
         "vx_paged_decode_attention": [P, I, P, P, P, I, P, P, P, P, I, P, I, F, I, I, I, I, I, I, I, P],
         "vx_sample": [P, I, I, I, P, P, P, P, P],
     }
@@ -286,6 +287,29 @@ def paged_decode_attention(q: torch.Tensor, q_row_stride: int, k_pool, v_pool, b
         _ptr(token_rows), _ptr(seq_of_token), _ptr(positions), _ptr(scratch), max_splits, _ptr(out),
         num_heads * head_dim, float(scale), int(window), requests, num_heads, num_kv_heads, head_dim,
         k_pool.shape[2], DECODE_CHUNK_TILES, _stream()), "paged_decode_attention")
+    return out
+
+
+def prefill_attention_supported(dtype, head_dim: int, page_size: int) -> bool:
+    return dtype == torch.bfloat16 and head_dim in (64, 128) and page_size % 16 == 0
+
+
+def paged_prefill_attention(q: torch.Tensor, q_row_stride: int, k_pool, v_pool, block_table: torch.Tensor,
+                            cu_seqlens, kv_offsets, scale: float, window: int, num_heads: int, num_kv_heads: int,
+                            head_dim: int, requests: int, max_new: int, tokens: int) -> torch.Tensor:
+    """Causal attention of prompt portions over the pages (bfloat16, tensor cores):
+    request i brings token rows [cu_seqlens[i], cu_seqlens[i+1]) at positions
+    kv_offsets[i] onward; `max_new` bounds the tokens of any request."""
+    _dev(q, k_pool, v_pool, block_table, cu_seqlens, kv_offsets)
+    _need(q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and v_pool.dtype == torch.bfloat16,
+          "paged_prefill_attention: bfloat16 only")
+    _need(block_table.dtype == torch.int32 and block_table.is_contiguous() and block_table.dim() == 2,
+          "paged_prefill_attention: int32 block table [requests, blocks]")
+    out = torch.empty((tokens, num_heads * head_dim), dtype=q.dtype, device=q.device)
+    _check(library().vx_paged_prefill_attention(
+        _ptr(q), q_row_stride, _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1],
+        _ptr(cu_seqlens), _ptr(kv_offsets), _ptr(out), num_heads * head_dim, float(scale), int(window), requests,
+        int(max_new), num_heads, num_kv_heads, head_dim, k_pool.shape[2], _stream()), "paged_prefill_attention")
     return out
 
 

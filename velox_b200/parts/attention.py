@@ -113,6 +113,10 @@ class PagedAttention(Mixer):
             return ops.paged_decode_attention(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
                                               ctx.seq_of_token, ctx.positions, self.scale, self.window, H, Hk, D,
                                               ctx.n_seqs, ctx.max_kv)
+        if ops.prefill_attention_supported(qkv.dtype, D, cache.k_pool.shape[2]):
+            return ops.paged_prefill_attention(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
+                                               ctx.cu_seqlens, ctx.kv_offsets, self.scale, self.window, H, Hk, D,
+                                               ctx.n_seqs, ctx.max_new, qkv.shape[0])
         return ops.paged_attention_generic(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
                                            ctx.seq_of_token, ctx.positions, self.scale, self.window, H, Hk, D,
                                            qkv.shape[0])
