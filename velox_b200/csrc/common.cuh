@@ -15,6 +15,7 @@
 #define VX_ERR_DTYPE (-2)    // an element type code the kernel does not know
 #define VX_ERR_ALIGN (-3)    // a pointer or stride that is not aligned as needed
 #define VX_ERR_LIMIT (-4)    // beyond a stated maximum
+#define VX_ERR_DRIVER (-5)   // the driver lacks an entry point the kernel needs
 
 #define VX_F32 0
 #define VX_BF16 1

@@ -1,0 +1,306 @@
+// C[M,N] = A[M,K] * W[N,K]^T (+ bias) in bfloat16 on the fifth-generation tensor
+// cores: tcgen05.mma with the accumulator in tensor memory, operands brought into
+// shared memory by TMA.
+//
+// A block computes one 128 x BN tile of C (BN = 128 or 256) and has six warps:
+//   warp 0   producer: one thread waits for a free stage and issues two tiled TMA
+//            loads (cp.async.bulk.tensor.2d, 128-byte swizzle): a 128 x 64 tile of A
+//            and a BN x 64 tile of W, completion counted on the stage's "full"
+//            mbarrier;
+//   warp 1   allocates BN columns of tensor memory; one thread waits for a full
+//            stage, issues four tcgen05.mma (M 128, N BN, K 16 each) whose operands
+//            are shared-memory descriptors of the swizzled tiles, and commits them to
+//            the stage's "empty" mbarrier, so the stage is free when the tensor core
+//            has read it; after the last k block it commits to the "accumulator
+//            ready" mbarrier;
+//   warps 2-5  epilogue: each reads its 32 lanes (rows) of the accumulator with
+//            tcgen05.ld, 32 columns at a time, adds the bias, rounds to bfloat16 and
+//            stores; or, gated, takes act(gate) * up of column tiles laid out as 8
+//            gate columns followed by their 8 up columns, in float32, and stores
+//            half as many columns.
+// Rows past M and columns past N are zero-filled by TMA on the way in and masked on
+// the way out; K may end inside a k block (zero-filled too).
+//
+// Every wait on an mbarrier is bounded.  If one runs out the block records a code
+// in the caller's error word, the other roles run out of their own bounded waits,
+// and the block frees its tensor memory and returns.
+//
+// Sizes: K a multiple of 8, rows of A, W and C 16-byte aligned, N a multiple of 16.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define TC_BM 128
+#define TC_BK 64
+#define TC_THREADS 192
+#define TC_SPIN_LIMIT (1 << 24)
+#define TC_ERR_PRODUCER 1
+#define TC_ERR_MMA 2
+#define TC_ERR_EPILOGUE 3
+
+__device__ __forceinline__ unsigned tc_smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void tc_mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void tc_mbar_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool tc_mbar_wait(unsigned bar, unsigned parity) {
+    for (int i = 0; i < TC_SPIN_LIMIT; ++i) {
+        unsigned ok;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tc_tma_load_2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+// Shared-memory descriptor of a K-major tile with 128-byte swizzle: rows 128 bytes
+// apart, groups of 8 rows 1024 bytes apart (the tile is exactly one swizzle atom
+// wide), version 1, layout type 2 (128-byte swizzle).
+__device__ __forceinline__ unsigned long long tc_smem_desc(unsigned addr) {
+    return (unsigned long long)((addr >> 4) & 0x3FFF) | (1ull << 16) | ((unsigned long long)(1024 >> 4) << 32) |
+           (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void tc_mma(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc,
+                                       unsigned idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void tc_commit(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(unsigned taddr, unsigned (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+template <int BN, int STAGES, bool GATED>
+__global__ void __launch_bounds__(TC_THREADS)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    const float* __restrict__ bias, bf16* __restrict__ C, int M, int N, int K, int ldc, int act,
+                    int* __restrict__ error) {
+    extern __shared__ unsigned char tc_smem_raw[];
+    __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], acc_bar;
+    __shared__ unsigned tmem_base_s;
+    __shared__ int failed;
+    constexpr unsigned A_BYTES = TC_BM * TC_BK * 2, W_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
+    // the swizzled tiles must start on 1024-byte boundaries
+    unsigned char* tiles = (unsigned char*)(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
+    pdl_trigger();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // consecutive blocks share a tile of W and walk over the rows of A (which stays in L2), so W is read once
+    const int m0 = blockIdx.x * TC_BM, n0 = blockIdx.y * BN;
+    const int nkb = (K + TC_BK - 1) / TC_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            tc_mbar_init(tc_smem_u32(&full_bar[s]), 1);
+            tc_mbar_init(tc_smem_u32(&empty_bar[s]), 1);
+        }
+        tc_mbar_init(tc_smem_u32(&acc_bar), 1);
+        failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {  // tensor memory for the accumulator: BN columns of 128 lanes
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(tc_smem_u32(&tmem_base_s)), "r"((unsigned)BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const unsigned tmem_base = tmem_base_s;
+
+    if (warp == 0) {
+        // ---- producer ----
+        if (lane == 0) {
+            for (int kb = 0; kb < nkb; ++kb) {
+                const int s = kb % STAGES;
+                if (kb >= STAGES &&
+                    !tc_mbar_wait(tc_smem_u32(&empty_bar[s]), (unsigned)(((kb / STAGES) - 1) & 1))) {
+                    failed = 1;
+                    atomicExch(error, TC_ERR_PRODUCER);
+                    break;
+                }
+                if (failed) break;
+                const unsigned bar = tc_smem_u32(&full_bar[s]);
+                tc_mbar_expect_tx(bar, STAGE_BYTES);
+                unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
+                tc_tma_load_2d(tc_smem_u32(st), &map_a, kb * TC_BK, m0, bar);
+                tc_tma_load_2d(tc_smem_u32(st + A_BYTES), &map_w, kb * TC_BK, n0, bar);
+            }
+        }
+    } else if (warp == 1) {
+        // ---- tensor core ----
+        if (lane == 0) {
+            // instruction descriptor: float32 accumulator, bfloat16 A and B, both K-major, N = BN, M = 128
+            const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) |
+                                   ((unsigned)(TC_BM >> 4) << 24);
+            bool ok = true;
+            for (int kb = 0; kb < nkb; ++kb) {
+                const int s = kb % STAGES;
+                if (!tc_mbar_wait(tc_smem_u32(&full_bar[s]), (unsigned)((kb / STAGES) & 1))) {
+                    failed = 1;
+                    atomicExch(error, TC_ERR_MMA);
+                    ok = false;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const unsigned a_addr = tc_smem_u32(tiles + (size_t)s * STAGE_BYTES);
+                const unsigned long long adesc = tc_smem_desc(a_addr), bdesc = tc_smem_desc(a_addr + A_BYTES);
+#pragma unroll
+                for (int k4 = 0; k4 < TC_BK / 16; ++k4)   // 32 bytes further along K inside the swizzle atom
+                    tc_mma(tmem_base, adesc + (unsigned long long)(k4 * 2), bdesc + (unsigned long long)(k4 * 2),
+                           idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+                tc_commit(tc_smem_u32(&empty_bar[s]));   // the stage is free once these have read it
+            }
+            if (ok) tc_commit(tc_smem_u32(&acc_bar));    // the accumulator is complete once all have finished
+        }
+    } else {
+        // ---- epilogue: warp w reads lanes 32 * (w % 4) .. + 31 of tensor memory ----
+        const int quarter = warp & 3;
+        const int row = m0 + quarter * 32 + lane;
+        bool ok = tc_mbar_wait(tc_smem_u32(&acc_bar), 0);
+        if (!ok && lane == 0) { failed = 1; atomicExch(error, TC_ERR_EPILOGUE); }
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                if (n0 + c0 >= N) break;   // (uniform) columns past N hold zeros
+                unsigned r[32];
+                tc_ld32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)c0, r);
+                if (row >= M) continue;
+                if (!GATED) {
+                    bf16* dst = C + (size_t)row * ldc + n0 + c0;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        if (n0 + c0 + j >= N) break;
+                        float v[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            v[i] = __uint_as_float(r[j + i]);
+                            if (bias) v[i] += bias[n0 + c0 + j + i];
+                        }
+                        uint4 pk;
+                        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                        *reinterpret_cast<uint4*>(dst + j) = pk;
+                    }
+                } else {
+                    bf16* dst = C + (size_t)row * ldc + ((n0 + c0) >> 1);
+#pragma unroll
+                    for (int t = 0; t < 2; ++t) {   // two tiles of 8 gates + 8 ups
+                        if (n0 + c0 + t * 16 >= N) break;
+                        uint4 pk;
+                        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float g0 = __uint_as_float(r[t * 16 + 2 * i]), g1 = __uint_as_float(r[t * 16 + 2 * i + 1]);
+                            const float u0 = __uint_as_float(r[t * 16 + 8 + 2 * i]), u1 = __uint_as_float(r[t * 16 + 9 + 2 * i]);
+                            h[i] = __floats2bfloat162_rn(activation(g0, act) * u0, activation(g1, act) * u1);
+                        }
+                        *reinterpret_cast<uint4*>(dst + t * 8) = pk;
+                    }
+                }
+            }
+        }
+    }
+    // everybody meets before the tensor memory goes back (every wait above was bounded)
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((unsigned)BN) : "memory");
+    }
+}
+
+// ---- host side ----
+typedef CUresult (*tc_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static tc_encode_fn tc_encoder() {
+    static tc_encode_fn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (tc_encode_fn)p;
+    }
+    return fn;
+}
+
+// A [rows, K] bfloat16 matrix with row stride ld, read in boxes of box_rows x 64.
+static bool tc_make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int box_rows) {
+    tc_encode_fn enc = tc_encoder();
+    if (!enc) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int STAGES, bool GATED>
+static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mw, const float* bias, bf16* C, int M, int N, int K,
+                     int ldc, int act, int* error, cudaStream_t stream) {
+    const size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, GATED>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid((M + TC_BM - 1) / TC_BM, (N + BN - 1) / BN);
+    VX_LAUNCH_K(VX_K_GEMM, (gemm_tcgen05_kernel<BN, STAGES, GATED>), grid, TC_THREADS, smem, stream, ma, mw, bias, C, M,
+                N, K, ldc, act, error);
+    VX_LAUNCH_CHECK();
+    return VX_OK;
+}
+
+// gated: 0 plain, C is [M, N]; 1: W's rows come in tiles of 8 gate rows followed by
+// their 8 up rows and C is [M, N/2] = act(gate) * up.  `error` is a device int that
+// a block sets (TC_ERR_*) if one of its bounded waits runs out; the caller zeroes it
+// and reads it when it wants to know.  `wide` picks 128 x 256 tiles (else 128 x 128).
+extern "C" int vx_gemm_tcgen05(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int lda,
+                               int ldw, int ldc, int gated, int act, int wide, int* error, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return VX_OK;
+    if (K <= 0 || (K & 7) || (N & 15) || !error) return VX_ERR_SHAPE;
+    if ((lda & 7) || (ldw & 7) || (ldc & 7) || lda < K || ldw < K) return VX_ERR_ALIGN;
+    if ((((uintptr_t)A) | ((uintptr_t)W) | ((uintptr_t)C)) & 15) return VX_ERR_ALIGN;
+    if (gated && (bias || act < 0 || act > 3)) return VX_ERR_SHAPE;
+    if (ldc < (gated ? N / 2 : N)) return VX_ERR_SHAPE;
+    if ((N + 127) / 128 > 65535) return VX_ERR_LIMIT;
+    CUtensorMap ma, mw;
+    const int bn = wide ? 256 : 128;
+    if (!tc_make_map(&ma, A, M, K, lda, TC_BM) || !tc_make_map(&mw, W, N, K, ldw, bn)) return VX_ERR_DRIVER;
+    bf16* c = (bf16*)C;
+    if (wide)
+        return gated ? tc_launch<256, 4, true>(ma, mw, bias, c, M, N, K, ldc, act, error, stream)
+                     : tc_launch<256, 4, false>(ma, mw, bias, c, M, N, K, ldc, act, error, stream);
+    return gated ? tc_launch<128, 6, true>(ma, mw, bias, c, M, N, K, ldc, act, error, stream)
+                 : tc_launch<128, 6, false>(ma, mw, bias, c, M, N, K, ldc, act, error, stream);
+}

@@ -71,6 +71,7 @@ def _declare(lib) -> None:
         "vx_qk_norm_rope_kv": [P, I, P, P, F, P, I, P, P, P, P, I, I, I, I, I, I, P],
         "vx_paged_attention_generic": [P, I, P, P, P, I, P, P, P, I, F, I, I, I, I, I, I, I, P],
         "vx_gemm_nt_simt": [P, P, P, P, I, I, I, I, I, I, I, I, P],
+        "vx_gemm_tcgen05": [P, P, P, P, I, I, I, I, I, I, I, I, I, P, P],
         "vx_gemm_skinny": [P, P, P, P, I, I, I, I, I, I, I, I, I, P],
         "vx_paged_prefill_attention": [P, I, P, P, P, I, P, P, P, I, F, I, I, I, I, I, I, I, P],
         "vx_paged_decode_attention": [P, I, P, P, P, I, P, P, P, P, I, P, I, F, I, I, I, I, I, I, I, P],
@@ -326,6 +327,59 @@ def gemm_nt_simt(a: torch.Tensor, w: torch.Tensor, bias=None, out_dtype: Optiona
     out = torch.empty((m, n), dtype=out_dtype, device=a.device)
     _check(library().vx_gemm_nt_simt(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), m, n, k, a.stride(0), w.stride(0), n,
                                      dtype_code(a.dtype), dtype_code(out_dtype), _stream()), "gemm_nt_simt")
+    return out
+
+
+_ERROR_WORDS = {}
+
+
+def _error_word(device) -> torch.Tensor:
+    """The device int that kernels with bounded waits report into."""
+    key = str(device)
+    if key not in _ERROR_WORDS:
+        _ERROR_WORDS[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _ERROR_WORDS[key]
+
+
+def check_device_errors() -> None:
+    """Raises if a kernel has reported that one of its bounded waits ran out since
+    the last check (its results are then missing).  Synchronises the device."""
+    for key, word in _ERROR_WORDS.items():
+        code = int(word.item())
+        if code:
+            word.zero_()
+            raise KernelError("a kernel on %s gave up a wait on its asynchronous copies or tensor-core work "
+                              "(code %d); its results are missing" % (key, code))
+
+
+def tcgen05_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and w.shape[0] % 16 == 0
+            and a.stride(1) == 1 and w.stride(1) == 1 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias=None, gated_activation: Optional[str] = None,
+                 wide: bool = True) -> torch.Tensor:
+    """a [M,K] times w [N,K] transposed on the tcgen05 tensor cores (bfloat16 in and
+    out, float32 accumulation in tensor memory, operands by TMA).  With
+    `gated_activation`, w's rows come in tiles of 8 gate rows followed by their 8 up
+    rows and the result is act(gate) * up, [M, N/2].  `wide`: 128 x 256 tiles, else
+    128 x 128."""
+    _dev(a, w, bias)
+    _need(a.dim() == 2 and w.dim() == 2 and a.shape[1] == w.shape[1], "gemm_tcgen05: a [M,K], w [N,K]")
+    _need(tcgen05_supported(a, w), "gemm_tcgen05: bfloat16, K a multiple of 8, N a multiple of 16, 16-byte aligned rows")
+    m, k = a.shape
+    n = w.shape[0]
+    cols = n // 2 if gated_activation else n
+    if gated_activation is not None:
+        _need(gated_activation in ACTIVATIONS, "gemm_tcgen05: unknown activation %r" % gated_activation)
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == n, "gemm_tcgen05: float32 bias of N elements")
+    out = torch.empty((m, cols), dtype=torch.bfloat16, device=a.device)
+    _need(cols % 8 == 0, "gemm_tcgen05: output rows must be 16-byte aligned")
+    _check(library().vx_gemm_tcgen05(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), m, n, k, a.stride(0), w.stride(0), cols,
+                                     1 if gated_activation else 0, ACTIVATIONS.get(gated_activation, 0),
+                                     1 if wide else 0, _ptr(_error_word(a.device)), _stream()), "gemm_tcgen05")
     return out
 
 
