@@ -19,6 +19,7 @@ import torch
 
 from .. import models as _models  # noqa: F401  (registers architectures)
 from ..cache.manager import CacheManager
+from ..csrc import ops
 from ..config.engine_config import EngineConfig
 from ..config.model_config import ModelConfig
 from ..config.registry import load_config, resolve_architecture
@@ -142,6 +143,9 @@ class Engine:
             0, len(r.generated)) for r in reqs]
         _logits, ids = self.runner.step_and_sample(entries, temps, tops, us)
         sampled: List[int] = ids.tolist() if ids is not None else []
+        if self.runner.pending_error_check:
+            self.runner.pending_error_check = False
+            ops.check_device_errors()
         return self.scheduler.update(entries, sampled)
 
     def run_step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:

@@ -26,6 +26,7 @@ class ModelRunner:
     def __init__(self, model, cache: CacheManager, device, vocab_size: int, cuda_graphs: bool = False):
         self.model, self.cache, self.device, self.vocab_size = model, cache, torch.device(device), int(vocab_size)
         self.steps = 0
+        self.pending_error_check = False
         self.graphs = None
         if cuda_graphs:
             from .graphs import DecodeGraphs
@@ -85,6 +86,10 @@ class ModelRunner:
         else:
             ctx = build_step_context(entries, self.cache, self.device, self.vocab_size)
             logits = self.run(ctx)
+            if ctx.n_tokens >= 1024:
+                # large steps use kernels whose waits are bounded: a wait that ran out
+                # must not pass for a result
+                self.pending_error_check = True
             if sample and logits is not None:
                 t = torch.tensor([sampling[0], sampling[1], sampling[2]], dtype=torch.float32).to(self.device, non_blocking=True)
                 ids = ops.sample(logits, t[0], t[1], t[2]) if any(x > 0 for x in sampling[0]) else ops.sample(logits)

@@ -19,6 +19,7 @@ from .linear import Linear
 
 
 GATE_TILE = 8
+FUSED_TCGEN05_MIN_ROWS = 1024
 
 
 class GatedMLP(FeedForward):
@@ -55,8 +56,14 @@ class GatedMLP(FeedForward):
 
     def forward(self, h: torch.Tensor, ctx=None) -> torch.Tensor:
         w = self.gate_up.weight
-        if self.tile and h.dtype == torch.bfloat16 and ops.skinny_supported(h.shape[0], h.shape[1], h, w):
+        fused = self.tile and h.dtype == torch.bfloat16
+        if fused and ops.skinny_supported(h.shape[0], h.shape[1], h, w):
+            # a decode step: W streamed once, act(gate) * up taken on the accumulators
             a = ops.gemm_skinny(h, w, None, h.dtype, gated_activation=self.activation)
+        elif fused and h.shape[0] >= FUSED_TCGEN05_MIN_ROWS and ops.tcgen05_supported(h, w):
+            # a prompt portion: tcgen05 product with the same epilogue (measured faster than
+            # the library product followed by the activation kernel from about a thousand rows)
+            a = ops.gemm_tcgen05(h, w, None, gated_activation=self.activation)
         else:
             a = ops.gated_act(self.gate_up(h), self.activation, self.tile)
         return self.down(a)
