@@ -471,3 +471,42 @@ def test_gemm_tcgen05_gated(M, I, K, wide):
     want = torch.nn.functional.silu(g) * u
     assert got.shape == (M, I)
     assert (got.float() - want).abs().max() <= 3e-2 + 3e-2 * float(want.abs().max())
+
+
+# ----------------------------------------------------------------------------
+TC_PREFILL_CASES = [
+    ([(0, 1)], 4, 2, 128, 16, 0),                                  # a sequence's first token
+    ([(0, 128)], 4, 1, 128, 16, 0),                                # 4 heads share a tile: 32 tokens each
+    ([(0, 65), (0, 3), (0, 127)], 4, 4, 128, 16, 0),               # no sharing: 128 tokens a tile
+    ([(100, 200), (63, 2), (64, 1), (300, 1)], 8, 2, 128, 16, 0),  # portions on top of cached keys, decodes beside them
+    ([(0, 300)], 16, 2, 128, 32, 0),                               # 8 heads share, pages of 32
+    ([(0, 400), (350, 90), (600, 1)], 4, 1, 128, 16, 170),         # a window that is no multiple of the tile
+    ([(7, 333)], 32, 8, 128, 16, 0),                               # the flagship's head layout
+    ([(0, 700)], 2, 1, 128, 16, 0),                                # two heads share: several tiles deep
+]
+
+
+@pytest.mark.parametrize("case", range(len(TC_PREFILL_CASES)))
+def test_paged_prefill_attention_tc(case):
+    seqs, H, Hk, D, S, window = TC_PREFILL_CASES[case]
+    q, kp, vp, bt, sot, pos, want = paged_case(torch.bfloat16, seqs, H, Hk, D, S, window, seed=80 + case)
+    cu, offs = prefill_inputs(seqs)
+    out = ops().paged_prefill_attention_tc(q, H * D, kp, vp, bt, cu, offs, 1 / math.sqrt(D), window, H, Hk, D,
+                                           len(seqs), max(n for _, n in seqs), q.shape[0])
+    ops().check_device_errors()
+    close(out, want, torch.bfloat16, what="tcgen05 prefill attention case %d" % case)
+    gen = ops().paged_attention_generic(q, H * D, kp, vp, bt, sot, pos, 1 / math.sqrt(D), window, H, Hk, D, q.shape[0])
+    assert (out.float() - gen.float()).abs().max() < 3e-2
+
+
+@pytest.mark.parametrize("far", [0, 127, 128, 500, 777])
+def test_prefill_attention_tc_finds_one_far_key(far):
+    H, Hk, D, S = 8, 2, 128, 16
+    seqs = [(700, 100)]
+    q, kp, vp, bt, sot, pos, want = paged_case(torch.bfloat16, seqs, H, Hk, D, S, 0, seed=16, spike=far)
+    cu, offs = prefill_inputs(seqs)
+    out = ops().paged_prefill_attention_tc(q, H * D, kp, vp, bt, cu, offs, 1 / math.sqrt(D), 0, H, Hk, D, 1, 100, 100)
+    ops().check_device_errors()
+    close(out, want, torch.bfloat16)
+    page, off = int(bt[0, far // S]), far % S
+    assert torch.allclose(out[-1, :D].float(), vp[page, 0, off].float(), atol=5e-2)

@@ -8,6 +8,7 @@ scratch; the library's built-in scratch array is shared by all calls and keeps
 the last call's contents, so the check is made on two calls in a row with
 different inputs.  This file is collected last on purpose."""
 import ctypes
+import gc
 import math
 
 import pytest
@@ -56,6 +57,7 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
         want = ops.paged_decode_attention(q, H * D, kp, vp, bt, sot, pos, 1 / math.sqrt(D), 0, H, Hk, D,
                                           len(lens), max_kv)
         got = torch.zeros_like(want)
+        gc.collect()   # garbage of earlier tests must not be freed between the two readings
         torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
         rc = fn(q.data_ptr(), H * D, kp.data_ptr(), vp.data_ptr(), bt.data_ptr(), bt.shape[1], None,
@@ -63,7 +65,7 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
                 len(lens), H, Hk, D, S, chunk, stream)
         torch.cuda.synchronize()
         assert rc == 0, "call %d returned %d" % (call, rc)
-        assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.memory_allocated() <= before, "the entry point made torch allocate"
         assert torch.isfinite(got.float()).all()
         # the tolerance of the kernel tests (3e-2 + 3e-2 |x|); in fact the two are the same kernels
         assert ((got.float() - want.float()).abs() <= 3e-2 + 3e-2 * want.float().abs()).all(), "call %d" % call

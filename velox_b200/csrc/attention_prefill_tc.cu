@@ -1,0 +1,514 @@
+// Paged causal attention for prompt portions on the fifth-generation tensor cores
+// (tcgen05.mma, accumulators in tensor memory, operands by TMA), bfloat16, head
+// size 128.
+//
+// grid (query tile, kv head, request), one block per SM at a time.  A block takes
+// 128 query rows of one request: 128 / G consecutive new tokens for each of the G
+// query heads of one kv head (G in {1, 2, 4, 8}), so the heads of a group share
+// every key/value tile.  It walks over the request's keys in tiles of 128.
+//
+//   warp 0      producer: loads the query tile once and then, tile by tile, the keys
+//               and the values page by page with tiled TMA loads (128-byte swizzle),
+//               one 16-key x 64-column box per lane, into two shared-memory buffers
+//               each;
+//   warp 1      tensor core: one thread issues S = Q K^T (128 x 128, 8 instructions
+//               of K 16) into one of two score buffers in tensor memory, and, when
+//               the softmax warps have turned a score buffer into probabilities,
+//               O += P V (A operand straight from tensor memory, V as the
+//               MN-major B operand).  S of tile i + 1 is issued before P V of tile i,
+//               so the tensor core works while the softmax of tile i runs;
+//   warps 2-5   softmax: a thread owns one query row (one lane of tensor memory):
+//               it reads the row's 128 scores, scales, masks by select (causal: key
+//               <= the row's position; window: key >= position + 1 - W), keeps the
+//               running maximum and sum in float32 (base 2), writes the
+//               probabilities back over the scores as packed bfloat16, and rescales
+//               the row of O only when the maximum has grown by more than 2^8 (the
+//               probabilities are then bounded by 256 instead of 1, which float32
+//               and bfloat16 hold without loss of accuracy).  At the end the same
+//               warps divide O by the sum and store it.
+//
+// Keys past the request's last key and below its window are masked; the values of a
+// tile that reaches past the last key are cleared in shared memory first, because a
+// never-written slot may hold NaN and 0 * NaN is NaN in the tensor core.
+//
+// Every wait on an mbarrier is bounded.  If one runs out the block records a code
+// in the caller's error word, the other roles run out of their own bounded waits,
+// and the block frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define PT_ROWS 128
+#define PT_KEYS 128
+#define PT_D 128
+#define PT_THREADS 192
+#define PT_SPIN_LIMIT (1 << 24)
+#define PT_LOG2E 1.4426950408889634f
+#define PT_HALF_BYTES (128 * 128)   // 128 rows x 64 columns of bf16: one swizzled half of a tile
+#define PT_TILE_BYTES (2 * PT_HALF_BYTES)
+#define PT_RESCALE_THRESHOLD 8.0f
+
+__device__ __forceinline__ unsigned pt_smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void pt_mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void pt_mbar_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void pt_mbar_arrive(unsigned bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool pt_mbar_wait(unsigned bar, unsigned parity) {
+    for (int i = 0; i < PT_SPIN_LIMIT; ++i) {
+        unsigned ok;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void pt_tma_load_2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+// Shared-memory descriptors, 128-byte swizzle, version 1.  K-major (Q and K: rows
+// 128 bytes apart, groups of 8 rows 1024 bytes apart); MN-major (V: the 64-column
+// halves 16 KB apart = leading offset, groups of 8 keys 1024 bytes apart).
+__device__ __forceinline__ unsigned long long pt_desc_kmajor(unsigned addr) {
+    return (unsigned long long)((addr >> 4) & 0x3FFF) | (1ull << 16) | ((unsigned long long)(1024 >> 4) << 32) |
+           (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ unsigned long long pt_desc_mnmajor(unsigned addr) {
+    return (unsigned long long)((addr >> 4) & 0x3FFF) | ((unsigned long long)(PT_HALF_BYTES >> 4) << 16) |
+           ((unsigned long long)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void pt_mma_ss(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc,
+                                          unsigned idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void pt_mma_ts(unsigned tmem_d, unsigned tmem_a, unsigned long long bdesc, unsigned idesc,
+                                          unsigned accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}\n"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ float pt_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ void pt_commit(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void pt_ld32(unsigned taddr, unsigned (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void pt_st32(unsigned taddr, const unsigned (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void pt_st16(unsigned taddr, const unsigned (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};\n"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+
+// barriers of a block
+struct PtBarriers {
+    unsigned long long q_full;
+    unsigned long long k_full[2], k_empty[2], v_full[2], v_empty[2];
+    unsigned long long s_full[2], p_ready[2], pv_done[2];
+};
+
+__global__ void __launch_bounds__(PT_THREADS)
+paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                                  const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
+                                  int max_blocks, const int* __restrict__ cu_seqlens,
+                                  const int* __restrict__ kv_offsets, bf16* __restrict__ out, int out_row_stride,
+                                  float scale_log2, int window, int H, int Hk, int S, int share_log2,
+                                  int* __restrict__ error) {
+    extern __shared__ unsigned char pt_smem_raw[];
+    __shared__ __align__(8) PtBarriers bars;
+    __shared__ unsigned tmem_base_s;
+    __shared__ int failed;
+    unsigned char* smem = (unsigned char*)(((uintptr_t)pt_smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* q_s = smem;                                   // 32 KB
+    unsigned char* k_s = smem + PT_TILE_BYTES;                   // 2 x 32 KB
+    unsigned char* v_s = smem + 3 * PT_TILE_BYTES;               // 2 x 32 KB
+    pdl_trigger();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // the longest tiles (the last tokens of a prompt) are handed out first
+    const int qt = gridDim.x - 1 - blockIdx.x, hk = blockIdx.y, seq = blockIdx.z;
+    const int share = 1 << share_log2;
+    const int toks_per_tile = PT_ROWS >> share_log2;
+    const int row_base = cu_seqlens[seq];
+    const int n_new = cu_seqlens[seq + 1] - row_base;
+    const int t0 = qt * toks_per_tile;
+    if (t0 >= n_new) return;   // (before anything is allocated)
+    const int off = kv_offsets[seq];
+    const int* bt = block_table + (size_t)seq * max_blocks;
+    const int toks_live = min(toks_per_tile, n_new - t0);
+    const int kv_hi = off + t0 + toks_live;               // one past the last visible key of the tile
+    const int kv_lo = window > 0 ? max(0, off + t0 + 1 - window) : 0;
+    const int tile_lo = kv_lo / PT_KEYS, tile_hi = (kv_hi + PT_KEYS - 1) / PT_KEYS;
+    const int ntiles = tile_hi - tile_lo;
+
+    if (threadIdx.x == 0) {
+        pt_mbar_init(pt_smem_u32(&bars.q_full), 1);
+        for (int i = 0; i < 2; ++i) {
+            pt_mbar_init(pt_smem_u32(&bars.k_full[i]), 1);
+            pt_mbar_init(pt_smem_u32(&bars.k_empty[i]), 1);
+            pt_mbar_init(pt_smem_u32(&bars.v_full[i]), 1);
+            pt_mbar_init(pt_smem_u32(&bars.v_empty[i]), 1);
+            pt_mbar_init(pt_smem_u32(&bars.s_full[i]), 1);
+            pt_mbar_init(pt_smem_u32(&bars.p_ready[i]), 4);   // one arrival per softmax warp
+            pt_mbar_init(pt_smem_u32(&bars.pv_done[i]), 1);
+        }
+        failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {  // tensor memory: scores/probabilities 0 and 1 (128 columns each), output (128)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(pt_smem_u32(&tmem_base_s)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const unsigned tmem_base = tmem_base_s;
+    const unsigned tmem_o = tmem_base + 256;
+
+    if (warp == 0) {
+        // ---------------- producer: the whole warp, one box per lane ----------------
+        // queries: for each shared head, its tokens' two 64-column halves
+        if (lane == 0) pt_mbar_expect_tx(pt_smem_u32(&bars.q_full), PT_TILE_BYTES);
+        __syncwarp();
+        if (lane < 2 * share) {
+            const int hi = lane >> 1, half = lane & 1;
+            pt_tma_load_2d(pt_smem_u32(q_s + half * PT_HALF_BYTES + hi * toks_per_tile * 128), &map_q,
+                           (hk * share + hi) * PT_D + half * 64, row_base + t0, pt_smem_u32(&bars.q_full));
+        }
+        // keys (lanes 0-15) and values (lanes 16-31) of a tile: 8 groups of 16 keys x 2 halves each
+        const int which = lane >> 4, g = (lane & 15) >> 1, half = lane & 1;
+        const CUtensorMap* map = which ? &map_v : &map_k;
+        for (int i = 0; i < ntiles; ++i) {
+            const int b = i & 1;
+            const int key_base = (tile_lo + i) * PT_KEYS;
+            bool ok = true;
+            if (lane == 0) {
+                if (i >= 2)
+                    ok = pt_mbar_wait(pt_smem_u32(&bars.k_empty[b]), (unsigned)(((i >> 1) - 1) & 1)) &&
+                         pt_mbar_wait(pt_smem_u32(&bars.v_empty[b]), (unsigned)(((i >> 1) - 1) & 1));
+                if (ok) {
+                    pt_mbar_expect_tx(pt_smem_u32(&bars.k_full[b]), PT_TILE_BYTES);
+                    pt_mbar_expect_tx(pt_smem_u32(&bars.v_full[b]), PT_TILE_BYTES);
+                } else {
+                    failed = 1;
+                    atomicExch(error, 11);
+                }
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            // Groups of 16 keys outside [kv_lo, kv_hi) repeat the nearest group inside: they
+            // are masked anyway, and their pages may not be this request's.
+            int key = key_base + g * 16;
+            key = max(min(key, (kv_hi - 1) & ~15), kv_lo & ~15);
+            const int page = bt[key / S];
+            const int y = (page * Hk + hk) * S + (key % S);
+            unsigned char* dst = (which ? v_s : k_s) + b * PT_TILE_BYTES;
+            pt_tma_load_2d(pt_smem_u32(dst + half * PT_HALF_BYTES + g * 16 * 128), map, half * 64, y,
+                           pt_smem_u32(which ? &bars.v_full[b] : &bars.k_full[b]));
+        }
+    } else if (warp == 1) {
+        // ---------------- tensor core ----------------
+        if (lane == 0) {
+            // S = Q K^T: float32 out, bf16 A and B, both K-major, N = 128 keys, M = 128 rows
+            const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(PT_KEYS >> 3) << 17) |
+                                     ((unsigned)(PT_ROWS >> 4) << 24);
+            // O += P V: A from tensor memory, B = V MN-major (bit 16), N = 128 (head size)
+            const unsigned idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(PT_D >> 3) << 17) |
+                                     ((unsigned)(PT_ROWS >> 4) << 24);
+            auto issue_s = [&](int i) {   // scores of tile i into buffer i & 1
+                const int b = i & 1;
+                const unsigned qa = pt_smem_u32(q_s), ka = pt_smem_u32(k_s + b * PT_TILE_BYTES);
+#pragma unroll
+                for (int k = 0; k < PT_D / 16; ++k) {
+                    const unsigned o = (unsigned)((k >> 2) * PT_HALF_BYTES + (k & 3) * 32);
+                    pt_mma_ss(tmem_base + (unsigned)(b * 128), pt_desc_kmajor(qa + o), pt_desc_kmajor(ka + o), idesc_s,
+                              k > 0 ? 1u : 0u);
+                }
+                pt_commit(pt_smem_u32(&bars.s_full[b]));
+                pt_commit(pt_smem_u32(&bars.k_empty[b]));
+            };
+            bool ok = pt_mbar_wait(pt_smem_u32(&bars.q_full), 0) && pt_mbar_wait(pt_smem_u32(&bars.k_full[0]), 0);
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                issue_s(0);
+            }
+            for (int i = 0; i < ntiles && ok; ++i) {
+                const int b = i & 1;
+                if (i + 1 < ntiles) {
+                    // the next scores go into the other buffer, which P V of tile i - 1 must have left
+                    ok = pt_mbar_wait(pt_smem_u32(&bars.k_full[b ^ 1]), (unsigned)(((i + 1) >> 1) & 1));
+                    if (ok && i >= 1) ok = pt_mbar_wait(pt_smem_u32(&bars.pv_done[b ^ 1]), (unsigned)(((i - 1) >> 1) & 1));
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    issue_s(i + 1);
+                }
+                ok = pt_mbar_wait(pt_smem_u32(&bars.v_full[b]), (unsigned)((i >> 1) & 1)) &&
+                     pt_mbar_wait(pt_smem_u32(&bars.p_ready[b]), (unsigned)((i >> 1) & 1));
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const unsigned va = pt_smem_u32(v_s + b * PT_TILE_BYTES);
+#pragma unroll
+                for (int k = 0; k < PT_KEYS / 16; ++k)   // 16 keys a step: 8 columns of packed P, 2 KB of V
+                    pt_mma_ts(tmem_o, tmem_base + (unsigned)(b * 128 + k * 8), pt_desc_mnmajor(va + (unsigned)(k * 2048)),
+                              idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+                pt_commit(pt_smem_u32(&bars.pv_done[b]));
+                pt_commit(pt_smem_u32(&bars.v_empty[b]));
+            }
+            if (!ok) { failed = 1; atomicExch(error, 12); }
+        }
+    } else {
+        // ---------------- softmax and epilogue: a thread owns one row ----------------
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;                       // row of the tile = lane of tensor memory
+        const int tok = r & (toks_per_tile - 1), hi = r >> (7 - share_log2);
+        const int pos = off + t0 + tok;
+        const int lo = window > 0 ? pos + 1 - window : 0;
+        const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
+        float m_used = -INFINITY, l = 0.f;
+        const int warp_min_pos = __reduce_min_sync(0xffffffffu, pos), warp_max_lo = __reduce_max_sync(0xffffffffu, lo);
+        bool ok = true;
+        for (int i = 0; i < ntiles; ++i) {
+            const int b = i & 1;
+            const int key_base = (tile_lo + i) * PT_KEYS;
+            ok = pt_mbar_wait(pt_smem_u32(&bars.s_full[b]), (unsigned)((i >> 1) & 1));
+            if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const unsigned s_addr = tmem_base + (unsigned)(b * 128) + lane_addr;
+            // A tile that every row of the warp sees whole needs no masking at all.
+            const bool whole = key_base + PT_KEYS - 1 <= warp_min_pos && key_base >= warp_max_lo;
+            // pass 1: the row's maximum over the visible keys of this tile
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                unsigned v[32];
+                pt_ld32(s_addr + (unsigned)(c * 32), v);
+                if (whole) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(v[j]));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int key = key_base + c * 32 + j;
+                        if (key <= pos && key >= lo) mx = fmaxf(mx, __uint_as_float(v[j]));
+                    }
+                }
+            }
+            mx *= scale_log2;   // (the scale is positive)
+            // The reference maximum moves only when it has grown by more than the threshold.
+            float alpha = 1.f;
+            bool move = mx > m_used + PT_RESCALE_THRESHOLD;
+            if (move) {
+                alpha = (m_used == -INFINITY) ? 0.f : exp2f(m_used - mx);
+                m_used = mx;
+                l *= alpha;
+            }
+            if (i > 0 && __any_sync(0xffffffffu, move)) {
+                // O of the rows that moved is rescaled; P V of the previous tile must be complete
+                ok = pt_mbar_wait(pt_smem_u32(&bars.pv_done[b ^ 1]), (unsigned)(((i - 1) >> 1) & 1));
+                if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    unsigned v[32];
+                    pt_ld32(tmem_o + lane_addr + (unsigned)(c * 32), v);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
+                    pt_st32(tmem_o + lane_addr + (unsigned)(c * 32), v);
+                }
+            }
+            // pass 2: probabilities, written back over the scores as packed bfloat16
+            float ps = 0.f;
+            const float neg_m = -m_used;   // (-inf only if the row has seen no key yet; then nothing is visible)
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                unsigned v[32], pk[16];
+                pt_ld32(s_addr + (unsigned)(c * 32), v);
+                if (whole) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        const float p0 = pt_ex2(fmaf(__uint_as_float(v[j]), scale_log2, neg_m));
+                        const float p1 = pt_ex2(fmaf(__uint_as_float(v[j + 1]), scale_log2, neg_m));
+                        ps += p0 + p1;
+                        const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                        pk[j >> 1] = *reinterpret_cast<const unsigned*>(&h);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        const int key = key_base + c * 32 + j;
+                        float p0 = 0.f, p1 = 0.f;
+                        if (key <= pos && key >= lo) p0 = pt_ex2(fmaf(__uint_as_float(v[j]), scale_log2, neg_m));
+                        if (key + 1 <= pos && key + 1 >= lo) p1 = pt_ex2(fmaf(__uint_as_float(v[j + 1]), scale_log2, neg_m));
+                        ps += p0 + p1;
+                        const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                        pk[j >> 1] = *reinterpret_cast<const unsigned*>(&h);
+                    }
+                }
+                pt_st16(s_addr + (unsigned)(c * 16), pk);
+            }
+            l += ps;
+            if (key_base + PT_KEYS > kv_hi) {
+                // the tile reaches past the last key: clear those value rows (both halves)
+                ok = pt_mbar_wait(pt_smem_u32(&bars.v_full[b]), (unsigned)((i >> 1) & 1));
+                if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+                unsigned char* vt = v_s + b * PT_TILE_BYTES;
+                const int first = max(kv_hi - key_base, 0);
+                for (int idx = (warp - 2) * 32 + lane; idx < (PT_KEYS - first) * 16; idx += 128) {
+                    const int row = first + (idx >> 4), c16 = idx & 15;
+                    *reinterpret_cast<uint4*>(vt + (c16 >> 3) * PT_HALF_BYTES + row * 128 + (c16 & 7) * 16) =
+                        make_uint4(0, 0, 0, 0);
+                }
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) pt_mbar_arrive(pt_smem_u32(&bars.p_ready[b]));
+        }
+        if (ok) {
+            const int last = ntiles - 1;
+            ok = pt_mbar_wait(pt_smem_u32(&bars.pv_done[last & 1]), (unsigned)((last >> 1) & 1));
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (!ok) {
+            if (lane == 0) { failed = 1; atomicExch(error, 13); }
+        } else {
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const float inv = 1.f / l;
+            const bool live = tok < toks_live;
+            bf16* dst = out + (size_t)(row_base + t0 + tok) * out_row_stride + (size_t)(hk * share + hi) * PT_D;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                unsigned v[32];
+                pt_ld32(tmem_o + lane_addr + (unsigned)(c * 32), v);
+                if (!live) continue;
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                    uint4 pk;
+                    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                    for (int q2 = 0; q2 < 4; ++q2)
+                        h[q2] = __floats2bfloat162_rn(__uint_as_float(v[j + 2 * q2]) * inv,
+                                                      __uint_as_float(v[j + 2 * q2 + 1]) * inv);
+                    *reinterpret_cast<uint4*>(dst + c * 32 + j) = pk;
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+// ---- host side ----
+typedef CUresult (*pt_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static pt_encode_fn pt_encoder() {
+    static pt_encode_fn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (pt_encode_fn)p;
+    }
+    return fn;
+}
+
+// a [rows, cols] bfloat16 matrix with row stride ld (elements), read in boxes of box_rows x 64
+static bool pt_make_map(CUtensorMap* map, const void* base, long long rows, int cols, long long ld, int box_rows) {
+    pt_encode_fn enc = pt_encoder();
+    if (!enc) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Request i brings the token rows [cu_seqlens[i], cu_seqlens[i+1]) of q (`tokens` rows
+// in all, row stride q_row_stride, query head h at columns h * 128) at positions
+// kv_offsets[i] onward; pools are [pages, Hk, S, 128].  `error`: a device int a block
+// sets if one of its bounded waits runs out.
+extern "C" int vx_paged_prefill_attention_tc(const void* q, int q_row_stride, int tokens, const void* k_pool,
+                                             const void* v_pool, int pages, const int* block_table, int max_blocks,
+                                             const int* cu_seqlens, const int* kv_offsets, void* out,
+                                             int out_row_stride, float scale, int window, int requests, int max_new,
+                                             int H, int Hk, int D, int S, int* error, cudaStream_t stream) {
+    if (requests <= 0 || max_new <= 0 || tokens <= 0) return VX_OK;
+    if (D != PT_D || H <= 0 || Hk <= 0 || H % Hk || S <= 0 || S % 16 || window < 0 || !error) return VX_ERR_SHAPE;
+    const int G = H / Hk;
+    if (G != 1 && G != 2 && G != 4 && G != 8) return VX_ERR_SHAPE;
+    if ((q_row_stride & 7) || (((uintptr_t)q) & 15) || (out_row_stride & 7) || (((uintptr_t)out) & 15) ||
+        ((((uintptr_t)k_pool) | ((uintptr_t)v_pool)) & 15))
+        return VX_ERR_ALIGN;
+    if (Hk > 65535 || requests > 65535) return VX_ERR_LIMIT;
+    int share_log2 = 0;
+    while ((1 << share_log2) < G) ++share_log2;
+    const int toks_per_tile = PT_ROWS >> share_log2;
+    CUtensorMap mq, mk, mv;
+    if (!pt_make_map(&mq, q, tokens, H * D, q_row_stride, toks_per_tile) ||
+        !pt_make_map(&mk, k_pool, (long long)pages * Hk * S, D, D, 16) ||
+        !pt_make_map(&mv, v_pool, (long long)pages * Hk * S, D, D, 16))
+        return VX_ERR_DRIVER;
+    const size_t smem = 5 * (size_t)PT_TILE_BYTES + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(paged_prefill_attention_tc_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid((max_new + toks_per_tile - 1) / toks_per_tile, Hk, requests);
+    VX_LAUNCH_K(VX_K_ATTENTION, paged_prefill_attention_tc_kernel, grid, PT_THREADS, smem, stream, mq, mk, mv,
+                block_table, max_blocks, cu_seqlens, kv_offsets, (bf16*)out, out_row_stride, scale * PT_LOG2E, window, H,
+                Hk, S, share_log2, error);
+    VX_LAUNCH_CHECK();
+    return VX_OK;
+}

@@ -73,6 +73,7 @@ def _declare(lib) -> None:
         "vx_gemm_nt_simt": [P, P, P, P, I, I, I, I, I, I, I, I, P],
         "vx_gemm_tcgen05": [P, P, P, P, I, I, I, I, I, I, I, I, I, P, P],
         "vx_gemm_skinny": [P, P, P, P, I, I, I, I, I, I, I, I, I, P],
+        "vx_paged_prefill_attention_tc": [P, I, I, P, P, I, P, I, P, P, P, I, F, I, I, I, I, I, I, I, P, P],
         "vx_paged_prefill_attention": [P, I, P, P, P, I, P, P, P, I, F, I, I, I, I, I, I, I, P],
         "vx_paged_decode_attention": [P, I, P, P, P, I, P, P, P, P, I, P, I, F, I, I, I, I, I, I, I, P],
         "vx_sample": [P, I, I, I, P, P, P, P, P],
@@ -311,6 +312,30 @@ def paged_prefill_attention(q: torch.Tensor, q_row_stride: int, k_pool, v_pool, 
         _ptr(q), q_row_stride, _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1],
         _ptr(cu_seqlens), _ptr(kv_offsets), _ptr(out), num_heads * head_dim, float(scale), int(window), requests,
         int(max_new), num_heads, num_kv_heads, head_dim, k_pool.shape[2], _stream()), "paged_prefill_attention")
+    return out
+
+
+def prefill_attention_tc_supported(dtype, head_dim: int, page_size: int, group: int) -> bool:
+    return dtype == torch.bfloat16 and head_dim == 128 and page_size % 16 == 0 and group in (1, 2, 4, 8)
+
+
+def paged_prefill_attention_tc(q: torch.Tensor, q_row_stride: int, k_pool, v_pool, block_table: torch.Tensor,
+                               cu_seqlens, kv_offsets, scale: float, window: int, num_heads: int, num_kv_heads: int,
+                               head_dim: int, requests: int, max_new: int, tokens: int) -> torch.Tensor:
+    """The same as `paged_prefill_attention` on the tcgen05 tensor cores (head size
+    128, accumulators in tensor memory, operands by TMA)."""
+    _dev(q, k_pool, v_pool, block_table, cu_seqlens, kv_offsets)
+    _need(q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and v_pool.dtype == torch.bfloat16,
+          "paged_prefill_attention_tc: bfloat16 only")
+    _need(block_table.dtype == torch.int32 and block_table.is_contiguous() and block_table.dim() == 2,
+          "paged_prefill_attention_tc: int32 block table [requests, blocks]")
+    _need(k_pool.is_contiguous() and v_pool.is_contiguous(), "paged_prefill_attention_tc: contiguous pools")
+    out = torch.empty((tokens, num_heads * head_dim), dtype=q.dtype, device=q.device)
+    _check(library().vx_paged_prefill_attention_tc(
+        _ptr(q), q_row_stride, tokens, _ptr(k_pool), _ptr(v_pool), k_pool.shape[0], _ptr(block_table),
+        block_table.shape[1], _ptr(cu_seqlens), _ptr(kv_offsets), _ptr(out), num_heads * head_dim, float(scale),
+        int(window), requests, int(max_new), num_heads, num_kv_heads, head_dim, k_pool.shape[2],
+        _ptr(_error_word(q.device)), _stream()), "paged_prefill_attention_tc")
     return out
 
 

@@ -27,6 +27,9 @@ from .plan import PartSpec
 from .registry import build_part
 
 
+TC_PREFILL_MIN_TOKENS = 32   # longest portion of a step from which the tcgen05 kernel is used
+
+
 class PagedAttention(Mixer):
     cuda_graph_safe = True  # reads nothing of a step but device tensors and sizes fixed per graph
 
@@ -113,6 +116,12 @@ class PagedAttention(Mixer):
             return ops.paged_decode_attention(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
                                               ctx.seq_of_token, ctx.positions, self.scale, self.window, H, Hk, D,
                                               ctx.n_seqs, ctx.max_kv)
+        if ctx.max_new >= TC_PREFILL_MIN_TOKENS and ops.prefill_attention_tc_supported(
+                qkv.dtype, D, cache.k_pool.shape[2], H // Hk):
+            # prompt portions on the tcgen05 tensor cores
+            return ops.paged_prefill_attention_tc(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
+                                                  ctx.cu_seqlens, ctx.kv_offsets, self.scale, self.window, H, Hk, D,
+                                                  ctx.n_seqs, ctx.max_new, qkv.shape[0])
         if ops.prefill_attention_supported(qkv.dtype, D, cache.k_pool.shape[2]):
             return ops.paged_prefill_attention(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
                                                ctx.cu_seqlens, ctx.kv_offsets, self.scale, self.window, H, Hk, D,
