@@ -7,6 +7,7 @@ Configurations of the architecture that differ in every size and option:
   tiny_b      3     96     8    2     32     160   384   1e6    1e-5  untied  yes   20 (layers    8
                                                                                     1 and 2)
   tiny_c      2     128    4    2     64     192   300   5e5    1e-6  untied  no    40 (layer 1)  16
+  tiny_d      2     256    4    2     128    384   320   1e6    1e-6  tied    no    200 (layer 1) 16
 """
 import json
 import os
@@ -38,6 +39,14 @@ TINY = {
                     num_attention_heads=4, head_dim=64, attention_bias=False, num_key_value_heads=2,
                     max_position_embeddings=2048, tie_word_embeddings=False, rope_theta=500000.0,
                     rms_norm_eps=1e-6, hidden_act="silu", use_sliding_window=True, sliding_window=40,
+                    max_window_layers=1)),
+    # head size 128, two query heads per kv head: the sizes the tcgen05 attention kernel takes
+    "tiny_d": dict(
+        seed=3, page_size=16,
+        config=dict(vocab_size=320, hidden_size=256, intermediate_size=384, num_hidden_layers=2,
+                    num_attention_heads=4, head_dim=128, attention_bias=False, num_key_value_heads=2,
+                    max_position_embeddings=4096, tie_word_embeddings=True, rope_theta=1000000.0,
+                    rms_norm_eps=1e-6, hidden_act="silu", use_sliding_window=True, sliding_window=200,
                     max_window_layers=1)),
 }
 

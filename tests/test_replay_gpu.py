@@ -13,7 +13,7 @@ from helpers import TINY, assert_close, random_tokens, run_trace
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"tiny_a": [70, 45, 33, 90, 1, 2, 3, 64], "tiny_b": [81, 40, 57, 96, 1, 2, 3, 48],
-           "tiny_c": [300, 45, 129, 77, 1, 2, 17, 64]}
+           "tiny_c": [300, 45, 129, 77, 1, 2, 17, 64], "tiny_d": [420, 45, 129, 300, 1, 2, 17, 64]}
 
 
 class Trace:
@@ -94,7 +94,7 @@ def build_trace(seqs, plain):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d"])
 def test_replay_every_way_of_cutting(model_folders, tmp_path, name, dtype):
     folder = model_folders[name]
     cfg, w = P.load_model_folder(folder)
@@ -132,3 +132,22 @@ def test_long_decoding(model_folders, tmp_path, dtype):
     got = run_trace(folder, dtype, tr.steps, 448 + 384, str(tmp_path / "out"), page_size=16)
     for n in sorted(tr.expect):
         assert_close(got[n], tr.expect[n], dtype, "long decode step %d" % n)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_long_prompt_in_one_step_and_in_two(model_folders, tmp_path, dtype):
+    """1,100 tokens at once (the step's matrix products and attention take their
+    large-shape kernels), then the same prompt as 1,030 + 70 on top of the cache."""
+    folder = model_folders["tiny_d"]
+    cfg, w = P.load_model_folder(folder)
+    toks = random_tokens(cfg["vocab_size"], 1100, 9)
+    plain = {"whole": P.forward_logits(cfg, w, toks)}
+    plain["cut"] = plain["whole"]
+    want = list(range(0, 1100, 37)) + [1099]
+    tr = Trace()
+    tr.add([("whole", toks, want, 0)], end=["whole"], plain=plain)
+    tr.add([("cut", toks[:1030], [w_ for w_ in want if w_ < 1030], 0)], plain=plain)
+    tr.add([("cut", toks[1030:], [w_ - 1030 for w_ in want if w_ >= 1030], 1030)], end=["cut"], plain=plain)
+    got = run_trace(folder, dtype, tr.steps, 1152, str(tmp_path / "out"), page_size=16)
+    for n in sorted(tr.expect):
+        assert_close(got[n], tr.expect[n], dtype, "long prompt step %d" % n)
