@@ -26,6 +26,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..parts.base import FixedState, PagedKV
@@ -75,6 +76,10 @@ class CacheManager:
         self.groups: List[CacheGroup] = []
         self.slots = SlotAllocator(max_requests)
         self.requests: Dict[object, RequestCache] = {}
+        # Host mirrors for building a step's description without loops: per group the
+        # block table of every slot (-1 where no page is held), and every slot's length.
+        self.table_of_slot: List[np.ndarray] = []
+        self.length_of_slot = np.zeros(max_requests, np.int64)
         self._layers: List[LayerCache] = []
         self._state_layers: List[int] = []
         by_spec: Dict[PagedKV, int] = {}
@@ -87,6 +92,7 @@ class CacheManager:
                     self.groups.append(CacheGroup(spec, [], PageAllocator(num_pages)))
                 layer_group[i] = by_spec[spec]
                 self.groups[by_spec[spec]].layers.append(i)
+        self.table_of_slot = [np.full((max_requests, self.max_blocks), -1, np.int32) for _ in self.groups]
         for g in self.groups:
             if device is not None:
                 shape = (len(g.layers), 2, num_pages, g.spec.num_kv_heads, self.page_size, g.spec.head_dim)
@@ -131,6 +137,9 @@ class CacheManager:
         if slot is None:
             return None
         self.requests[request_id] = RequestCache(slot, 0, [[] for _ in self.groups])
+        self.length_of_slot[slot] = 0
+        for t in self.table_of_slot:
+            t[slot, :] = -1
         for i in self._state_layers:
             st = self._layers[i].state
             if st is not None:
@@ -170,8 +179,11 @@ class CacheManager:
         need = self.pages_needed(request_id, new_tokens)
         if any(n > g.allocator.num_free for n, g in zip(need, self.groups)):
             return False
-        for n, g, table in zip(need, self.groups, rc.tables):
-            table.extend(g.allocator.alloc(n))
+        for n, g, table, mirror in zip(need, self.groups, rc.tables, self.table_of_slot):
+            if n:
+                pages = g.allocator.alloc(n)
+                mirror[rc.slot, len(table):len(table) + n] = pages
+                table.extend(pages)
         return True
 
     def commit(self, request_id, new_tokens: int) -> None:
@@ -179,7 +191,8 @@ class CacheManager:
         pages that every later query's window has passed."""
         rc = self.requests[request_id]
         rc.length += new_tokens
-        for g, table in zip(self.groups, rc.tables):
+        self.length_of_slot[rc.slot] = rc.length
+        for g, table, mirror in zip(self.groups, rc.tables, self.table_of_slot):
             if len(table) * self.page_size < rc.length:
                 raise CacheAccountingError("request %r wrote %d positions into %d pages"
                                            % (request_id, rc.length, len(table)))
@@ -189,6 +202,7 @@ class CacheManager:
                     if table[i] >= 0:
                         g.allocator.free([table[i]])
                         table[i] = -1
+                        mirror[rc.slot, i] = -1
 
     def release(self, request_id) -> None:
         """Gives back everything the request holds."""

@@ -84,24 +84,26 @@ class _Graph:
             self.copied.synchronize()  # the pinned buffer is free once its last copy has run
         n, B, S = len(entries), self.bucket, cache.page_size
         h = self.h
-        h["token_ids"][n:] = 0
-        h["positions"][n:] = 0
-        h["kv_offsets"][n:] = 0
-        h["state_slots"][n:] = 0
-        for bt, sm in self.h_groups:
-            sm[n:] = -1
-            bt[n:, :] = 0
-        for i, e in enumerate(entries):
-            rc = cache.requests[e.request_id]
-            pos = rc.length
-            h["token_ids"][i] = e.tokens[0]
-            h["positions"][i] = pos
-            h["kv_offsets"][i] = pos
-            h["state_slots"][i] = rc.slot
-            for (bt, sm), table in zip(self.h_groups, rc.tables):
-                k = len(table)
-                bt[i, :k] = table
-                sm[i] = table[pos // S] * S + pos % S
+        slots = np.fromiter((cache.requests[e.request_id].slot for e in entries), np.int64, n)
+        pos = cache.length_of_slot[slots]
+        h["token_ids"][:n] = [e.tokens[0] for e in entries]
+        h["positions"][:n] = pos
+        h["kv_offsets"][:n] = pos
+        h["state_slots"][:n] = slots
+        if n < B:
+            h["token_ids"][n:] = 0
+            h["positions"][n:] = 0
+            h["kv_offsets"][n:] = 0
+            h["state_slots"][n:] = 0
+        cols = min(cache.max_blocks, int(pos.max()) // S + 1)   # pages any of these requests can reach
+        rows = np.arange(n)
+        for (bt, sm), mirror in zip(self.h_groups, cache.table_of_slot):
+            tables = mirror[slots, :cols]
+            bt[:n, :cols] = tables
+            sm[:n] = tables[rows, pos // S] * S + pos % S
+            if n < B:
+                sm[n:] = -1
+                bt[n:, :cols] = 0
         if sampling is None:
             self.h_temp[:] = 0.0
         else:

@@ -55,6 +55,19 @@ class Request:
     def tokens(self) -> List[int]:
         return self.prompt + self.generated
 
+    @property
+    def num_tokens(self) -> int:
+        return len(self.prompt) + len(self.generated)
+
+    def token_slice(self, start: int, stop: int) -> List[int]:
+        """tokens[start:stop] without building the whole list."""
+        n = len(self.prompt)
+        if stop <= n:
+            return self.prompt[start:stop]
+        if start >= n:
+            return self.generated[start - n:stop - n]
+        return self.prompt[start:] + self.generated[:stop - n]
+
 
 @dataclass
 class SchedulerStats:
@@ -204,7 +217,7 @@ class Scheduler:
             r = self.waiting[0]
             if self.cache.add_request(r.request_id) is None:
                 break
-            k = self._fit(r.request_id, min(len(r.tokens), budget, self._portion_cap()))
+            k = self._fit(r.request_id, min(r.num_tokens, budget, self._portion_cap()))
             if k <= 0:
                 self.cache.release(r.request_id)
                 if not self.running:  # nothing will ever free a page for it
@@ -225,8 +238,8 @@ class Scheduler:
         for rid in sorted(chosen):
             r = self.running[rid]
             done = self.cache.length(rid)
-            toks = r.tokens[done:done + chosen[rid]]
-            last = done + chosen[rid] == len(r.tokens)
+            toks = r.token_slice(done, done + chosen[rid])
+            last = done + chosen[rid] == r.num_tokens
             entries.append(StepEntry(rid, toks, [len(toks) - 1] if last else []))
         return entries
 
