@@ -27,9 +27,10 @@ import numpy as np
 # ----------------------------------------------------------------------------
 # files
 # ----------------------------------------------------------------------------
-def load_model_folder(folder):
+def load_model_folder(folder, dtype="float64"):
     """(config dict, {name: float64 array}) of a folder with config.json and
-    model.safetensors.  bfloat16 is widened exactly through its bit pattern."""
+    model.safetensors.  bfloat16 is widened exactly through its bit pattern.
+    `dtype="float32"` holds the arrays in 32-bit, for models of many gigabytes."""
     from safetensors import safe_open
 
     with open(os.path.join(folder, "config.json")) as f:
@@ -39,7 +40,7 @@ def load_model_folder(folder):
 
     with safe_open(os.path.join(folder, "model.safetensors"), framework="pt") as f:
         for name in f.keys():
-            weights[name] = f.get_tensor(name).to(torch.float64).numpy()
+            weights[name] = f.get_tensor(name).to(getattr(torch, dtype)).numpy()
     return config, weights
 
 
@@ -129,13 +130,28 @@ def silu(z):
     return z / (1.0 + np.exp(-z))
 
 
-def gated_mlp(x, w_gate, w_up, w_down):
+def keep(x):
+    """Activations held as computed (the default `store`)."""
+    return x
+
+
+def store_bfloat16(x):
+    """x rounded to bfloat16 (nearest, ties to even) and widened again: what is
+    left of an activation that a bfloat16 model holds between two operations,
+    as the reference does with its bfloat16 weights and activations
+    (src/paged/qwen3.rs:226-239: the matmul's output takes the input's dtype)."""
+    b = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    b = (b + np.uint32(0x7FFF) + ((b >> np.uint32(16)) & np.uint32(1))) & np.uint32(0xFFFF0000)
+    return b.view(np.float32).astype(np.asarray(x).dtype)
+
+
+def gated_mlp(x, w_gate, w_up, w_down, store=keep):
     """down(act(gate(x)) * up(x)), never biased (src/paged/qwen3.rs:324-326,
     333-339)."""
-    return linear(silu(linear(x, w_gate)) * linear(x, w_up), w_down)
+    return store(linear(store(silu(linear(x, w_gate)) * linear(x, w_up)), w_down))
 
 
-def attention_block(x, positions, w, prefix, cfg, window):
+def attention_block(x, positions, w, prefix, cfg, window, store=keep):
     """q/k/v projections, per-head RMSNorm of q and k before the rotation, the
     rotation, attention, output projection (src/paged/qwen3.rs:428-448,
     506-544).  The output projection's input width is H*D, not the hidden size
@@ -144,15 +160,15 @@ def attention_block(x, positions, w, prefix, cfg, window):
     h, hk, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
     eps = cfg["rms_norm_eps"]
     bias = (lambda n: w[prefix + n + ".bias"]) if cfg["attention_bias"] else (lambda n: None)
-    q = linear(x, w[prefix + "q_proj.weight"], bias("q_proj")).reshape(t, h, d)
-    k = linear(x, w[prefix + "k_proj.weight"], bias("k_proj")).reshape(t, hk, d)
-    v = linear(x, w[prefix + "v_proj.weight"], bias("v_proj")).reshape(t, hk, d)
+    q = store(linear(x, w[prefix + "q_proj.weight"], bias("q_proj"))).reshape(t, h, d)
+    k = store(linear(x, w[prefix + "k_proj.weight"], bias("k_proj"))).reshape(t, hk, d)
+    v = store(linear(x, w[prefix + "v_proj.weight"], bias("v_proj"))).reshape(t, hk, d)
     q = rms_norm(q, w[prefix + "q_norm.weight"], eps)
     k = rms_norm(k, w[prefix + "k_norm.weight"], eps)
-    q = rope(q, positions, cfg["rope_theta"])
-    k = rope(k, positions, cfg["rope_theta"])
-    a = causal_attention(q, k, v, window).reshape(t, h * d)
-    return linear(a, w[prefix + "o_proj.weight"], bias("o_proj"))
+    q = store(rope(q, positions, cfg["rope_theta"]))
+    k = store(rope(k, positions, cfg["rope_theta"]))
+    a = store(causal_attention(q, k, v, window)).reshape(t, h * d)
+    return store(linear(a, w[prefix + "o_proj.weight"], bias("o_proj")))
 
 
 def layer_window(cfg, layer):
@@ -168,29 +184,35 @@ def layer_window(cfg, layer):
     return w if layer >= cfg.get("max_window_layers", 0) else 0
 
 
-def decoder_layer(x, positions, w, layer, cfg):
-    """Pre-norm residual block (src/paged/qwen3.rs:932-939)."""
+def decoder_layer(x, positions, w, layer, cfg, store=keep):
+    """Pre-norm residual block (src/paged/qwen3.rs:932-939).  `store` is applied
+    to what a model would hold between operations; the residual sum is not."""
     p = "model.layers.%d." % layer
     eps = cfg["rms_norm_eps"]
-    h = rms_norm(x, w[p + "input_layernorm.weight"], eps)
-    x = x + attention_block(h, positions, w, p + "self_attn.", cfg, layer_window(cfg, layer))
-    h = rms_norm(x, w[p + "post_attention_layernorm.weight"], eps)
+    h = store(rms_norm(x, w[p + "input_layernorm.weight"], eps))
+    x = x + attention_block(h, positions, w, p + "self_attn.", cfg, layer_window(cfg, layer), store)
+    h = store(rms_norm(x, w[p + "post_attention_layernorm.weight"], eps))
     x = x + gated_mlp(
-        h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"]
+        h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"], store
     )
     return x
 
 
-def forward_logits(cfg, w, ids, dtype=np.float64):
-    """Logits [T, V] at every position of one whole sequence
-    (src/paged/qwen3.rs:1019-1036: embed, the layers, final norm, output head;
-    the head is the embedding table when `tie_word_embeddings`, :966-976)."""
-    w = {k: v.astype(dtype) for k, v in w.items()}
+def forward_logits(cfg, w, ids, dtype=np.float64, store=keep, rows=None):
+    """Logits [T, V] at every position of one whole sequence (at `rows` only,
+    if given) (src/paged/qwen3.rs:1019-1036: embed, the layers, final norm,
+    output head; the head is the embedding table when `tie_word_embeddings`,
+    :966-976).  With `store=store_bfloat16` every activation between two
+    operations is rounded to bfloat16, the residual sum and the logits are not:
+    the distance of that result from the exact one is what bfloat16 costs."""
+    w = {k: v.astype(dtype, copy=False) for k, v in w.items()}
     positions = np.arange(len(ids))
     x = embedding(ids, w["model.embed_tokens.weight"])
     for layer in range(cfg["num_hidden_layers"]):
-        x = decoder_layer(x, positions, w, layer, cfg)
-    x = rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"])
+        x = decoder_layer(x, positions, w, layer, cfg, store)
+    if rows is not None:
+        x = x[np.asarray(rows, dtype=np.int64)]
+    x = store(rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"]))
     head = w["model.embed_tokens.weight"] if cfg["tie_word_embeddings"] else w["lm_head.weight"]
     return linear(x, head)
 

@@ -97,3 +97,12 @@ def test_sampling():
     assert P.sample_from(p, 0.0) == 0 and P.sample_from(p, 0.999999) == 4
     c = np.cumsum(p)
     assert P.sample_from(p, float(c[1] - 1e-9)) == 1 and P.sample_from(p, float(c[1] + 1e-9)) == 2
+
+
+def test_store_bfloat16_rounds_to_nearest_even():
+    import torch
+    x = np.random.default_rng(5).standard_normal(4096).astype(np.float32) * 3
+    x[:4] = [1.0, 1.00390625, 1.01171875, -0.0]   # exact; a tie that goes down to even; a tie that goes up
+    want = torch.from_numpy(x).to(torch.bfloat16).to(torch.float32).numpy()
+    assert (P.store_bfloat16(x) == want).all()
+    assert P.store_bfloat16(x.astype(np.float64)).dtype == np.float64
