@@ -5,7 +5,7 @@
 // 16-row side of a tensor-core tile (mma.sync.m16n8k16, bf16 in, float32 out) and
 // the few rows of x sit on the 8-column side.  A block owns 16 rows of W (or,
 // with a gated epilogue, 8 gate rows and their 8 up rows) and the whole of K; its
-// 8 warps take the 32-wide k chunks in turn (chunk c goes to warp c mod 8), each
+// warps take the 32-wide k chunks in turn (chunk c goes to warp c mod the number of warps), each
 // thread loading 16 contiguous bytes of two W rows per chunk straight from global
 // memory into registers, four chunks in flight, with no shared memory on the way:
 // every byte of W is used exactly once.  The first chunks are asked for before the
@@ -23,8 +23,9 @@
 // epilogue); 16-byte aligned rows.
 #include "common.cuh"
 
-#define SK_WARPS 8
-#define SK_UNROLL 4
+// Warps per block and chunks a warp keeps in flight are template parameters: a
+// matrix of few rows gives few blocks, and then each block must keep more bytes
+// on their way to fill the memory pipe (see pick_variant).
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
     uint4 v;
@@ -39,8 +40,8 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], unsigned a0, unsig
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <bool GATED, typename TOut>
-__global__ void __launch_bounds__(SK_WARPS * 32, 4)
+template <bool GATED, typename TOut, int SK_WARPS, int SK_UNROLL, int MIN_BLOCKS>
+__global__ void __launch_bounds__(SK_WARPS * 32, MIN_BLOCKS)
 gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, const float* __restrict__ bias,
                    TOut* __restrict__ out, int M, int N, int K, int ldx, int ldw, int ldo, int act) {
     __shared__ float red[SK_WARPS][16][9];
@@ -130,20 +131,57 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, const
     }
 }
 
+// Variants (warps, chunks in flight per warp, blocks per SM the registers allow):
+//   1: 8, 4, 4   many blocks: four per SM keep the pipe full
+//   2: 16, 4, 2  fewer blocks than 4 per SM: twice the warps on each tile
+//   3: 8, 8, 2
+//   4: 16, 8, 1
+//   5: 16, 2, 4
+// Measured on a B200 (M = 8, microseconds, variants 1/2/3): 4096x4096 9.5/8.0/8.5;
+// 4096x12288 22.2/18.4/18.8; 6144x4096 11.3/12.8/13.2; 24576x4096 35.8/37.5/36.2;
+// 151936x4096 202/194/185.  The wider variants hold two blocks per SM, so they
+// only pay while all blocks fit at once or when there are very many.
+static int pick_variant(int N, int K) {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+        sms = n;
+    }
+    const int blocks = (N + 15) / 16;
+    if (blocks <= 2 * sms) return 2;
+    if (blocks >= 16 * sms) return 3;
+    return 1;
+}
+
 template <bool GATED, typename TOut>
 static int launch_skinny(const bf16* x, const bf16* W, const float* bias, TOut* out, int M, int N, int K, int ldx,
-                         int ldw, int ldo, int act, cudaStream_t stream) {
+                         int ldw, int ldo, int act, int variant, cudaStream_t stream) {
     const int blocks = (N + 15) / 16;
-    VX_LAUNCH_K(VX_K_GEMM, (gemm_skinny_kernel<GATED, TOut>), blocks, SK_WARPS * 32, 0, stream, x, W, bias, out, M, N, K, ldx,
-              ldw, ldo, act);
+    if (variant == 0) variant = pick_variant(N, K);
+#define SK_GO(WARPS, UNROLL, MINB)                                                                                  \
+    VX_LAUNCH_K(VX_K_GEMM, (gemm_skinny_kernel<GATED, TOut, WARPS, UNROLL, MINB>), blocks, WARPS * 32, 0, stream, x, W, \
+                bias, out, M, N, K, ldx, ldw, ldo, act)
+    switch (variant) {
+        case 1: SK_GO(8, 4, 4); break;
+        case 2: SK_GO(16, 4, 2); break;
+        case 3: SK_GO(8, 8, 2); break;
+        case 4: SK_GO(16, 8, 1); break;
+        case 5: SK_GO(16, 2, 4); break;
+        default: return VX_ERR_SHAPE;
+    }
+#undef SK_GO
     VX_LAUNCH_CHECK();
     return VX_OK;
 }
 
 // gated: 0 plain; 1: W rows come in tiles of 16 = 8 gate rows then their 8 up
 // rows, and out is [M, N/2] = act(gate) * up.  out_dtype: VX_BF16 or VX_F32.
+// variant: 0 lets the sizes choose (pick_variant); 1..5 name one, for tuning.
 extern "C" int vx_gemm_skinny(const void* x, const void* W, const float* bias, void* out, int M, int N, int K,
-                              int ldx, int ldw, int ldo, int gated, int act, int out_dtype,
+                              int ldx, int ldw, int ldo, int gated, int act, int out_dtype, int variant,
                               cudaStream_t stream) {
     if (M <= 0 || N <= 0) return VX_OK;
     if (M > 8 || K <= 0 || (K & 31)) return VX_ERR_SHAPE;
@@ -153,7 +191,7 @@ extern "C" int vx_gemm_skinny(const void* x, const void* W, const float* bias, v
     if (ldo < (gated ? N / 2 : N)) return VX_ERR_SHAPE;
     const bf16* xp = (const bf16*)x;
     const bf16* wp = (const bf16*)W;
-#define SK_CALL(G, T) launch_skinny<G, T>(xp, wp, bias, (T*)out, M, N, K, ldx, ldw, ldo, act, stream)
+#define SK_CALL(G, T) launch_skinny<G, T>(xp, wp, bias, (T*)out, M, N, K, ldx, ldw, ldo, act, variant, stream)
     if (out_dtype == VX_BF16) return gated ? SK_CALL(true, bf16) : SK_CALL(false, bf16);
     if (out_dtype == VX_F32) return gated ? SK_CALL(true, float) : SK_CALL(false, float);
 #undef SK_CALL

@@ -72,7 +72,7 @@ def _declare(lib) -> None:
         "vx_paged_attention_generic": [P, I, P, P, P, I, P, P, P, I, F, I, I, I, I, I, I, I, P],
         "vx_gemm_nt_simt": [P, P, P, P, I, I, I, I, I, I, I, I, P],
         "vx_gemm_tcgen05": [P, P, P, P, I, I, I, I, I, I, I, I, I, P, P],
-        "vx_gemm_skinny": [P, P, P, P, I, I, I, I, I, I, I, I, I, P],
+        "vx_gemm_skinny": [P, P, P, P, I, I, I, I, I, I, I, I, I, I, P],
         "vx_paged_prefill_attention_tc": [P, I, I, P, P, I, P, I, P, P, P, I, F, I, I, I, I, I, I, I, P, P],
         "vx_paged_prefill_attention": [P, I, P, P, P, I, P, P, P, I, F, I, I, I, I, I, I, I, P],
         "vx_paged_decode_attention": [P, I, P, P, P, I, P, P, P, P, I, P, I, F, I, I, I, I, I, I, I, P],
@@ -417,7 +417,7 @@ def skinny_supported(m: int, k: int, a: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias=None, out_dtype: Optional[torch.dtype] = None,
-                gated_activation: Optional[str] = None) -> torch.Tensor:
+                gated_activation: Optional[str] = None, variant: int = 0) -> torch.Tensor:
     """a [M<=8, K] times w [N,K] transposed, W streamed once (bfloat16).  With
     `gated_activation`, w's rows come in tiles of 8 gate rows followed by their 8 up
     rows and the result is act(gate) * up, [M, N/2]."""
@@ -433,7 +433,7 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias=None, out_dtype: Optional
     out = torch.empty((m, cols), dtype=out_dtype, device=a.device)
     _check(library().vx_gemm_skinny(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), m, n, k, a.stride(0), w.stride(0), cols,
                                     1 if gated_activation else 0, ACTIVATIONS.get(gated_activation, 0),
-                                    dtype_code(out_dtype), _stream()), "gemm_skinny")
+                                    dtype_code(out_dtype), variant, _stream()), "gemm_skinny")
     return out
 
 
