@@ -42,7 +42,6 @@ paged_decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, cons
                               bf16* __restrict__ out, int out_row_stride, float scale_log2, int window,
                               int H, int Hk, int S, int piece_tiles) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    pdl_trigger();
     constexpr int TILE_BYTES = 16 * D * 2;
     constexpr int CHUNKS_PER_ROW = D / 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -67,6 +66,7 @@ paged_decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, cons
 
     unsigned char* my_smem = smem_raw + (size_t)warp * DEC_STAGES * 2 * TILE_BYTES;
     pdl_wait();
+    pdl_trigger();
 
     auto issue = [&](int j) {
         const int key0 = (tile_begin + j) << 4;
@@ -240,15 +240,15 @@ __global__ void paged_decode_join_kernel(const float* __restrict__ part_o, const
                                          int max_pieces, const int* __restrict__ token_rows,
                                          const int* __restrict__ positions, bf16* __restrict__ out,
                                          int out_row_stride, int window, int H, int piece_tiles) {
-    pdl_trigger();
     const int b = blockIdx.x, h = blockIdx.y;
     const int row_tok = token_rows ? token_rows[b] : b;
     const int kv_len = positions[row_tok] + 1;
     const int start = (window > 0 && kv_len > window) ? kv_len - window : 0;
     const int ntiles = ((kv_len + 15) >> 4) - (start >> 4);
     const int npieces = (ntiles + piece_tiles - 1) / piece_tiles;
+    pdl_wait();  // on every path: a grid that ends without waiting would let its successor run ahead of its predecessor
+    pdl_trigger();
     if (npieces <= 1) return;  // written by the first pass
-    pdl_wait();
     const size_t p0 = ((size_t)b * H + h) * max_pieces;
     float M = -INFINITY;
     for (int s = 0; s < npieces; ++s) M = fmaxf(M, part_ml[(p0 + s) * 2]);

@@ -26,8 +26,8 @@ __global__ void paged_attention_generic_kernel(
     const T* __restrict__ v_pool, const int* __restrict__ block_table, int max_blocks,
     const int* __restrict__ seq_of_token, const int* __restrict__ positions, T* __restrict__ out,
     int out_row_stride, float scale, int window, int H, int Hk, int D, int S) {
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     __shared__ float q_s[ATT_MAX_D];
     __shared__ float acc_s[ATT_WARPS][ATT_MAX_D];
     __shared__ float m_s[ATT_WARPS], l_s[ATT_WARPS];

@@ -38,8 +38,8 @@ paged_prefill_attention_kernel(const bf16* __restrict__ q, int q_row_stride, con
     extern __shared__ __align__(128) unsigned char pf_smem[];
     constexpr int CHUNKS_PER_ROW = D / 8;
     constexpr int TILE_BYTES = PF_BN * D * 2;
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // the longest tiles (the last tokens of a prompt) are handed out first
     const int qt = gridDim.x - 1 - blockIdx.x, seq = blockIdx.z;

@@ -160,8 +160,8 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
     unsigned char* q_s = smem;                                   // 32 KB
     unsigned char* k_s = smem + PT_TILE_BYTES;                   // 2 x 32 KB
     unsigned char* v_s = smem + 3 * PT_TILE_BYTES;               // 2 x 32 KB
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // the longest tiles (the last tokens of a prompt) are handed out first
     const int qt = gridDim.x - 1 - blockIdx.x, hk = blockIdx.y, seq = blockIdx.z;

@@ -28,14 +28,22 @@
 
 typedef __nv_bfloat16 bf16;
 
-// Programmatic dependent launch (off unless vx_set_pdl(1)).  With it, kernels of
-// this library are launched so that the next kernel in the stream may become
-// resident while the previous one is still running.  A kernel first calls pdl_trigger() (its dependents may be
-// launched), does whatever needs nothing of earlier kernels (loading weights),
-// and calls pdl_wait() before it reads anything an earlier kernel wrote and
-// before it writes anything at all; pdl_wait() returns when all earlier work in
-// the stream is complete and visible.  Launched without the attribute (or after a
-// kernel of another library) both calls do nothing and the order is the stream's.
+// Programmatic dependent launch (on unless vx_set_pdl(0)).  With it, the next
+// kernel in the stream may become resident while this one is still running, so
+// that its launch and its prologue (for the matrix products: the first loads of
+// weights, which depend on nothing) overlap this kernel's work.  The rules every
+// kernel here keeps:
+//   - pdl_wait() before it reads anything an earlier kernel wrote and before it
+//     writes anything at all; it returns when all earlier work in the stream is
+//     complete and visible.  At least one block of every launch reaches it: a grid
+//     that ended without waiting would let its successor run ahead of its
+//     predecessor.
+//   - pdl_trigger() (dependents may be launched) only AFTER pdl_wait().  So at most
+//     one successor is resident beside the running kernel.  Triggering first let
+//     the whole chain of later kernels pile up on the SMs, and a decode step ran
+//     18 % slower.
+// Launched without the attribute (or after a kernel of another library) both
+// calls do nothing and the order is the stream's.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

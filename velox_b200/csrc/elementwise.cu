@@ -12,8 +12,8 @@
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ out, int hidden, int vocab) {
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * hidden;
@@ -49,8 +49,8 @@ __global__ void add_rmsnorm_kernel(const float* __restrict__ residual_in, const 
                                    const int* __restrict__ row_index, float* __restrict__ residual_out,
                                    const float* __restrict__ weight, T* __restrict__ out, int width,
                                    float eps) {
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     __shared__ float scratch[32];
     const int r = blockIdx.x;
     const int s = row_index ? row_index[r] : r;
@@ -115,8 +115,8 @@ add_rmsnorm_vec_kernel(const float* __restrict__ residual_in, const T* __restric
                        const int* __restrict__ row_index, float* __restrict__ residual_out,
                        const float* __restrict__ weight, T* __restrict__ out, int width, float eps) {
     __shared__ float scratch[32];
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     const int r = blockIdx.x;
     const int s = row_index ? row_index[r] : r;
     const float* xin = residual_in + (size_t)s * width;
@@ -202,8 +202,8 @@ extern "C" int vx_add_rmsnorm(const float* residual_in, const void* delta, const
 template <typename T>
 __global__ void rmsnorm_kernel(const T* __restrict__ x, const float* __restrict__ weight,
                                T* __restrict__ out, int width, float eps) {
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     __shared__ float scratch[32];
     const T* xin = x + (size_t)blockIdx.x * width;
     T* o = out + (size_t)blockIdx.x * width;
@@ -240,8 +240,8 @@ extern "C" int vx_rmsnorm(const void* x, const float* weight, void* out, int row
 template <typename T>
 __global__ void gated_act_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long total,
                                  int inner, int act, int block) {
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x) {
         const long long t = idx / inner;
@@ -259,8 +259,8 @@ __global__ void gated_act_kernel(const T* __restrict__ gate_up, T* __restrict__ 
 template <typename T>
 __global__ void gated_act_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long chunks,
                                      int inner, int act, int block) {
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     const int per_row = inner >> 3;
     for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < chunks;
          idx += (long long)gridDim.x * blockDim.x) {

@@ -15,8 +15,8 @@ template <typename TA, typename TC>
 __global__ void __launch_bounds__(256)
 gemm_nt_simt_kernel(const TA* __restrict__ A, const TA* __restrict__ W, const float* __restrict__ bias,
                     TC* __restrict__ C, int M, int N, int K, int lda, int ldw, int ldc) {
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     __shared__ float As[GS_BK][GS_BM + 1];
     __shared__ float Ws[GS_BK][GS_BN + 1];
     const int tid = threadIdx.x;

@@ -45,7 +45,6 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MIN_BLOCKS)
 gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, const float* __restrict__ bias,
                    TOut* __restrict__ out, int M, int N, int K, int ldx, int ldw, int ldo, int act) {
     __shared__ float red[SK_WARPS][16][9];
-    pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int row0 = blockIdx.x * 16;
@@ -72,6 +71,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, const
         loaded = true;
     }
     pdl_wait();
+    pdl_trigger();
     for (; c + (SK_UNROLL - 1) * SK_WARPS < nchunks; c += SK_UNROLL * SK_WARPS) {
         if (!loaded) {
 #pragma unroll

@@ -44,8 +44,8 @@ def library():
         except OSError as e:
             raise KernelError("the kernel library %s could not be loaded: %s" % (path, e))
         _declare(_LIB)
-        if os.environ.get("VELOX_B200_PDL", "0") == "1":
-            _LIB.vx_set_pdl(1)
+        if os.environ.get("VELOX_B200_PDL", "1") == "0":
+            _LIB.vx_set_pdl(0)
         if os.environ.get("VELOX_B200_PDL_MASK"):
             _LIB.vx_set_pdl_mask(int(os.environ["VELOX_B200_PDL_MASK"], 0))
     return _LIB
@@ -53,7 +53,7 @@ def library():
 
 def set_pdl(enabled: bool) -> None:
     """Programmatic dependent launch on or off for kernels launched from now on
-    (off by default; VELOX_B200_PDL=1 in the environment starts with it on)."""
+    (on by default; VELOX_B200_PDL=0 in the environment starts with it off)."""
     library().vx_set_pdl(1 if enabled else 0)
 
 

@@ -27,8 +27,8 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, int row_stride,
                                        const int* __restrict__ positions,
                                        const int* __restrict__ slot_mapping, T* __restrict__ k_pool,
                                        T* __restrict__ v_pool, int H, int Hk, int D, int S) {
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
@@ -91,8 +91,8 @@ qk_norm_rope_kv_128_kernel(bf16* __restrict__ qkv, int row_stride, const float* 
                            const float* __restrict__ k_weight, float eps, const float* __restrict__ inv_freq,
                            const int* __restrict__ positions, const int* __restrict__ slot_mapping,
                            bf16* __restrict__ k_pool, bf16* __restrict__ v_pool, int H, int Hk, int S) {
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     constexpr int D = 128;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;

@@ -54,8 +54,8 @@ __device__ __forceinline__ int block_min_int(int v, int* si) {
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __restrict__ temperature,
               const float* __restrict__ top_p, const float* __restrict__ uniform, int* __restrict__ out) {
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     __shared__ float sv[32];
     __shared__ int si[32];
     __shared__ float scan[SAMPLE_THREADS];
