@@ -43,15 +43,30 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], unsigned a0, unsig
 template <bool GATED, typename TOut, int SK_WARPS, int SK_UNROLL, int MIN_BLOCKS>
 __global__ void __launch_bounds__(SK_WARPS * 32, MIN_BLOCKS)
 gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, const float* __restrict__ bias,
-                   TOut* __restrict__ out, int M, int N, int K, int ldx, int ldw, int ldo, int act) {
+                   TOut* __restrict__ out, int M, int N, int K, int ldx, int ldw, int ldo, int act, int R) {
     __shared__ float red[SK_WARPS][16][9];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int row0 = blockIdx.x * 16;
-    // rows of W this thread loads (clamped at the matrix' edge; the result is not stored there)
-    const int ra = min(row0 + g, N - 1), rb = min(row0 + g + 8, N - 1);
-    const bf16* wa = W + (size_t)ra * ldw + t * 8;
-    const bf16* wb = W + (size_t)rb * ldw + t * 8;
+    // A block owns R <= 16 rows of W (gated: R <= 8 output features, each a gate row
+    // and the up row 8 below it in its 16-row tile); rows of the tile beyond R are
+    // not loaded.  R is chosen so that the blocks fill whole waves of the GPU.
+    const int row0 = blockIdx.x * R;
+    int ra, rb;
+    bool va, vb;
+    if (!GATED) {
+        ra = row0 + g;
+        rb = row0 + g + 8;
+        va = g < R && ra < N;
+        vb = g + 8 < R && rb < N;
+    } else {
+        const int f = row0 + g;  // output feature
+        ra = ((f >> 3) << 4) + (f & 7);
+        rb = ra + 8;
+        va = vb = g < R && rb < N;
+    }
+    const bf16* wa = W + (size_t)(va ? ra : 0) * ldw + t * 8;
+    const bf16* wb = W + (size_t)(vb ? rb : 0) * ldw + t * 8;
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
     // row of x this thread loads: column g of the 8-column tile
     const bool xok = g < M;
     const bf16* xr = x + (size_t)min(g, M - 1) * ldx + t * 8;
@@ -65,8 +80,8 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, const
 #pragma unroll
         for (int u = 0; u < SK_UNROLL; ++u) {
             const int k = (c + u * SK_WARPS) << 5;
-            a[u] = ld_stream16(wa + k);
-            b[u] = ld_stream16(wb + k);
+            a[u] = va ? ld_stream16(wa + k) : zero4;
+            b[u] = vb ? ld_stream16(wb + k) : zero4;
         }
         loaded = true;
     }
@@ -77,8 +92,8 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, const
 #pragma unroll
             for (int u = 0; u < SK_UNROLL; ++u) {
                 const int k = (c + u * SK_WARPS) << 5;
-                a[u] = ld_stream16(wa + k);
-                b[u] = ld_stream16(wb + k);
+                a[u] = va ? ld_stream16(wa + k) : zero4;
+                b[u] = vb ? ld_stream16(wb + k) : zero4;
             }
         }
         loaded = false;
@@ -94,7 +109,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, const
     }
     for (; c < nchunks; c += SK_WARPS) {
         const int k = c << 5;
-        const uint4 ta = ld_stream16(wa + k), tb = ld_stream16(wb + k);
+        const uint4 ta = va ? ld_stream16(wa + k) : zero4, tb = vb ? ld_stream16(wb + k) : zero4;
         const uint4 xv = xok ? *reinterpret_cast<const uint4*>(xr + k) : make_uint4(0, 0, 0, 0);
         mma_bf16_16816(acc, ta.x, tb.x, ta.y, tb.y, xv.x, xv.y);
         mma_bf16_16816(acc, ta.z, tb.z, ta.w, tb.w, xv.z, xv.w);
@@ -109,7 +124,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, const
         if (threadIdx.x < 16 * 8) {
             const int r = threadIdx.x & 15, m = threadIdx.x >> 4;  // consecutive threads -> consecutive output columns
             const int nrow = row0 + r;
-            if (m < M && nrow < N) {
+            if (m < M && r < R && nrow < N) {
                 float v = 0.f;
 #pragma unroll
                 for (int w = 0; w < SK_WARPS; ++w) v += red[w][r][m];
@@ -120,8 +135,8 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, const
     } else {
         if (threadIdx.x < 8 * 8) {
             const int r = threadIdx.x & 7, m = threadIdx.x >> 3;
-            const int col = blockIdx.x * 8 + r;  // output feature
-            if (m < M && col * 2 < N) {
+            const int col = row0 + r;  // output feature
+            if (m < M && r < R && col * 2 < N) {
                 float gate = 0.f, up = 0.f;
 #pragma unroll
                 for (int w = 0; w < SK_WARPS; ++w) { gate += red[w][r][m]; up += red[w][r + 8][m]; }
@@ -137,11 +152,15 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, const
 //   3: 8, 8, 2
 //   4: 16, 8, 1
 //   5: 16, 2, 4
-// Measured on a B200 (M = 8, microseconds, variants 1/2/3): 4096x4096 9.5/8.0/8.5;
-// 4096x12288 22.2/18.4/18.8; 6144x4096 11.3/12.8/13.2; 24576x4096 35.8/37.5/36.2;
-// 151936x4096 202/194/185.  The wider variants hold two blocks per SM, so they
-// only pay while all blocks fit at once or when there are very many.
-static int pick_variant(int N, int K) {
+//   6: 8, 8, 3
+//   7: 4, 8, 4
+// Measured on a B200 (M = 8, microseconds, back to back under programmatic
+// launch, variants 1/2/3/7): 4096x4096 9.2/7.4/7.0/7.6; 4096x12288 24/19/16.8/18.7;
+// 6144x4096 11.4/11.4/10.3/9.6; 24576x4096 gated 44/45/33.6/35.4; 151936x4096
+// 218/204/178/200; 5120x5120 12.1/13.7/13.7/9.8; 5120x17408 37/40/34/30;
+// 10240x5120 23/23/22/19.  Variant 1 fills the register file, which keeps the
+// next kernel's blocks out until it ends.
+static int sm_count() {
     static int sms = 0;
     if (sms == 0) {
         int dev = 0, n = 0;
@@ -150,26 +169,46 @@ static int pick_variant(int N, int K) {
             n = 148;
         sms = n;
     }
-    const int blocks = (N + 15) / 16;
-    if (blocks <= 2 * sms) return 2;
-    if (blocks >= 16 * sms) return 3;
-    return 1;
+    return sms;
+}
+
+static int pick_variant(int N, int K) {
+    const int sms = sm_count();
+    const int tiles = (N + 15) / 16;
+    if (tiles <= 2 * sms || tiles >= 8 * sms) return 3;
+    return 7;
 }
 
 template <bool GATED, typename TOut>
 static int launch_skinny(const bf16* x, const bf16* W, const float* bias, TOut* out, int M, int N, int K, int ldx,
                          int ldw, int ldo, int act, int variant, cudaStream_t stream) {
-    const int blocks = (N + 15) / 16;
+    const bool balance = variant < 100;  // variant + 100: whole tiles per block, for comparison
+    if (variant >= 100) variant -= 100;
     if (variant == 0) variant = pick_variant(N, K);
+    // Rows (gated: features) per block: the most a tile holds, lowered until the
+    // blocks fill whole waves (slots = SMs x blocks per SM of the variant).
+    const int units = GATED ? N / 2 : N, tile = GATED ? 8 : 16;
+    int R = tile;
+    if (variant >= 1 && variant <= 7 && balance) {
+        static const int per_sm[8] = {0, 4, 2, 2, 1, 4, 3, 4};
+        const long long slots = (long long)sm_count() * per_sm[variant];
+        const long long tiles = (units + tile - 1) / tile;
+        const long long waves = (tiles + slots - 1) / slots;
+        R = (int)((units + waves * slots - 1) / (waves * slots));
+        R = R < 1 ? 1 : (R > tile ? tile : R);
+    }
+    const int blocks = (units + R - 1) / R;
 #define SK_GO(WARPS, UNROLL, MINB)                                                                                  \
     VX_LAUNCH_K(VX_K_GEMM, (gemm_skinny_kernel<GATED, TOut, WARPS, UNROLL, MINB>), blocks, WARPS * 32, 0, stream, x, W, \
-                bias, out, M, N, K, ldx, ldw, ldo, act)
+                bias, out, M, N, K, ldx, ldw, ldo, act, R)
     switch (variant) {
         case 1: SK_GO(8, 4, 4); break;
         case 2: SK_GO(16, 4, 2); break;
         case 3: SK_GO(8, 8, 2); break;
         case 4: SK_GO(16, 8, 1); break;
         case 5: SK_GO(16, 2, 4); break;
+        case 6: SK_GO(8, 8, 3); break;
+        case 7: SK_GO(4, 8, 4); break;
         default: return VX_ERR_SHAPE;
     }
 #undef SK_GO
