@@ -235,6 +235,7 @@ paged_decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, cons
 
 // Joins the pieces of requests that have several: one block per (request, head),
 // pieces added in piece order.
+#define JOIN_MAX_PIECES 1024
 template <int D>
 __global__ void paged_decode_join_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          int max_pieces, const int* __restrict__ token_rows,
@@ -250,17 +251,41 @@ __global__ void paged_decode_join_kernel(const float* __restrict__ part_o, const
     pdl_trigger();
     if (npieces <= 1) return;  // written by the first pass
     const size_t p0 = ((size_t)b * H + h) * max_pieces;
-    float M = -INFINITY;
-    for (int s = 0; s < npieces; ++s) M = fmaxf(M, part_ml[(p0 + s) * 2]);
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float L = 0.f, O = 0.f;
-        for (int s = 0; s < npieces; ++s) {
+    // weights of the pieces, once per block: w_s = 2^(m_s - M), and L = sum w_s l_s
+    // in piece order (so the result does not depend on the number of threads)
+    __shared__ float wgt[JOIN_MAX_PIECES];
+    __shared__ float inv_l;
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        float M = -INFINITY;
+        for (int s = lane; s < npieces; s += 32) M = fmaxf(M, part_ml[(p0 + s) * 2]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        for (int s = lane; s < npieces; s += 32) {
             const float ms = part_ml[(p0 + s) * 2];
-            const float wgt = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
-            L += wgt * part_ml[(p0 + s) * 2 + 1];
-            O += wgt * part_o[(p0 + s) * D + d];
+            wgt[s] = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
         }
-        out[(size_t)row_tok * out_row_stride + (size_t)h * D + d] = __float2bfloat16_rn(O / L);
+        __syncwarp();
+        if (lane == 0) {
+            float L = 0.f;
+            for (int s = 0; s < npieces; ++s) L += wgt[s] * part_ml[(p0 + s) * 2 + 1];
+            inv_l = 1.f / L;
+        }
+    }
+    __syncthreads();
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        const float* po = part_o + p0 * D + d;
+        float O = 0.f;
+        int s = 0;
+        for (; s + 8 <= npieces; s += 8) {  // eight independent loads at a time, added in piece order
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = po[(size_t)(s + u) * D];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) O += wgt[s + u] * v[u];
+        }
+        for (; s < npieces; ++s) O += wgt[s] * po[(size_t)s * D];
+        out[(size_t)row_tok * out_row_stride + (size_t)h * D + d] = __float2bfloat16_rn(O * inv_l);
     }
 }
 
@@ -315,7 +340,7 @@ extern "C" int vx_paged_decode_attention(const void* q, int q_row_stride, const 
     if (requests <= 0) return VX_OK;
     if (H <= 0 || Hk <= 0 || H % Hk || H / Hk > 16 || S <= 0 || S % 16 || window < 0) return VX_ERR_SHAPE;
     if (piece_tiles <= 0 || piece_tiles > 32 || max_pieces <= 0 || (max_pieces > 1 && !scratch)) return VX_ERR_SHAPE;
-    if (Hk > 65535 || requests > 65535) return VX_ERR_LIMIT;
+    if (Hk > 65535 || requests > 65535 || max_pieces > JOIN_MAX_PIECES) return VX_ERR_LIMIT;
     if ((q_row_stride & 1) || (((uintptr_t)q) & 3) || (out_row_stride & 1) || (((uintptr_t)out) & 3)) return VX_ERR_ALIGN;
     if (D == 128)
         return launch_decode<128>((const bf16*)q, q_row_stride, (const bf16*)k_pool, (const bf16*)v_pool,
