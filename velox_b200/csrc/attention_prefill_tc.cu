@@ -7,25 +7,30 @@
 // query heads of one kv head (G in {1, 2, 4, 8}), so the heads of a group share
 // every key/value tile.  It walks over the request's keys in tiles of 128.
 //
-//   warp 0      producer: loads the query tile once and then, tile by tile, the keys
-//               and the values page by page with tiled TMA loads (128-byte swizzle),
-//               one 16-key x 64-column box per lane, into two shared-memory buffers
-//               each;
+//   warps 0, 10-12  producers: warp 0 loads the query tile once; then, tile by tile,
+//               warps 0 and 10 load the keys and warps 11 and 12 the values, page by
+//               page with tiled TMA loads (128-byte swizzle), one 16-key x 64-column
+//               box per lane (eight lanes a warp), into two shared-memory buffers each;
 //   warp 1      tensor core: one thread issues S = Q K^T (128 x 128, 8 instructions
 //               of K 16) into one of two score buffers in tensor memory, and, when
 //               the softmax warps have turned a score buffer into probabilities,
 //               O += P V (A operand straight from tensor memory, V as the
 //               MN-major B operand).  S of tile i + 1 is issued before P V of tile i,
 //               so the tensor core works while the softmax of tile i runs;
-//   warps 2-5   softmax: a thread owns one query row (one lane of tensor memory):
-//               it reads the row's 128 scores, scales, masks by select (causal: key
-//               <= the row's position; window: key >= position + 1 - W), keeps the
-//               running maximum and sum in float32 (base 2), writes the
-//               probabilities back over the scores as packed bfloat16, and rescales
-//               the row of O only when the maximum has grown by more than 2^8 (the
-//               probabilities are then bounded by 256 instead of 1, which float32
-//               and bfloat16 hold without loss of accuracy).  At the end the same
-//               warps divide O by the sum and store it.
+//   warps 2-9   softmax: two threads own one query row (one lane of tensor memory),
+//               warps 2-5 its keys 0-63 of the tile, warps 6-9 its keys 64-127.  A
+//               thread reads its 64 scores, masks by select (causal: key <= the
+//               row's position; window: key >= position + 1 - W), exchanges the
+//               maximum with its partner through shared memory (one named barrier a
+//               tile), keeps the running maximum and its half of the sum in float32
+//               (base 2), writes the probabilities back over the scores as packed
+//               bfloat16, and rescales its half of the row of O only when the
+//               maximum has grown by more than 2^8 (the probabilities are then
+//               bounded by 256 instead of 1, which float32 and bfloat16 hold
+//               without loss of accuracy).  At the end the same warps add the two
+//               half sums, divide O by the sum and store it.  The softmax, not the
+//               tensor core, sets the pace of this kernel: with one thread per row
+//               a tile took about 4,300 cycles against 1,024 of tensor-core work.
 //
 // Keys past the request's last key and below its window are masked; the values of a
 // tile that reaches past the last key are cleared in shared memory first, because a
@@ -41,7 +46,8 @@
 #define PT_ROWS 128
 #define PT_KEYS 128
 #define PT_D 128
-#define PT_THREADS 192
+#define PT_THREADS 416
+#define PT_SOFTMAX_THREADS 256
 #define PT_SPIN_LIMIT (1 << 24)
 #define PT_LOG2E 1.4426950408889634f
 #define PT_HALF_BYTES (128 * 128)   // 128 rows x 64 columns of bf16: one swizzled half of a tile
@@ -106,7 +112,7 @@ __device__ __forceinline__ float pt_ex2(float x) {
 __device__ __forceinline__ void pt_commit(unsigned bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void pt_ld32(unsigned taddr, unsigned (&r)[32]) {
+__device__ __forceinline__ void pt_ld32_issue(unsigned taddr, unsigned (&r)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -116,7 +122,11 @@ __device__ __forceinline__ void pt_ld32(unsigned taddr, unsigned (&r)[32]) {
           "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void pt_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void pt_ld32(unsigned taddr, unsigned (&r)[32]) {
+    pt_ld32_issue(taddr, r);
+    pt_wait_ld();
 }
 __device__ __forceinline__ void pt_st32(unsigned taddr, const unsigned (&r)[32]) {
     asm volatile(
@@ -138,6 +148,15 @@ __device__ __forceinline__ void pt_st16(unsigned taddr, const unsigned (&r)[16])
         : "memory");
 }
 
+// Named barrier 1 over the softmax threads, with the AND of `ok` returned to all.
+__device__ __forceinline__ bool pt_softmax_barrier_and(bool ok) {
+    unsigned all;
+    asm volatile(
+        "{\n .reg .pred p, q;\n setp.ne.u32 p, %1, 0;\n barrier.red.and.pred q, 1, %2, p;\n selp.u32 %0, 1, 0, q;\n}\n"
+        : "=r"(all) : "r"((unsigned)ok), "n"(PT_SOFTMAX_THREADS) : "memory");
+    return all != 0;
+}
+
 // barriers of a block
 struct PtBarriers {
     unsigned long long q_full;
@@ -156,6 +175,8 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
     __shared__ __align__(8) PtBarriers bars;
     __shared__ unsigned tmem_base_s;
     __shared__ int failed;
+    __shared__ float row_max[2][2][PT_ROWS];   // [tile parity][half of the keys][row]: the halves' maxima
+    __shared__ float row_sum[2][PT_ROWS];      // [half of the keys][row]: the halves' sums, at the end
     unsigned char* smem = (unsigned char*)(((uintptr_t)pt_smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* q_s = smem;                                   // 32 KB
     unsigned char* k_s = smem + PT_TILE_BYTES;                   // 2 x 32 KB
@@ -187,7 +208,7 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
             pt_mbar_init(pt_smem_u32(&bars.v_full[i]), 1);
             pt_mbar_init(pt_smem_u32(&bars.v_empty[i]), 1);
             pt_mbar_init(pt_smem_u32(&bars.s_full[i]), 1);
-            pt_mbar_init(pt_smem_u32(&bars.p_ready[i]), 4);   // one arrival per softmax warp
+            pt_mbar_init(pt_smem_u32(&bars.p_ready[i]), 8);   // one arrival per softmax warp
             pt_mbar_init(pt_smem_u32(&bars.pv_done[i]), 1);
         }
         failed = 0;
@@ -204,46 +225,56 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
     const unsigned tmem_base = tmem_base_s;
     const unsigned tmem_o = tmem_base + 256;
 
-    if (warp == 0) {
-        // ---------------- producer: the whole warp, one box per lane ----------------
-        // queries: for each shared head, its tokens' two 64-column halves
-        if (lane == 0) pt_mbar_expect_tx(pt_smem_u32(&bars.q_full), PT_TILE_BYTES);
-        __syncwarp();
-        if (lane < 2 * share) {
-            const int hi = lane >> 1, half = lane & 1;
-            pt_tma_load_2d(pt_smem_u32(q_s + half * PT_HALF_BYTES + hi * toks_per_tile * 128), &map_q,
-                           (hk * share + hi) * PT_D + half * 64, row_base + t0, pt_smem_u32(&bars.q_full));
+    if (warp == 0 || warp >= 10) {
+        // ---------------- producers: warps 0 and 10 the keys, 11 and 12 the values ----------------
+        // A tiled TMA load takes some 70 cycles to issue, and a tile of keys and values is 32
+        // boxes of 16 keys x 64 columns (a page holds 16 keys), so the boxes are spread over four
+        // warps of eight lanes; keys and values wait for their own buffers (a key buffer is free
+        // as soon as its scores are formed, long before the value buffer of the same tile).
+        const int pw = warp == 0 ? 0 : warp - 9;            // 0..3
+        const int which = pw >> 1, part = pw & 1;           // keys / values; groups 0-3 / 4-7 of the tile
+        if (pw == 0) {
+            // queries: for each shared head, its tokens' two 64-column halves
+            if (lane == 0) pt_mbar_expect_tx(pt_smem_u32(&bars.q_full), PT_TILE_BYTES);
+            __syncwarp();
+            if (lane < 2 * share) {
+                const int hi = lane >> 1, half = lane & 1;
+                pt_tma_load_2d(pt_smem_u32(q_s + half * PT_HALF_BYTES + hi * toks_per_tile * 128), &map_q,
+                               (hk * share + hi) * PT_D + half * 64, row_base + t0, pt_smem_u32(&bars.q_full));
+            }
         }
-        // keys (lanes 0-15) and values (lanes 16-31) of a tile: 8 groups of 16 keys x 2 halves each
-        const int which = lane >> 4, g = (lane & 15) >> 1, half = lane & 1;
+        const int g = part * 4 + ((lane & 7) >> 1), half = lane & 1;
         const CUtensorMap* map = which ? &map_v : &map_k;
         for (int i = 0; i < ntiles; ++i) {
             const int b = i & 1;
             const int key_base = (tile_lo + i) * PT_KEYS;
-            bool ok = true;
-            if (lane == 0) {
-                if (i >= 2)
-                    ok = pt_mbar_wait(pt_smem_u32(&bars.k_empty[b]), (unsigned)(((i >> 1) - 1) & 1)) &&
-                         pt_mbar_wait(pt_smem_u32(&bars.v_empty[b]), (unsigned)(((i >> 1) - 1) & 1));
-                if (ok) {
-                    pt_mbar_expect_tx(pt_smem_u32(&bars.k_full[b]), PT_TILE_BYTES);
-                    pt_mbar_expect_tx(pt_smem_u32(&bars.v_full[b]), PT_TILE_BYTES);
-                } else {
-                    failed = 1;
-                    atomicExch(error, 11);
-                }
-            }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) break;
             // Groups of 16 keys outside [kv_lo, kv_hi) repeat the nearest group inside: they
             // are masked anyway, and their pages may not be this request's.
             int key = key_base + g * 16;
             key = max(min(key, (kv_hi - 1) & ~15), kv_lo & ~15);
-            const int page = bt[key / S];
-            const int y = (page * Hk + hk) * S + (key % S);
-            unsigned char* dst = (which ? v_s : k_s) + b * PT_TILE_BYTES;
-            pt_tma_load_2d(pt_smem_u32(dst + half * PT_HALF_BYTES + g * 16 * 128), map, half * 64, y,
-                           pt_smem_u32(which ? &bars.v_full[b] : &bars.k_full[b]));
+            const int page = bt[key / S];   // (asked for before the wait below)
+            const unsigned full = pt_smem_u32(which ? &bars.v_full[b] : &bars.k_full[b]);
+            bool ok = true;
+            if (lane == 0) {
+                if (i >= 2)
+                    ok = pt_mbar_wait(pt_smem_u32(which ? &bars.v_empty[b] : &bars.k_empty[b]),
+                                      (unsigned)(((i >> 1) - 1) & 1));
+                if (!ok) {
+                    failed = 1;
+                    atomicExch(error, 11);
+                } else if (part == 0) {
+                    // (the other warp's boxes may land before this is posted: the barrier's phase
+                    // cannot end before this arrival)
+                    pt_mbar_expect_tx(full, PT_TILE_BYTES);
+                }
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            if (lane < 8) {
+                const int y = (page * Hk + hk) * S + (key % S);
+                unsigned char* dst = (which ? v_s : k_s) + b * PT_TILE_BYTES;
+                pt_tma_load_2d(pt_smem_u32(dst + half * PT_HALF_BYTES + g * 16 * 128), map, half * 64, y, full);
+            }
         }
     } else if (warp == 1) {
         // ---------------- tensor core ----------------
@@ -296,8 +327,10 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
             if (!ok) { failed = 1; atomicExch(error, 12); }
         }
     } else {
-        // ---------------- softmax and epilogue: a thread owns one row ----------------
-        const int quarter = warp & 3;
+        // ---------------- softmax and epilogue: two threads own one row ----------------
+        const int sw = warp - 2;                                 // 0..7
+        const int quarter = warp & 3;                            // the warp's quarter of tensor memory's lanes
+        const int hc = sw >> 2;                                  // which 64 keys of a tile, which 64 columns of O
         const int r = quarter * 32 + lane;                       // row of the tile = lane of tensor memory
         const int tok = r & (toks_per_tile - 1), hi = r >> (7 - share_log2);
         const int pos = off + t0 + tok;
@@ -305,34 +338,49 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
         const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
         float m_used = -INFINITY, l = 0.f;
         const int warp_min_pos = __reduce_min_sync(0xffffffffu, pos), warp_max_lo = __reduce_max_sync(0xffffffffu, lo);
+        // All 256 threads pass the same named barriers in the same order whatever
+        // happens: a thread whose bounded wait ran out skips its work, and the
+        // barrier's AND tells everybody to stop at the same place.
         bool ok = true;
-        for (int i = 0; i < ntiles; ++i) {
+        int i = 0;
+        for (; i < ntiles; ++i) {
             const int b = i & 1;
-            const int key_base = (tile_lo + i) * PT_KEYS;
-            ok = pt_mbar_wait(pt_smem_u32(&bars.s_full[b]), (unsigned)((i >> 1) & 1));
-            if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const int key_base = (tile_lo + i) * PT_KEYS + hc * 64;   // of this thread's 64 keys
+            if (ok) ok = pt_mbar_wait(pt_smem_u32(&bars.s_full[b]), (unsigned)((i >> 1) & 1));
+            ok = __all_sync(0xffffffffu, ok);
             const unsigned s_addr = tmem_base + (unsigned)(b * 128) + lane_addr;
-            // A tile that every row of the warp sees whole needs no masking at all.
-            const bool whole = key_base + PT_KEYS - 1 <= warp_min_pos && key_base >= warp_max_lo;
-            // pass 1: the row's maximum over the visible keys of this tile
+            // A stretch of keys that every row of the warp sees whole needs no masking at all.
+            const bool whole = key_base + 63 <= warp_min_pos && key_base >= warp_max_lo;
+            unsigned v[2][32];
             float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                unsigned v[32];
-                pt_ld32(s_addr + (unsigned)(c * 32), v);
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                // the 64 scores are read once and stay in registers for both passes
+                pt_ld32_issue(s_addr + (unsigned)(hc * 64), v[0]);
+                pt_ld32_issue(s_addr + (unsigned)(hc * 64 + 32), v[1]);
+                pt_wait_ld();
+                // pass 1: the maximum over the visible keys
                 if (whole) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(v[j]));
+                    for (int c = 0; c < 2; ++c) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(v[c][j]));
+                    }
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int key = key_base + c * 32 + j;
-                        if (key <= pos && key >= lo) mx = fmaxf(mx, __uint_as_float(v[j]));
+                    for (int c = 0; c < 2; ++c) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const int key = key_base + c * 32 + j;
+                            if (key <= pos && key >= lo) mx = fmaxf(mx, __uint_as_float(v[c][j]));
+                        }
                     }
                 }
             }
-            mx *= scale_log2;   // (the scale is positive)
+            row_max[b][hc][r] = mx;
+            // (also orders every thread's reads of the scores before anybody's writes of probabilities)
+            if (!pt_softmax_barrier_and(ok)) { ok = false; break; }
+            mx = fmaxf(mx, row_max[b][hc ^ 1][r]) * scale_log2;   // (the scale is positive)
             // The reference maximum moves only when it has grown by more than the threshold.
             float alpha = 1.f;
             bool move = mx > m_used + PT_RESCALE_THRESHOLD;
@@ -342,84 +390,94 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
                 l *= alpha;
             }
             if (i > 0 && __any_sync(0xffffffffu, move)) {
-                // O of the rows that moved is rescaled; P V of the previous tile must be complete
+                // this half of O is rescaled in the rows that moved; P V of the previous tile must be complete
                 ok = pt_mbar_wait(pt_smem_u32(&bars.pv_done[b ^ 1]), (unsigned)(((i - 1) >> 1) & 1));
-                if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                ok = __all_sync(0xffffffffu, ok);
+                if (ok) {
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 #pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    unsigned v[32];
-                    pt_ld32(tmem_o + lane_addr + (unsigned)(c * 32), v);
+                    for (int c = 0; c < 2; ++c) {
+                        unsigned acc[32];
+                        pt_ld32(tmem_o + lane_addr + (unsigned)(hc * 64 + c * 32), acc);
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
-                    pt_st32(tmem_o + lane_addr + (unsigned)(c * 32), v);
-                }
-            }
-            // pass 2: probabilities, written back over the scores as packed bfloat16
-            float ps = 0.f;
-            const float neg_m = -m_used;   // (-inf only if the row has seen no key yet; then nothing is visible)
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                unsigned v[32], pk[16];
-                pt_ld32(s_addr + (unsigned)(c * 32), v);
-                if (whole) {
-#pragma unroll
-                    for (int j = 0; j < 32; j += 2) {
-                        const float p0 = pt_ex2(fmaf(__uint_as_float(v[j]), scale_log2, neg_m));
-                        const float p1 = pt_ex2(fmaf(__uint_as_float(v[j + 1]), scale_log2, neg_m));
-                        ps += p0 + p1;
-                        const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                        pk[j >> 1] = *reinterpret_cast<const unsigned*>(&h);
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; j += 2) {
-                        const int key = key_base + c * 32 + j;
-                        float p0 = 0.f, p1 = 0.f;
-                        if (key <= pos && key >= lo) p0 = pt_ex2(fmaf(__uint_as_float(v[j]), scale_log2, neg_m));
-                        if (key + 1 <= pos && key + 1 >= lo) p1 = pt_ex2(fmaf(__uint_as_float(v[j + 1]), scale_log2, neg_m));
-                        ps += p0 + p1;
-                        const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                        pk[j >> 1] = *reinterpret_cast<const unsigned*>(&h);
+                        for (int j = 0; j < 32; ++j) acc[j] = __float_as_uint(__uint_as_float(acc[j]) * alpha);
+                        pt_st32(tmem_o + lane_addr + (unsigned)(hc * 64 + c * 32), acc);
                     }
                 }
-                pt_st16(s_addr + (unsigned)(c * 16), pk);
             }
-            l += ps;
-            if (key_base + PT_KEYS > kv_hi) {
+            if (ok) {
+                // pass 2: probabilities, written back over the scores as packed bfloat16
+                float ps = 0.f;
+                const float neg_m = -m_used;   // (-inf only if the row has seen no key yet; then nothing is visible)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    unsigned pk[16];
+                    if (whole) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 2) {
+                            const float p0 = pt_ex2(fmaf(__uint_as_float(v[c][j]), scale_log2, neg_m));
+                            const float p1 = pt_ex2(fmaf(__uint_as_float(v[c][j + 1]), scale_log2, neg_m));
+                            ps += p0 + p1;
+                            const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                            pk[j >> 1] = *reinterpret_cast<const unsigned*>(&h);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 2) {
+                            const int key = key_base + c * 32 + j;
+                            float p0 = 0.f, p1 = 0.f;
+                            if (key <= pos && key >= lo) p0 = pt_ex2(fmaf(__uint_as_float(v[c][j]), scale_log2, neg_m));
+                            if (key + 1 <= pos && key + 1 >= lo) p1 = pt_ex2(fmaf(__uint_as_float(v[c][j + 1]), scale_log2, neg_m));
+                            ps += p0 + p1;
+                            const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                            pk[j >> 1] = *reinterpret_cast<const unsigned*>(&h);
+                        }
+                    }
+                    pt_st16(s_addr + (unsigned)(hc * 32 + c * 16), pk);
+                }
+                l += ps;
+            }
+            if (ok && (tile_lo + i + 1) * PT_KEYS > kv_hi) {
                 // the tile reaches past the last key: clear those value rows (both halves)
                 ok = pt_mbar_wait(pt_smem_u32(&bars.v_full[b]), (unsigned)((i >> 1) & 1));
-                if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-                unsigned char* vt = v_s + b * PT_TILE_BYTES;
-                const int first = max(kv_hi - key_base, 0);
-                for (int idx = (warp - 2) * 32 + lane; idx < (PT_KEYS - first) * 16; idx += 128) {
-                    const int row = first + (idx >> 4), c16 = idx & 15;
-                    *reinterpret_cast<uint4*>(vt + (c16 >> 3) * PT_HALF_BYTES + row * 128 + (c16 & 7) * 16) =
-                        make_uint4(0, 0, 0, 0);
+                ok = __all_sync(0xffffffffu, ok);
+                if (ok) {
+                    unsigned char* vt = v_s + b * PT_TILE_BYTES;
+                    const int first = max(kv_hi - (tile_lo + i) * PT_KEYS, 0);
+                    for (int idx = sw * 32 + lane; idx < (PT_KEYS - first) * 16; idx += PT_SOFTMAX_THREADS) {
+                        const int row = first + (idx >> 4), c16 = idx & 15;
+                        *reinterpret_cast<uint4*>(vt + (c16 >> 3) * PT_HALF_BYTES + row * 128 + (c16 & 7) * 16) =
+                            make_uint4(0, 0, 0, 0);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
                 }
-                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             }
-            asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
-            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-            __syncwarp();
-            if (lane == 0) pt_mbar_arrive(pt_smem_u32(&bars.p_ready[b]));
+            if (ok) {
+                asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+                __syncwarp();
+                if (lane == 0) pt_mbar_arrive(pt_smem_u32(&bars.p_ready[b]));
+            }
         }
-        if (ok) {
+        if (ok && ntiles > 0) {
             const int last = ntiles - 1;
             ok = pt_mbar_wait(pt_smem_u32(&bars.pv_done[last & 1]), (unsigned)((last >> 1) & 1));
             ok = __all_sync(0xffffffffu, ok);
         }
-        if (!ok) {
-            if (lane == 0) { failed = 1; atomicExch(error, 13); }
+        // the two halves of a row's sum meet here (every thread arrives, failed or not)
+        row_sum[hc][r] = l;
+        const bool all_ok = pt_softmax_barrier_and(ok);
+        if (!all_ok) {
+            if (!ok && lane == 0) { failed = 1; atomicExch(error, 13); }
         } else {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            const float inv = 1.f / l;
+            const float inv = 1.f / (row_sum[0][r] + row_sum[1][r]);
             const bool live = tok < toks_live;
-            bf16* dst = out + (size_t)(row_base + t0 + tok) * out_row_stride + (size_t)(hk * share + hi) * PT_D;
+            bf16* dst = out + (size_t)(row_base + t0 + tok) * out_row_stride + (size_t)(hk * share + hi) * PT_D + hc * 64;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                unsigned v[32];
-                pt_ld32(tmem_o + lane_addr + (unsigned)(c * 32), v);
+            for (int c = 0; c < 2; ++c) {
+                unsigned acc[32];
+                pt_ld32(tmem_o + lane_addr + (unsigned)(hc * 64 + c * 32), acc);
                 if (!live) continue;
 #pragma unroll
                 for (int j = 0; j < 32; j += 8) {
@@ -427,8 +485,8 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
                     __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
 #pragma unroll
                     for (int q2 = 0; q2 < 4; ++q2)
-                        h[q2] = __floats2bfloat162_rn(__uint_as_float(v[j + 2 * q2]) * inv,
-                                                      __uint_as_float(v[j + 2 * q2 + 1]) * inv);
+                        h[q2] = __floats2bfloat162_rn(__uint_as_float(acc[j + 2 * q2]) * inv,
+                                                      __uint_as_float(acc[j + 2 * q2 + 1]) * inv);
                     *reinterpret_cast<uint4*>(dst + c * 32 + j) = pk;
                 }
             }
