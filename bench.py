@@ -180,7 +180,7 @@ def main() -> int:
             engine.step()
         e2e_ms = timed(engine.step, steps)
         assert len(engine.scheduler.running) == batch
-        entries = [StepEntry(r.request_id, [r.generated[-1]], [0]) for r in engine.scheduler.running.values()]
+        entries = [StepEntry(r.request_id, [r.last_token], [0]) for r in engine.scheduler.running.values()]
         zeros, ones = [0.0] * batch, [1.0] * batch
         held = sum(engine.cache.length(r) for r in engine.scheduler.running) / batch
 

@@ -19,16 +19,23 @@ Layers whose mixers ask for `FixedState` get one tensor [slots, *shape] each;
 a request holds one slot id from admission to its end, in every such layer.
 Qwen3 has no such layer; the slot is assigned all the same.
 
-The bookkeeping is host-only and runs without a device (`device=None`).
+The bookkeeping is host-only and runs without a device (`device=None`).  It is
+kept by the host library (`csrc/host/cache_book.hpp`): pools, block tables, slots
+and lengths live there, where the scheduler and the step builders read them
+directly; this class owns the device storage and answers questions about the
+books.
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, Iterator, List, Mapping, Optional, Sequence
 
 import numpy as np
 import torch
 
+from .. import native
+from ..native import OutOfPages  # noqa: F401  (part of this module's interface)
 from ..parts.base import FixedState, PagedKV
 from .pages import CacheAccountingError, PageAllocator, SlotAllocator
 
@@ -58,13 +65,39 @@ class CacheGroup:
 
 @dataclass
 class RequestCache:
+    """A request's books as they were when it was looked up."""
     slot: int
     length: int = 0  # positions whose keys/values (or state) are in the cache
     tables: List[List[int]] = field(default_factory=list)  # per group
 
 
-class OutOfPages(RuntimeError):
-    pass
+class _Requests(Mapping):
+    """`manager.requests`: request id -> `RequestCache` (a copy made at the lookup)."""
+
+    def __init__(self, manager: "CacheManager"):
+        self._m = manager
+
+    def __getitem__(self, request_id) -> RequestCache:
+        m = self._m
+        h = m._handle(request_id, create=False)
+        if h is None or not m._lib.vxh_cache_has(m._book, h):
+            raise KeyError(request_id)
+        tables = []
+        buf = (ctypes.c_int * m.max_blocks)()
+        for g in range(len(m.groups)):
+            n = native.check(m._lib.vxh_cache_table(m._book, h, g, buf, m.max_blocks))
+            tables.append(list(buf[:n]))
+        return RequestCache(m._lib.vxh_cache_slot(m._book, h), int(m._lib.vxh_cache_length(m._book, h)), tables)
+
+    def __iter__(self) -> Iterator:
+        m = self._m
+        n = m._lib.vxh_cache_num_requests(m._book)
+        ids = (ctypes.c_int64 * max(n, 1))()
+        m._lib.vxh_cache_request_ids(m._book, ids, n)
+        return iter([m._names.get(h, h) for h in ids[:n]])
+
+    def __len__(self) -> int:
+        return int(self._m._lib.vxh_cache_num_requests(self._m._book))
 
 
 class CacheManager:
@@ -74,25 +107,46 @@ class CacheManager:
         self.page_size, self.max_blocks = int(page_size), int(max_blocks)
         self.dtype, self.device = dtype, device
         self.groups: List[CacheGroup] = []
-        self.slots = SlotAllocator(max_requests)
-        self.requests: Dict[object, RequestCache] = {}
-        # Host mirrors for building a step's description without loops: per group the
-        # block table of every slot (-1 where no page is held), and every slot's length.
-        self.table_of_slot: List[np.ndarray] = []
-        self.length_of_slot = np.zeros(max_requests, np.int64)
         self._layers: List[LayerCache] = []
         self._state_layers: List[int] = []
         by_spec: Dict[PagedKV, int] = {}
         n_layers = len(cache_specs)
         layer_group = [-1] * n_layers
+        specs_of_groups: List[PagedKV] = []
+        layers_of_groups: List[List[int]] = []
         for i, spec in enumerate(cache_specs):
             if isinstance(spec, PagedKV):
                 if spec not in by_spec:
-                    by_spec[spec] = len(self.groups)
-                    self.groups.append(CacheGroup(spec, [], PageAllocator(num_pages)))
+                    by_spec[spec] = len(specs_of_groups)
+                    specs_of_groups.append(spec)
+                    layers_of_groups.append([])
                 layer_group[i] = by_spec[spec]
-                self.groups[by_spec[spec]].layers.append(i)
-        self.table_of_slot = [np.full((max_requests, self.max_blocks), -1, np.int32) for _ in self.groups]
+                layers_of_groups[by_spec[spec]].append(i)
+        # the books: pools, block tables, slots and lengths live in the host library
+        self._lib = native.library()
+        if num_pages <= 0:
+            raise ValueError("a page pool needs at least one page")
+        windows = native.int_array([s.window for s in specs_of_groups])
+        self._book = ctypes.c_void_p(self._lib.vxh_cache_create(len(specs_of_groups), windows, self.page_size,
+                                                                int(num_pages), int(max_requests), self.max_blocks))
+        if not self._book:
+            raise ValueError("page size, pages, requests and blocks per request must be positive")
+        self.slots = SlotAllocator(0, _borrowed=self._lib.vxh_cache_slots(self._book))
+        for g, (spec, layers) in enumerate(zip(specs_of_groups, layers_of_groups)):
+            self.groups.append(CacheGroup(spec, layers, PageAllocator(0, _borrowed=self._lib.vxh_cache_pool(self._book, g))))
+        # request ids: non-negative integers are their own handle in the library
+        # (the scheduler's ids are such), anything else gets a negative one
+        self._handles: Dict[object, int] = {}
+        self._names: Dict[int, object] = {}
+        self._next_handle = -1
+        self.requests = _Requests(self)
+        # Views of the library's dense mirrors, for building a step's description
+        # without loops: per group the block table of every slot (-1 where no page is
+        # held), and every slot's length.
+        self.table_of_slot: List[np.ndarray] = [
+            np.ctypeslib.as_array(self._lib.vxh_cache_mirror(self._book, g), shape=(int(max_requests), self.max_blocks))
+            for g in range(len(self.groups))]
+        self.length_of_slot = np.ctypeslib.as_array(self._lib.vxh_cache_lengths(self._book), shape=(int(max_requests),))
         for g in self.groups:
             if device is not None:
                 shape = (len(g.layers), 2, num_pages, g.spec.num_kv_heads, self.page_size, g.spec.head_dim)
@@ -123,6 +177,39 @@ class CacheManager:
                 src = self._layers[j]
                 self._layers[i] = LayerCache(src.group, False, src.k_pool, src.v_pool, src.state)
 
+    def __del__(self):
+        book = getattr(self, "_book", None)
+        if book:
+            self.table_of_slot, self.length_of_slot = [], None  # views into the book
+            self._lib.vxh_cache_destroy(book)
+            self._book = None
+
+    def _handle(self, request_id, create: bool = True) -> Optional[int]:
+        if isinstance(request_id, int) and not isinstance(request_id, bool) and 0 <= request_id < (1 << 62):
+            return request_id
+        h = self._handles.get(request_id)
+        if h is None and create:
+            h = self._handles[request_id] = self._next_handle
+            self._names[h] = request_id
+            self._next_handle -= 1
+        return h
+
+    def _known(self, request_id) -> int:
+        h = self._handle(request_id, create=False)
+        if h is None:
+            raise KeyError(request_id)
+        return h
+
+    def handles(self, request_ids) -> "ctypes.Array":
+        """The library's ids of requests that hold cache, as a C array."""
+        return native.int64_array(self._known(r) for r in request_ids)
+
+    def zero_state(self, slot: int) -> None:
+        for i in self._state_layers:
+            st = self._layers[i].state
+            if st is not None:
+                st[slot].zero_()
+
     # -- what layers see -------------------------------------------------------
     def layer(self, i: int) -> LayerCache:
         return self._layers[i]
@@ -131,85 +218,49 @@ class CacheManager:
     def add_request(self, request_id) -> Optional[int]:
         """Gives the request a state slot (zeroed) and empty block tables; None
         if no slot is free."""
-        if request_id in self.requests:
-            raise CacheAccountingError("request %r already holds cache" % (request_id,))
-        slot = self.slots.alloc()
-        if slot is None:
+        slot = self._lib.vxh_cache_add(self._book, self._handle(request_id))
+        if slot == -1:
             return None
-        self.requests[request_id] = RequestCache(slot, 0, [[] for _ in self.groups])
-        self.length_of_slot[slot] = 0
-        for t in self.table_of_slot:
-            t[slot, :] = -1
-        for i in self._state_layers:
-            st = self._layers[i].state
-            if st is not None:
-                st[slot].zero_()
+        if slot < 0:
+            if slot == native.ERR_ACCOUNTING:
+                raise CacheAccountingError("request %r already holds cache" % (request_id,))
+            native.check(slot)
+        self.zero_state(slot)
         return slot
 
     def has_request(self, request_id) -> bool:
-        return request_id in self.requests
+        h = self._handle(request_id, create=False)
+        return h is not None and bool(self._lib.vxh_cache_has(self._book, h))
 
     def length(self, request_id) -> int:
-        return self.requests[request_id].length
-
-    def _first_needed_page(self, g: CacheGroup, next_position: int) -> int:
-        """Index of the first page that the query at `next_position` can still see."""
-        if g.window <= 0:
-            return 0
-        first_key = max(0, next_position + 1 - g.window)
-        return first_key // self.page_size
+        return int(native.check(self._lib.vxh_cache_length(self._book, self._known(request_id))))
 
     def pages_needed(self, request_id, new_tokens: int) -> List[int]:
         """Per group, the pages `reserve` would have to take for `new_tokens` more positions."""
-        rc = self.requests[request_id]
-        want = -(-(rc.length + new_tokens) // self.page_size)
-        return [max(0, want - len(t)) for t in rc.tables]
+        out = (ctypes.c_int * max(len(self.groups), 1))()
+        native.check(self._lib.vxh_cache_pages_needed(self._book, self._known(request_id), int(new_tokens), out))
+        return list(out[:len(self.groups)])
 
     def can_reserve(self, request_id, new_tokens: int) -> bool:
-        need = self.pages_needed(request_id, new_tokens)
-        return all(n <= g.allocator.num_free for n, g in zip(need, self.groups))
+        return bool(native.check(self._lib.vxh_cache_can_reserve(self._book, self._known(request_id), int(new_tokens))))
 
     def reserve(self, request_id, new_tokens: int) -> bool:
         """Takes, in every group, the pages for positions [length, length + new_tokens);
         all or nothing.  False if some group has too few free pages."""
-        rc = self.requests[request_id]
-        if rc.length + new_tokens > self.max_blocks * self.page_size:
-            raise OutOfPages("request %r would reach %d positions; block tables hold %d"
-                             % (request_id, rc.length + new_tokens, self.max_blocks * self.page_size))
-        need = self.pages_needed(request_id, new_tokens)
-        if any(n > g.allocator.num_free for n, g in zip(need, self.groups)):
-            return False
-        for n, g, table, mirror in zip(need, self.groups, rc.tables, self.table_of_slot):
-            if n:
-                pages = g.allocator.alloc(n)
-                mirror[rc.slot, len(table):len(table) + n] = pages
-                table.extend(pages)
-        return True
+        return bool(native.check(self._lib.vxh_cache_reserve(self._book, self._known(request_id), int(new_tokens))))
 
     def commit(self, request_id, new_tokens: int) -> None:
         """The step has written `new_tokens` positions: advance, and give back
         pages that every later query's window has passed."""
-        rc = self.requests[request_id]
-        rc.length += new_tokens
-        self.length_of_slot[rc.slot] = rc.length
-        for g, table, mirror in zip(self.groups, rc.tables, self.table_of_slot):
-            if len(table) * self.page_size < rc.length:
-                raise CacheAccountingError("request %r wrote %d positions into %d pages"
-                                           % (request_id, rc.length, len(table)))
-            if g.window > 0:
-                keep_from = self._first_needed_page(g, rc.length)
-                for i in range(min(keep_from, len(table))):
-                    if table[i] >= 0:
-                        g.allocator.free([table[i]])
-                        table[i] = -1
-                        mirror[rc.slot, i] = -1
+        native.check(self._lib.vxh_cache_commit(self._book, self._known(request_id), int(new_tokens)))
 
     def release(self, request_id) -> None:
         """Gives back everything the request holds."""
-        rc = self.requests.pop(request_id)
-        for g, table in zip(self.groups, rc.tables):
-            g.allocator.free([p for p in table if p >= 0])
-        self.slots.free(rc.slot)
+        h = self._known(request_id)
+        native.check(self._lib.vxh_cache_release(self._book, h))
+        if h < 0:
+            del self._handles[request_id]
+            del self._names[h]
 
     # -- accounting ---------------------------------------------------------------
     def free_pages(self) -> List[int]:
@@ -218,18 +269,4 @@ class CacheManager:
     def check(self) -> None:
         """Every page is either free or held by exactly as many tables as its
         count says; raises otherwise."""
-        for gi, g in enumerate(self.groups):
-            held: Dict[int, int] = {}
-            for rc in self.requests.values():
-                for p in rc.tables[gi]:
-                    if p >= 0:
-                        held[p] = held.get(p, 0) + 1
-            free = set(g.allocator._free)
-            if len(free) != len(g.allocator._free):
-                raise CacheAccountingError("group %d: a page is on the free list twice" % gi)
-            for p in range(g.allocator.num_pages):
-                rcnt = g.allocator.refcount(p)
-                if (p in free) != (rcnt == 0) or held.get(p, 0) != rcnt:
-                    raise CacheAccountingError(
-                        "group %d page %d: count %d, held by %d tables, %s the free list"
-                        % (gi, p, rcnt, held.get(p, 0), "on" if p in free else "not on"))
+        native.check(self._lib.vxh_cache_check(self._book))

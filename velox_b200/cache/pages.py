@@ -6,89 +6,89 @@ handed out first, `alloc(n)` all or nothing, a count per page that `free`
 lowers and that returns the page to the stack at zero.  Where the reference only
 warns about a bad id or a second free (src/paged/pages.rs:205-212), these raise:
 a page freed twice would be handed to two requests.
+
+The pools themselves live in the host library (`csrc/host/pages.hpp`); these
+classes own one, or look into one that a `CacheManager` owns.
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Iterable, List, Optional
 
-
-class CacheAccountingError(RuntimeError):
-    pass
+from .. import native
+from ..native import CacheAccountingError  # noqa: F401  (part of this module's interface)
 
 
 class PageAllocator:
-    def __init__(self, num_pages: int):
-        if num_pages <= 0:
-            raise ValueError("a page pool needs at least one page")
-        self.num_pages = int(num_pages)
-        self._free: List[int] = list(range(self.num_pages - 1, -1, -1))
-        self._refs: List[int] = [0] * self.num_pages
+    def __init__(self, num_pages: int, _borrowed: Optional[int] = None):
+        self._lib = native.library()
+        if _borrowed is not None:
+            self._pool, self._owned = ctypes.c_void_p(_borrowed), False
+        else:
+            if num_pages <= 0:
+                raise ValueError("a page pool needs at least one page")
+            self._pool, self._owned = ctypes.c_void_p(self._lib.vxh_pages_create(int(num_pages))), True
+        self.num_pages = self._lib.vxh_pages_num_pages(self._pool)
+
+    def __del__(self):
+        if getattr(self, "_owned", False) and self._pool:
+            self._lib.vxh_pages_destroy(self._pool)
+            self._pool = None
 
     @property
     def num_free(self) -> int:
-        return len(self._free)
+        return self._lib.vxh_pages_num_free(self._pool)
 
     def alloc(self, n: int) -> Optional[List[int]]:
         """n pages with count 1, or None (and nothing taken) if fewer are free."""
         if n < 0:
             raise ValueError("cannot allocate %d pages" % n)
-        if len(self._free) < n:
-            return None
-        out = [self._free.pop() for _ in range(n)]
-        for p in out:
-            if self._refs[p] != 0:
-                raise CacheAccountingError("page %d was on the free list with count %d" % (p, self._refs[p]))
-            self._refs[p] = 1
-        return out
+        out = (ctypes.c_int * max(n, 1))()
+        return list(out[:n]) if native.check(self._lib.vxh_pages_alloc(self._pool, n, out)) else None
 
     def incref(self, pages: Iterable[int]) -> None:
-        for p in pages:
-            self._check(p)
-            if self._refs[p] < 1:
-                raise CacheAccountingError("page %d is free and cannot be shared" % p)
-            self._refs[p] += 1
+        arr = native.int_array(pages)
+        native.check(self._lib.vxh_pages_incref(self._pool, arr, len(arr)))
 
     def free(self, pages: Iterable[int]) -> None:
-        for p in pages:
-            self._check(p)
-            if self._refs[p] < 1:
-                raise CacheAccountingError("page %d freed twice" % p)
-            self._refs[p] -= 1
-            if self._refs[p] == 0:
-                self._free.append(p)
+        arr = native.int_array(pages)
+        native.check(self._lib.vxh_pages_free(self._pool, arr, len(arr)))
 
     def refcount(self, page: int) -> int:
-        self._check(page)
-        return self._refs[page]
+        return native.check(self._lib.vxh_pages_refcount(self._pool, int(page)))
 
-    def _check(self, p: int) -> None:
-        if not 0 <= p < self.num_pages:
-            raise CacheAccountingError("page id %r is outside the pool of %d" % (p, self.num_pages))
+    def free_list(self) -> List[int]:
+        """The free ids, the next one handed out last."""
+        out = (ctypes.c_int * self.num_pages)()
+        n = self._lib.vxh_pages_free_list(self._pool, out, self.num_pages)
+        return list(out[:n])
 
 
 class SlotAllocator:
     """Slots for per-request state of fixed size; the lowest free slot first."""
 
-    def __init__(self, num_slots: int):
-        if num_slots <= 0:
-            raise ValueError("a slot pool needs at least one slot")
-        self.num_slots = int(num_slots)
-        self._free: List[int] = list(range(self.num_slots - 1, -1, -1))
-        self._held = [False] * self.num_slots
+    def __init__(self, num_slots: int, _borrowed: Optional[int] = None):
+        self._lib = native.library()
+        if _borrowed is not None:
+            self._pool, self._owned = ctypes.c_void_p(_borrowed), False
+        else:
+            if num_slots <= 0:
+                raise ValueError("a slot pool needs at least one slot")
+            self._pool, self._owned = ctypes.c_void_p(self._lib.vxh_slots_create(int(num_slots))), True
+        self.num_slots = self._lib.vxh_slots_num_slots(self._pool)
+
+    def __del__(self):
+        if getattr(self, "_owned", False) and self._pool:
+            self._lib.vxh_slots_destroy(self._pool)
+            self._pool = None
 
     @property
     def num_free(self) -> int:
-        return len(self._free)
+        return self._lib.vxh_slots_num_free(self._pool)
 
     def alloc(self) -> Optional[int]:
-        if not self._free:
-            return None
-        s = self._free.pop()
-        self._held[s] = True
-        return s
+        s = self._lib.vxh_slots_alloc(self._pool)
+        return None if s < 0 else s
 
     def free(self, slot: int) -> None:
-        if not 0 <= slot < self.num_slots or not self._held[slot]:
-            raise CacheAccountingError("state slot %r is not held" % slot)
-        self._held[slot] = False
-        self._free.append(slot)
+        native.check(self._lib.vxh_slots_free(self._pool, int(slot)))

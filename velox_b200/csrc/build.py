@@ -1,4 +1,5 @@
-"""Compiles the CUDA sources beside this file into one shared library for sm_100a.
+"""Compiles the CUDA sources beside this file into one shared library for sm_100a,
+and the host sources under `host/` (C++, no CUDA) into a second one.
 
 `nvcc` is called directly, one object per source file in parallel, then one link;
 no Python or torch header is included by the sources, so a full build takes well
@@ -144,5 +145,49 @@ def build(force: bool = False, verbose: bool = True, ptxas_info: bool = False) -
             fcntl.flock(lock, fcntl.LOCK_UN)
 
 
+HOST_LIB_NAME = "libvelox_b200_host.so"
+HOST_DIR = os.path.join(HERE, "host")
+
+
+def find_cxx() -> str:
+    for cand in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"), shutil.which("clang++")):
+        if cand and (os.path.isfile(cand) or shutil.which(cand)):
+            return cand
+    raise BuildError("no C++ compiler found (looked at $CXX, g++, c++, clang++); the host library cannot be compiled")
+
+
+def build_host(force: bool = False, verbose: bool = True) -> str:
+    """Build the host library (scheduler, cache books, step builders) if it is out
+    of date; returns its path.  Needs a C++17 compiler and nothing else."""
+    out_dir = build_dir()
+    lib = os.path.join(out_dir, HOST_LIB_NAME)
+    srcs = sorted(glob.glob(os.path.join(HOST_DIR, "*.cpp")))
+    deps = srcs + sorted(glob.glob(os.path.join(HOST_DIR, "*.hpp"))) + [os.path.abspath(__file__)]
+    if not srcs:
+        raise BuildError("no .cpp sources in %s" % HOST_DIR)
+    if not force and not _stale(lib, deps):
+        return lib
+    with open(os.path.join(out_dir, ".lock_host"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and not _stale(lib, deps):
+                return lib
+            t0 = time.time()
+            if verbose:
+                _say("compiling the host library into %s" % out_dir)
+            tmp = lib + ".tmp%d" % os.getpid()
+            cmd = [find_cxx(), "-O2", "-std=c++17", "-Wall", "-shared", "-fPIC", "-I", HOST_DIR] + srcs + ["-o", tmp]
+            p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+            if p.returncode != 0:
+                raise BuildError("the host library failed to compile:\n%s\n%s" % (" ".join(cmd), p.stdout))
+            os.replace(tmp, lib)
+            if verbose:
+                _say("built %s in %.0f s" % (lib, time.time() - t0))
+            return lib
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
 if __name__ == "__main__":
     build(force="--force" in sys.argv, ptxas_info="--ptxas" in sys.argv)
+    build_host(force="--force" in sys.argv)

@@ -5,10 +5,13 @@ prompt, or one decoded token), and the places among them whose logits are
 wanted.  The reference's counterpart is `BatchStep`/`SeqSlice`
 (src/paged/qwen3.rs:245-269), which rebuilds and uploads block tables and
 offsets inside every layer (src/paged/qwen3.rs:584-627); here the description is
-built once per step on the host, sent in one copy, and shared by all layers.
+built once per step on the host (by the host library, `csrc/host/step_builder.hpp`,
+straight from the cache manager's books), sent in one copy, and shared by all
+layers.
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence
 
@@ -53,78 +56,69 @@ class StepContext:
         return self.max_new == 1
 
 
-def build_step_arrays(entries: Sequence[StepEntry], cache, vocab_size: Optional[int] = None):
-    """Host arrays of a step (numpy int32), after the cache has reserved the
-    pages: a dict of named arrays and the list of per-group (block_table, slot_mapping)."""
-    S, MB = cache.page_size, cache.max_blocks
-    n = len(entries)
-    lens = [len(e.tokens) for e in entries]
-    total = sum(lens)
-    token_ids = np.empty(total, np.int32)
-    positions = np.empty(total, np.int32)
-    seq_of_token = np.empty(total, np.int32)
-    cu = np.zeros(n + 1, np.int32)
-    offsets = np.empty(n, np.int32)
-    slots = np.empty(n, np.int32)
-    wanted: List[int] = []
-    groups = [(np.full((n, MB), -1, np.int32), np.empty(total, np.int32)) for _ in cache.groups]
-    row = 0
-    for i, e in enumerate(entries):
-        rc = cache.requests[e.request_id]
-        k = lens[i]
-        toks = np.asarray(e.tokens, dtype=np.int64)
-        if vocab_size is not None and k and (toks.min() < 0 or toks.max() >= vocab_size):
-            raise ValueError("request %r: token id outside [0, %d)" % (e.request_id, vocab_size))
-        token_ids[row:row + k] = toks
-        pos = np.arange(rc.length, rc.length + k, dtype=np.int32)
-        positions[row:row + k] = pos
-        seq_of_token[row:row + k] = i
-        cu[i + 1] = row + k
-        offsets[i] = rc.length
-        slots[i] = rc.slot
-        for w in e.want:
-            if not 0 <= w < k:
-                raise ValueError("request %r: wanted place %r is not among its %d tokens" % (e.request_id, w, k))
-            wanted.append(row + int(w))
-        for (bt, sm), table in zip(groups, rc.tables):
-            if len(table) * S < rc.length + k:
-                raise ValueError("request %r: block table too short (%d pages for %d positions)"
-                                 % (e.request_id, len(table), rc.length + k))
-            bt[i, :len(table)] = table
-            pages = np.asarray(table, np.int32)[pos // S]
-            if k and pages.min() < 0:
-                raise ValueError("request %r: a new position falls into a page that was given back" % (e.request_id,))
-            sm[row:row + k] = pages * S + pos % S
-        row += k
-    arrays = dict(token_ids=token_ids, positions=positions, seq_of_token=seq_of_token, cu_seqlens=cu,
-                  kv_offsets=offsets, state_slots=slots, wanted_rows=np.asarray(wanted, np.int32))
-    return arrays, groups, lens
-
-
-def build_step_context(entries: Sequence[StepEntry], cache, device, vocab_size: Optional[int] = None) -> StepContext:
-    """Packs the step's description into one pinned buffer and copies it once."""
-    arrays, groups, lens = build_step_arrays(entries, cache, vocab_size)
-    parts = list(arrays.values())
-    for bt, sm in groups:
-        parts += [bt.reshape(-1), sm]
-    sizes = [p.size for p in parts]
-    # every section starts on a 16-byte boundary
+def _sections(n: int, total: int, wanted: int, n_groups: int, max_blocks: int):
+    """Sizes and starts (in 32-bit words, every section on a 16-byte boundary) of the
+    sections of a step's description, in the host library's order."""
+    sizes = [total, total, total, n + 1, n, n, wanted]
+    for _ in range(n_groups):
+        sizes += [n * max_blocks, total]
     starts, cur = [], 0
     for s in sizes:
         starts.append(cur)
         cur += (s + 3) // 4 * 4
-    host = torch.empty(max(cur, 4), dtype=torch.int32, pin_memory=(torch.device(device).type == "cuda"))
-    hv = host.numpy()
-    for p, st, s in zip(parts, starts, sizes):
-        hv[st:st + s] = p
+    return sizes, starts, cur
+
+
+def build_step_arrays(entries: Sequence[StepEntry], cache, vocab_size: Optional[int] = None, out=None):
+    """The step's description after the cache has reserved the pages, written by the
+    host library into `out` (a writable int32 numpy array, made if not given).
+    Returns (out, sizes, starts, summary) with summary = (tokens, wanted rows,
+    longest portion, most keys of any request after the step)."""
+    from .. import native
+
+    n = len(entries)
+    lens = [len(e.tokens) for e in entries]
+    total, wanted = sum(lens), sum(len(e.want) for e in entries)
+    sizes, starts, words = _sections(n, total, wanted, len(cache.groups), cache.max_blocks)
+    if out is None:
+        out = np.empty(max(words, 4), np.int32)
+    try:
+        rids = cache.handles(e.request_id for e in entries)
+    except KeyError as e:
+        raise KeyError("request %r holds no cache; add it first" % (e.args[0],))
+    tokens = np.fromiter((t for e in entries for t in e.tokens), np.int64, total)
+    if vocab_size is not None and total and (tokens.min() < 0 or tokens.max() >= vocab_size):
+        bad = next(e.request_id for e in entries if any(not 0 <= int(t) < vocab_size for t in e.tokens))
+        raise ValueError("request %r: token id outside [0, %d)" % (bad, vocab_size))
+    tokens = tokens.astype(np.int32)
+    for e, k in zip(entries, lens):
+        for w in e.want:
+            if not 0 <= w < k:
+                raise ValueError("request %r: wanted place %r is not among its %d tokens" % (e.request_id, w, k))
+    summary = (ctypes.c_int64 * 4)()
+    native.check(cache._lib.vxh_build_step(
+        cache._book, n, rids, native.int_array(lens), tokens.ctypes.data_as(ctypes.POINTER(ctypes.c_int)),
+        native.int_array(len(e.want) for e in entries), native.int_array(w for e in entries for w in e.want),
+        -1 if vocab_size is None else int(vocab_size), out.ctypes.data_as(ctypes.c_void_p),
+        native.int64_array(starts), summary))
+    return out, sizes, starts, [int(x) for x in summary]
+
+
+def build_step_context(entries: Sequence[StepEntry], cache, device, vocab_size: Optional[int] = None) -> StepContext:
+    """Has the step's description written into one pinned buffer and copies it once."""
+    n = len(entries)
+    lens = [len(e.tokens) for e in entries]
+    _, _, words = _sections(n, sum(lens), sum(len(e.want) for e in entries), len(cache.groups), cache.max_blocks)
+    host = torch.empty(max(words, 4), dtype=torch.int32, pin_memory=(torch.device(device).type == "cuda"))
+    hv, sizes, starts, summary = build_step_arrays(entries, cache, vocab_size, out=host.numpy())
     dev = host.to(device, non_blocking=True)
     views = [dev[st:st + s] for st, s in zip(starts, sizes)]
-    named = dict(zip(arrays.keys(), views[:len(arrays)]))
-    gviews = views[len(arrays):]
-    n, MB = len(entries), cache.max_blocks
-    gctx = [GroupContext(gviews[2 * i].view(n, MB), gviews[2 * i + 1]) for i in range(len(groups))]
-    offs = [int(x) for x in arrays["kv_offsets"]]
+    names = ["token_ids", "positions", "seq_of_token", "cu_seqlens", "kv_offsets", "state_slots", "wanted_rows"]
+    named = dict(zip(names, views[:7]))
+    gviews = views[7:]
+    MB = cache.max_blocks
+    gctx = [GroupContext(gviews[2 * i].view(n, MB), gviews[2 * i + 1]) for i in range(len(cache.groups))]
+    offs = [int(x) for x in hv[starts[4]:starts[4] + n]]
     return StepContext(
-        n_tokens=int(sum(lens)), n_seqs=n, groups=gctx, new_lens=lens, offsets=offs,
-        slots=[int(x) for x in arrays["state_slots"]], max_new=max(lens) if lens else 0,
-        max_kv=max((o + l for o, l in zip(offs, lens)), default=0), **named)
+        n_tokens=summary[0], n_seqs=n, groups=gctx, new_lens=lens, offsets=offs,
+        slots=[int(x) for x in hv[starts[5]:starts[5] + n]], max_new=summary[2], max_kv=summary[3], **named)

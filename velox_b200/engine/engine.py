@@ -135,12 +135,12 @@ class Engine:
         entries, _ended = self.scheduler.plan()
         if not entries:
             return []
-        reqs = [self.scheduler.running[e.request_id] for e in entries if e.want]
+        reqs = [self.scheduler.request(e.request_id) for e in entries if e.want]
         temps = [0.0 if r.params.greedy else r.params.temperature for r in reqs]
         tops = [r.params.top_p if r.params.nucleus else 1.0 for r in reqs]
         us = [0.0 if r.params.greedy else uniform(
             r.params.seed if r.params.seed is not None else self.config.seed * 1000003 + r.request_id,
-            0, len(r.generated)) for r in reqs]
+            0, r.num_generated) for r in reqs]
         _logits, ids = self.runner.step_and_sample(entries, temps, tops, us)
         sampled: List[int] = ids.tolist() if ids is not None else []
         if self.runner.pending_error_check:
@@ -167,15 +167,7 @@ class Engine:
         return [list(self.scheduler.finished[i].generated) for i in ids]
 
     def request(self, request_id: int) -> Request:
-        s = self.scheduler
-        if request_id in s.running:
-            return s.running[request_id]
-        if request_id in s.finished:
-            return s.finished[request_id]
-        for r in s.waiting:
-            if r.request_id == request_id:
-                return r
-        raise KeyError(request_id)
+        return self.scheduler.request(request_id)
 
     def stats(self) -> Dict:
         d = dict(vars(self.scheduler.stats))

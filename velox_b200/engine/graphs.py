@@ -15,6 +15,7 @@ fields of the step) do not use graphs at all.
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -59,6 +60,8 @@ class _Graph:
         self.sizes = sizes
         self.host = torch.zeros(cur, dtype=torch.int32, pin_memory=True)
         self.hv = self.host.numpy()
+        self.host_ptr = ctypes.c_void_p(self.host.data_ptr())
+        self.starts_c = (ctypes.c_int64 * len(self.starts))(*self.starts)
         self.dev = torch.zeros(cur, dtype=torch.int32, device=device)
         v = [self.dev[st:st + s] for st, s in zip(self.starts, sizes)]
         hvv = [self.hv[st:st + s] for st, s in zip(self.starts, sizes)]
@@ -79,31 +82,16 @@ class _Graph:
         self.launches = 0
         self.copied: Optional[torch.cuda.Event] = None  # the last copy out of the pinned buffer
 
-    def fill(self, entries: Sequence[StepEntry], cache, sampling) -> None:
+    def fill(self, entries: Sequence[StepEntry], cache, sampling, vocab_size: int = -1) -> None:
         if self.copied is not None:
             self.copied.synchronize()  # the pinned buffer is free once its last copy has run
-        n, B, S = len(entries), self.bucket, cache.page_size
-        h = self.h
-        slots = np.fromiter((cache.requests[e.request_id].slot for e in entries), np.int64, n)
-        pos = cache.length_of_slot[slots]
-        h["token_ids"][:n] = [e.tokens[0] for e in entries]
-        h["positions"][:n] = pos
-        h["kv_offsets"][:n] = pos
-        h["state_slots"][:n] = slots
-        if n < B:
-            h["token_ids"][n:] = 0
-            h["positions"][n:] = 0
-            h["kv_offsets"][n:] = 0
-            h["state_slots"][n:] = 0
-        cols = min(cache.max_blocks, int(pos.max()) // S + 1)   # pages any of these requests can reach
-        rows = np.arange(n)
-        for (bt, sm), mirror in zip(self.h_groups, cache.table_of_slot):
-            tables = mirror[slots, :cols]
-            bt[:n, :cols] = tables
-            sm[:n] = tables[rows, pos // S] * S + pos % S
-            if n < B:
-                sm[n:] = -1
-                bt[n:, :cols] = 0
+        from .. import native
+        n = len(entries)
+        max_kv = ctypes.c_int64(0)
+        native.check(cache._lib.vxh_fill_decode(
+            cache._book, n, self.bucket, cache.handles(e.request_id for e in entries),
+            native.int_array(int(e.tokens[0]) for e in entries), int(vocab_size), self.host_ptr, self.starts_c,
+            ctypes.byref(max_kv)))
         if sampling is None:
             self.h_temp[:] = 0.0
         else:
@@ -139,12 +127,12 @@ class DecodeGraphs:
         the first len(entries) rows are the entries'."""
         cache = self.runner.cache
         n = len(entries)
-        max_kv = max(cache.requests[e.request_id].length for e in entries) + 1
+        max_kv = max(cache.length(e.request_id) for e in entries) + 1
         key = (batch_bucket(n, self.has_state, self.cap), keys_bucket(max_kv))
         g = self.graphs.get(key)
         if g is None:
             g = self.graphs[key] = _Graph(self.runner, *key)
-        g.fill(entries, cache, sampling)
+        g.fill(entries, cache, sampling, self.runner.vocab_size)
         if g.graph is None:
             self._capture(g)
         g.graph.replay()

@@ -26,30 +26,81 @@ What differs, on purpose:
 
 The scheduler decides and keeps books; it runs nothing on the device.  `plan()`
 reserves the pages of the step it returns; `update()` takes the sampled tokens.
+
+The decisions are made by the host library (`csrc/host/scheduler.hpp`), next to
+the cache manager's books that they read and change.  This module is its Python
+face: it keeps what only Python needs (the sampling parameters of a request) and
+shows requests and queues as views that ask the library when they are read.
 """
 from __future__ import annotations
 
-from collections import deque
-from dataclasses import dataclass, field
-from typing import Deque, Dict, List, Optional, Sequence, Tuple
+import ctypes
+from dataclasses import dataclass
+from typing import Dict, Iterator, List, Mapping, Optional, Sequence, Tuple
 
+from .. import native
 from ..cache.manager import CacheManager
+from ..native import RequestRefused  # noqa: F401  (part of this module's interface)
 from ..sampling.params import SamplingParams
 from .batch import StepEntry
 
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+_STATUS = (WAITING, RUNNING, FINISHED)
+_REASON = (None, "stop", "length")
 
 
-@dataclass
 class Request:
-    request_id: int
-    prompt: List[int]
-    params: SamplingParams
-    generated: List[int] = field(default_factory=list)
-    status: str = WAITING
-    finish_reason: Optional[str] = None
-    admitted_at: int = -1  # admission counter: the latest is preempted first
-    preemptions: int = 0
+    """A request as the library holds it; every attribute is read there."""
+
+    def __init__(self, scheduler: "Scheduler", request_id: int):
+        self._s, self.request_id = scheduler, int(request_id)
+
+    def _info(self) -> List[int]:
+        info = (ctypes.c_int64 * 8)()
+        native.check(self._s._lib.vxh_sched_request(self._s._sched, self.request_id, info))
+        return list(info)
+
+    def _tokens(self, generated: int, start: int, stop: int) -> List[int]:
+        out = (ctypes.c_int * max(stop - start, 1))()
+        native.check(self._s._lib.vxh_sched_request_tokens(self._s._sched, self.request_id, generated, start, stop, out))
+        return list(out[:stop - start])
+
+    @property
+    def params(self) -> SamplingParams:
+        return self._s._params[self.request_id]
+
+    @property
+    def prompt(self) -> List[int]:
+        return self._tokens(0, 0, self._info()[0])
+
+    @property
+    def generated(self) -> List[int]:
+        return self._tokens(1, 0, self._info()[1])
+
+    @property
+    def num_generated(self) -> int:
+        return self._info()[1]
+
+    @property
+    def last_token(self) -> int:
+        n = self._info()[1]
+        return self._tokens(1, n - 1, n)[0]
+
+    @property
+    def status(self) -> str:
+        return _STATUS[self._info()[2]]
+
+    @property
+    def finish_reason(self) -> Optional[str]:
+        return _REASON[self._info()[3]]
+
+    @property
+    def admitted_at(self) -> int:
+        return self._info()[4]
+
+    @property
+    def preemptions(self) -> int:
+        return self._info()[5]
 
     @property
     def tokens(self) -> List[int]:
@@ -57,16 +108,17 @@ class Request:
 
     @property
     def num_tokens(self) -> int:
-        return len(self.prompt) + len(self.generated)
+        info = self._info()
+        return info[0] + info[1]
 
-    def token_slice(self, start: int, stop: int) -> List[int]:
-        """tokens[start:stop] without building the whole list."""
-        n = len(self.prompt)
-        if stop <= n:
-            return self.prompt[start:stop]
-        if start >= n:
-            return self.generated[start - n:stop - n]
-        return self.prompt[start:] + self.generated[:stop - n]
+    def __eq__(self, other) -> bool:
+        return isinstance(other, Request) and other._s is self._s and other.request_id == self.request_id
+
+    def __hash__(self) -> int:
+        return hash(self.request_id)
+
+    def __repr__(self) -> str:
+        return "Request(%d, %s)" % (self.request_id, self.status)
 
 
 @dataclass
@@ -81,8 +133,45 @@ class SchedulerStats:
     last_batch_tokens: int = 0
 
 
-class RequestRefused(ValueError):
-    pass
+class _Queue(Mapping):
+    """`scheduler.running` / `scheduler.finished`: request id -> `Request`, by id."""
+
+    def __init__(self, scheduler: "Scheduler", which: int):
+        self._s, self._which = scheduler, which
+
+    def _ids(self) -> List[int]:
+        s = self._s
+        n = s._lib.vxh_sched_list(s._sched, self._which, None, 0)
+        out = (ctypes.c_int64 * max(n, 1))()
+        s._lib.vxh_sched_list(s._sched, self._which, out, n)
+        return list(out[:n])
+
+    def __getitem__(self, request_id) -> Request:
+        if not isinstance(request_id, int) or not self._s._lib.vxh_sched_contains(self._s._sched, self._which, request_id):
+            raise KeyError(request_id)
+        return Request(self._s, request_id)
+
+    def __iter__(self) -> Iterator[int]:
+        return iter(self._ids())
+
+    def __len__(self) -> int:
+        return int(self._s._lib.vxh_sched_list(self._s._sched, self._which, None, 0))
+
+
+class _Waiting(Sequence):
+    """`scheduler.waiting`: the queue, its head first."""
+
+    def __init__(self, scheduler: "Scheduler"):
+        self._q = _Queue(scheduler, 0)
+
+    def __getitem__(self, i):
+        ids = self._q._ids()
+        if isinstance(i, slice):
+            return [Request(self._q._s, r) for r in ids[i]]
+        return Request(self._q._s, ids[i])
+
+    def __len__(self) -> int:
+        return len(self._q)
 
 
 class Scheduler:
@@ -92,197 +181,97 @@ class Scheduler:
         self.max_running_requests = int(max_running_requests)
         self.max_batch_tokens = int(max_batch_tokens)
         self.chunk_size = chunk_size
-        limit = cache.max_blocks * cache.page_size
-        self.max_model_len = min(int(max_model_len), limit) if max_model_len else limit
-        self.waiting: Deque[Request] = deque()
-        self.running: Dict[int, Request] = {}
-        self.finished: Dict[int, Request] = {}
-        self.stats = SchedulerStats()
-        self._next_id = 0
-        self._admissions = 0
+        self._lib = native.library()
+        self._sched = ctypes.c_void_p(self._lib.vxh_sched_create(
+            cache._book, self.max_running_requests, self.max_batch_tokens, int(chunk_size or 0), int(max_model_len or 0)))
+        if not self._sched:
+            raise ValueError("max_running_requests and max_batch_tokens must be positive")
+        self.max_model_len = int(self._lib.vxh_sched_max_model_len(self._sched))
+        self._params: Dict[int, SamplingParams] = {}
+        self.waiting = _Waiting(self)
+        self.running = _Queue(self, 1)
+        self.finished = _Queue(self, 2)
+
+    def __del__(self):
+        if getattr(self, "_sched", None):
+            self._lib.vxh_sched_destroy(self._sched)
+            self._sched = None
+
+    @property
+    def stats(self) -> SchedulerStats:
+        out = (ctypes.c_int64 * 8)()
+        self._lib.vxh_sched_stats(self._sched, out)
+        return SchedulerStats(*[int(x) for x in out])
+
+    def request(self, request_id: int) -> Request:
+        """The request with that id, wherever it is (KeyError if there is none)."""
+        r = Request(self, request_id)
+        r._info()
+        return r
 
     # -- submit ---------------------------------------------------------------
     def submit(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> int:
         params = params or SamplingParams()
-        prompt = [int(t) for t in prompt]
-        if not prompt:  # the reference rejects an empty prompt too (src/paged/scheduler.rs:165-167)
-            self.stats.requests_refused += 1
-            raise RequestRefused("empty prompt")
-        total = len(prompt) + params.max_tokens
-        if total > self.max_model_len:
-            self.stats.requests_refused += 1
-            raise RequestRefused("prompt (%d) + max_tokens (%d) exceeds the longest sequence %d"
-                                 % (len(prompt), params.max_tokens, self.max_model_len))
-        pages = -(-total // self.cache.page_size)
-        for g in self.cache.groups:
-            need = pages if g.window <= 0 else min(pages, -(-(g.window + min(self._portion_cap(), total))
-                                                           // self.cache.page_size) + 1)
-            if need > g.allocator.num_pages:
-                self.stats.requests_refused += 1
-                raise RequestRefused("the request needs %d pages of a pool of %d and could never run"
-                                     % (need, g.allocator.num_pages))
-        rid = self._next_id
-        self._next_id += 1
-        self.waiting.append(Request(rid, prompt, params))
+        toks = native.int_array(int(t) for t in prompt)
+        stops = native.int_array(list(params.eos_token_ids) + list(params.stop_token_ids))
+        rid = native.check(self._lib.vxh_sched_submit(self._sched, toks, len(toks), int(params.max_tokens),
+                                                      1 if params.ignore_eos else 0, stops, len(stops)))
+        self._params[rid] = params
         return rid
 
-    def _portion_cap(self) -> int:
-        return min(self.max_batch_tokens, self.chunk_size) if self.chunk_size else self.max_batch_tokens
-
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self._lib.vxh_sched_has_work(self._sched))
 
     # -- one step's plan ------------------------------------------------------
-    def _remaining(self, r: Request) -> int:
-        return len(r.prompt) + len(r.generated) - self.cache.length(r.request_id)
-
-    def _preempt(self, victim: Request) -> None:
-        self.cache.release(victim.request_id)
-        del self.running[victim.request_id]
-        victim.status = WAITING
-        victim.preemptions += 1
-        self.stats.preemptions += 1
-        self.waiting.appendleft(victim)
-
-    def _finish(self, r: Request, reason: str) -> None:
-        if self.cache.has_request(r.request_id):
-            self.cache.release(r.request_id)
-        self.running.pop(r.request_id, None)
-        r.status, r.finish_reason = FINISHED, reason
-        self.finished[r.request_id] = r
-        self.stats.requests_completed += 1
-
     def plan(self) -> Tuple[List[StepEntry], List[Request]]:
         """The next step: its entries (pages already reserved) and the requests
         that were ended while planning (alone and out of pages)."""
-        ended: List[Request] = []
-        while True:
-            entries = self._plan_once(ended)
-            if entries or not self.running:
-                return entries, ended
-            # Requests hold cache but none can move (every one waits for pages
-            # the others hold): the one admitted last makes room.
-            victim = max(self.running.values(), key=lambda q: q.admitted_at)
-            if len(self.running) == 1:
-                self._finish(victim, "length")
-                ended.append(victim)
-            else:
-                self._preempt(victim)
-
-    def _plan_once(self, ended: List[Request]) -> List[StepEntry]:
-        budget = self.max_batch_tokens
-        chosen: Dict[int, int] = {}
-        preempted = False
-
-        # 1. requests that decode: one token each, oldest id first
-        for rid in sorted(self.running):
-            r = self.running.get(rid)
-            if r is None or self._remaining(r) != 1 or not r.generated:
-                continue
-            if budget <= 0:
-                break
-            while not self.cache.reserve(rid, 1):
-                victim = max(self.running.values(), key=lambda q: q.admitted_at)
-                if victim is r and len(self.running) == 1:
-                    self._finish(r, "length")
-                    ended.append(r)
-                    break
-                chosen.pop(victim.request_id, None)
-                self._preempt(victim)
-                preempted = True
-                if victim is r:
-                    break
-            else:
-                chosen[rid] = 1
-                budget -= 1
-
-        # 2. prompts under way (and recomputations), oldest id first
-        for rid in sorted(self.running):
-            r = self.running[rid]
-            if rid in chosen or budget <= 0:
-                continue
-            rem = self._remaining(r)
-            if rem == 1 and r.generated and rid not in chosen:
-                continue  # a decode that found no budget
-            k = min(rem, budget, self._portion_cap())
-            k = self._fit(rid, k)
-            if k > 0:
-                chosen[rid] = k
-                budget -= k
-
-        # 3. admissions, first come first served; none in a step that had to
-        # preempt (the pages just freed are for those that stayed)
-        while (not preempted and self.waiting and budget > 0
-               and len(self.running) < self.max_running_requests):
-            r = self.waiting[0]
-            if self.cache.add_request(r.request_id) is None:
-                break
-            k = self._fit(r.request_id, min(r.num_tokens, budget, self._portion_cap()))
-            if k <= 0:
-                self.cache.release(r.request_id)
-                if not self.running:  # nothing will ever free a page for it
-                    self.waiting.popleft()
-                    self._finish(r, "length")
-                    ended.append(r)
-                    continue
-                break  # head of the line waits; nobody overtakes it
-            self.waiting.popleft()
-            r.status = RUNNING
-            r.admitted_at = self._admissions
-            self._admissions += 1
-            self.running[r.request_id] = r
-            chosen[r.request_id] = k
-            budget -= k
-
+        counts = (ctypes.c_longlong * 4)()
+        native.check(self._lib.vxh_sched_plan(self._sched, counts))
+        n, total, n_ended, n_admitted = (int(x) for x in counts)
         entries: List[StepEntry] = []
-        for rid in sorted(chosen):
-            r = self.running[rid]
-            done = self.cache.length(rid)
-            toks = r.token_slice(done, done + chosen[rid])
-            last = done + chosen[rid] == r.num_tokens
-            entries.append(StepEntry(rid, toks, [len(toks) - 1] if last else []))
-        return entries
-
-    def _fit(self, rid: int, k: int) -> int:
-        """The largest portion <= k whose pages can be reserved now (reserves it)."""
-        while k > 0:
-            if self.cache.reserve(rid, k):
-                return k
-            # fewer pages: shrink to what the scarcest group can still hold
-            rc = self.cache.requests[rid]
-            room = min((len(t) + g.allocator.num_free) * self.cache.page_size - rc.length
-                       for t, g in zip(rc.tables, self.cache.groups))
-            k = min(k - 1, room)
-        return 0
+        if n:
+            ids, starts, lens = (ctypes.c_int64 * n)(), (ctypes.c_int64 * n)(), (ctypes.c_int64 * n)()
+            wants, tokens = (ctypes.c_int * n)(), (ctypes.c_int * max(total, 1))()
+            self._lib.vxh_sched_plan_entries(self._sched, ids, starts, lens, wants, tokens)
+            at = 0
+            for i in range(n):
+                k = int(lens[i])
+                entries.append(StepEntry(int(ids[i]), tokens[at:at + k], [k - 1] if wants[i] else []))
+                at += k
+        ended: List[Request] = []
+        if n_ended:
+            ids = (ctypes.c_int64 * n_ended)()
+            self._lib.vxh_sched_plan_ended(self._sched, ids)
+            ended = [Request(self, int(r)) for r in ids]
+        if n_admitted and self.cache._state_layers:
+            ids, slots = (ctypes.c_int64 * n_admitted)(), (ctypes.c_int * n_admitted)()
+            self._lib.vxh_sched_plan_admitted(self._sched, ids, slots)
+            for slot in slots:  # a state slot starts from zero
+                self.cache.zero_state(int(slot))
+        return entries, ended
 
     # -- after the step -------------------------------------------------------
     def update(self, entries: Sequence[StepEntry], sampled: Sequence[int]) -> List[Tuple[int, int, bool]]:
         """Takes the tokens sampled for the entries that wanted one (in order).
         Returns (request id, token, finished) for each."""
-        out: List[Tuple[int, int, bool]] = []
-        it = iter(sampled)
-        self.stats.steps += 1
-        self.stats.last_batch_size = len(entries)
-        self.stats.last_batch_tokens = sum(len(e.tokens) for e in entries)
-        for e in entries:
-            r = self.running[e.request_id]
-            if not e.want:
-                self.stats.prompt_tokens += len(e.tokens)
-                continue
-            tok = int(next(it))
-            if len(e.tokens) > 1 or not r.generated:
-                self.stats.prompt_tokens += len(e.tokens)
-            r.generated.append(tok)
-            self.stats.tokens_generated += 1
-            p = r.params
-            reason = None
-            if not p.ignore_eos and (tok in p.eos_token_ids or tok in p.stop_token_ids):
-                reason = "stop"
-            elif len(r.generated) >= p.max_tokens:
-                reason = "length"
-            elif len(r.prompt) + len(r.generated) >= self.max_model_len:
-                reason = "length"
-            if reason:
-                self._finish(r, reason)
-            out.append((r.request_id, tok, reason is not None))
-        return out
+        n = len(entries)
+        ids = native.int64_array(e.request_id for e in entries)
+        lens = native.int64_array(len(e.tokens) for e in entries)
+        wants = native.int_array(1 if e.want else 0 for e in entries)
+        toks = native.int_array(int(t) for t in sampled)
+        m = max(len(toks), 1)
+        out_ids, out_tok, out_fin = (ctypes.c_int64 * m)(), (ctypes.c_int * m)(), (ctypes.c_int * m)()
+        k = native.check(self._lib.vxh_sched_update(self._sched, n, ids, lens, wants, toks, len(toks),
+                                                    out_ids, out_tok, out_fin))
+        return [(int(out_ids[i]), int(out_tok[i]), bool(out_fin[i])) for i in range(k)]
+
+    def _finish(self, request, reason: str) -> None:
+        """Ends a request from outside (its cache is given back)."""
+        rid = request.request_id if isinstance(request, Request) else int(request)
+        native.check(self._lib.vxh_sched_finish(self._sched, rid, _REASON.index(reason)))
+
+    def forget(self, request_id: int) -> None:
+        """Drops the record of a finished request whose tokens have been read."""
+        self._lib.vxh_sched_forget(self._sched, int(request_id))
+        self._params.pop(int(request_id), None)

@@ -15,6 +15,7 @@ from typing import List, Optional, Sequence
 
 import torch
 
+from .. import native
 from ..cache.manager import CacheManager, OutOfPages
 from ..csrc import ops
 from .batch import StepContext, StepEntry, build_step_context
@@ -59,14 +60,17 @@ class ModelRunner:
 
     def _step(self, entries, sampling, sample: bool):
         self.validate(entries)
-        taken: List[StepEntry] = []
-        for e in entries:
-            if not self.cache.reserve(e.request_id, len(e.tokens)):
-                # give back nothing: pages already reserved stay with their
-                # requests (they are theirs to use in a later step)
-                raise OutOfPages("no pages left for request %r (%d new tokens); free pages per group: %s"
-                                 % (e.request_id, len(e.tokens), self.cache.free_pages()))
-            taken.append(e)
+        cache = self.cache
+        n = len(entries)
+        rids = cache.handles(e.request_id for e in entries)
+        counts = native.int_array(len(e.tokens) for e in entries)
+        got = native.check(cache._lib.vxh_cache_reserve_many(cache._book, n, rids, counts))
+        if got < n:
+            # give back nothing: pages already reserved stay with their
+            # requests (they are theirs to use in a later step)
+            e = entries[got]
+            raise OutOfPages("no pages left for request %r (%d new tokens); free pages per group: %s"
+                             % (e.request_id, len(e.tokens), cache.free_pages()))
         ids = None
         if self.graphs is not None and self.graphs.eligible(entries):
             for e in entries:
@@ -93,8 +97,7 @@ class ModelRunner:
             if sample and logits is not None:
                 t = torch.tensor([sampling[0], sampling[1], sampling[2]], dtype=torch.float32).to(self.device, non_blocking=True)
                 ids = ops.sample(logits, t[0], t[1], t[2]) if any(x > 0 for x in sampling[0]) else ops.sample(logits)
-        for e in entries:
-            self.cache.commit(e.request_id, len(e.tokens))
+        native.check(cache._lib.vxh_cache_commit_many(cache._book, n, rids, counts))
         self.steps += 1
         return logits, (ids if sample else None)
 
