@@ -29,6 +29,12 @@ MODEL = dict(vocab_size=151936, hidden_size=4096, intermediate_size=12288, num_h
              num_attention_heads=32, head_dim=128, attention_bias=False, num_key_value_heads=8,
              max_position_embeddings=40960, tie_word_embeddings=False, rope_theta=1000000.0,
              rms_norm_eps=1e-6, hidden_act="silu")
+# Other shapes of the same architecture, for measurements beside the benchmark's (`--shape`).
+SHAPES = {
+    "8b": {},
+    "14b": dict(hidden_size=5120, intermediate_size=17408, num_hidden_layers=40, num_attention_heads=40),
+    "32b": dict(hidden_size=5120, intermediate_size=25600, num_hidden_layers=64, num_attention_heads=64),
+}
 CONTEXT, PROMPT, PAGE, BATCH, SEED = 4096, 2048, 16, 8, 2
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -90,6 +96,12 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(mhz)}
 
 
+def weight_bytes(cfg, layers, elt=2):
+    E, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    H, Hk, D = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    return (layers * ((H + 2 * Hk) * D * E + E * H * D + 3 * I * E) + 2 * V * E) * elt
+
+
 def decode_bytes(cfg, layers, batch, kv_len, elt=2):
     """Bytes a decode step has to read: every weight once, and the live requests' cache."""
     E, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
@@ -116,6 +128,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (recorded in config)")
     ap.add_argument("--batch", type=int, default=BATCH)
+    ap.add_argument("--shape", default="8b", choices=sorted(SHAPES),
+                    help="layer sizes: 8b is the benchmark's; 14b and 32b are Qwen3-14B / 32B")
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64 and prefill")
     args = ap.parse_args()
 
@@ -134,8 +148,9 @@ def main() -> int:
     from velox_b200.csrc import ops
     from velox_b200.engine import StepEntry
 
-    layers = args.layers or MODEL["num_hidden_layers"]
-    raw = dict(MODEL, num_hidden_layers=layers)
+    model = dict(MODEL, **SHAPES[args.shape])
+    layers = args.layers or model["num_hidden_layers"]
+    raw = dict(model, num_hidden_layers=layers)
     cfg = Qwen3Config.from_dict(raw)
     pk = peaks()
     max_batch = 64 if not args.skip_points else args.batch
@@ -194,7 +209,7 @@ def main() -> int:
             engine.scheduler._finish(r, "length")
         return e2e_ms, dev_ms, launches, held + steps / 2.0
 
-    out = {"metric": "decode tok/s @ batch %d, Qwen3-8B bf16, context %d" % (args.batch, CONTEXT),
+    out = {"metric": "decode tok/s @ batch %d, Qwen3-%s bf16, context %d" % (args.batch, args.shape.upper(), CONTEXT),
            "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "higher_is_better": True, "scaling": "weak",
            "vs_baseline": None, "dtype": "bf16", "data": "synthetic: random weights N(0,0.02) seed 2, uniform random token ids"}
 
@@ -234,11 +249,12 @@ def main() -> int:
             pts["decode_b%d" % b] = round(b * 1000.0 / m, 1)
         out["points"] = pts
 
-    out["config"] = {"model": "Qwen3-8B shape", "layers": layers, "layers_full": MODEL["num_hidden_layers"],
+    out["config"] = {"model": "Qwen3-%s shape" % args.shape.upper(), "layers": layers,
+                     "layers_full": model["num_hidden_layers"],
                      "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                      "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
                      "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT, "page_size": PAGE,
-                     "parallelism": "single GPU", "l2": "inputs larger than L2 (weights 15 GB)",
+                     "parallelism": "single GPU", "l2": "inputs larger than L2 (weights %.0f GB)" % (weight_bytes(raw, layers) / 1e9),
                      "peaks": pk["source"]}
     print(json.dumps(out))
     return 0

@@ -151,3 +151,23 @@ def test_a_long_prompt_in_one_step_and_in_two(model_folders, tmp_path, dtype):
     got = run_trace(folder, dtype, tr.steps, 1152, str(tmp_path / "out"), page_size=16)
     for n in sorted(tr.expect):
         assert_close(got[n], tr.expect[n], dtype, "long prompt step %d" % n)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_context_of_4000_tokens(model_folders, tmp_path, dtype):
+    """A prompt of 3,950 tokens in portions of 2,048 and 1,902 (the second on top of
+    2,048 cached positions), then 50 tokens one by one beside a short request:
+    sixteen pieces of keys per decoded token, a window of 200 far from the start."""
+    folder = model_folders["tiny_d"]
+    cfg, w = P.load_model_folder(folder)
+    long_, short = random_tokens(cfg["vocab_size"], 4000, 41), random_tokens(cfg["vocab_size"], 60, 42)
+    plain = {"L": P.forward_logits(cfg, w, long_), "s": P.forward_logits(cfg, w, short)}
+    tr = Trace()
+    tr.add([("L", long_[:2048], [0, 1000, 2047], 0)], plain=plain)
+    tr.add([("L", long_[2048:3950], [0, 1, 951, 1901], 2048), ("s", short[:10], [9], 0)], plain=plain)
+    for k in range(50):
+        tr.add([("L", [long_[3950 + k]], [0], 3950 + k), ("s", [short[10 + k]], [0], 10 + k)],
+               end=["L", "s"] if k == 49 else [], plain=plain)
+    got = run_trace(folder, dtype, tr.steps, 4032 + 64, str(tmp_path / "out"), page_size=16)
+    for n in sorted(tr.expect):
+        assert_close(got[n], tr.expect[n], dtype, "context of 4000, step %d" % n)
