@@ -120,6 +120,70 @@ def prefill_flops(cfg, layers, tokens):
     return linear + attn + 2 * V * E
 
 
+def stream_workload(args, cfg, layers):
+    """Continuous batching under arrivals: 64 requests with prompts of 128 to 4,096
+    random tokens and 256 new tokens each arrive as a Poisson stream; every step goes
+    through `Engine.step`.  Reports generated tokens a second over the whole run,
+    time to the first token and time between tokens (host clock around the steps,
+    which end with the read of the sampled ids), and the scheduler's counters."""
+    import random
+
+    import torch
+    from velox_b200 import Engine, EngineConfig, SamplingParams
+
+    n_req, new_tokens, longest = 64, 256, 4096
+    rng = random.Random(SEED + 1)
+    lens = [rng.randint(128, longest) for _ in range(n_req)]
+    arrivals, t = [], 0.0
+    for _ in range(n_req):
+        t += rng.expovariate(args.arrival_rate)
+        arrivals.append(t)
+    pool = args.pool_tokens or n_req * (longest + new_tokens + PAGE)
+    engine = Engine(model_config=cfg, random_seed=SEED, config=EngineConfig(
+        dtype="bfloat16", page_size=PAGE, num_pages=-(-pool // PAGE), max_running_requests=n_req,
+        max_batch_tokens=2048, max_model_len=longest + new_tokens + PAGE))
+    gen = torch.Generator().manual_seed(SEED + 2)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist() for n in lens]
+    # warm-up: kernels, graphs of a few batch sizes, the library's handles
+    engine.generate([prompts[0][:300], prompts[1][:40]], SamplingParams(max_tokens=4, ignore_eos=True))
+    torch.cuda.synchronize()
+    first, last, gaps, submitted_at = {}, {}, [], {}
+    nxt, done = 0, 0
+    t0 = time.perf_counter()
+    while done < n_req:
+        now = time.perf_counter() - t0
+        while nxt < n_req and arrivals[nxt] <= now:
+            rid = engine.add_request(prompts[nxt], SamplingParams(max_tokens=new_tokens, ignore_eos=True))
+            submitted_at[rid] = arrivals[nxt]
+            nxt += 1
+        if not engine.scheduler.has_work():
+            time.sleep(max(0.0, arrivals[nxt] - (time.perf_counter() - t0)))
+            continue
+        out = engine.step()
+        now = time.perf_counter() - t0
+        for rid, _tok, finished in out:
+            if rid in last:
+                gaps.append(now - last[rid])
+            else:
+                first[rid] = now - submitted_at[rid]
+            last[rid] = now
+            done += bool(finished)
+    wall = time.perf_counter() - t0
+    st = engine.stats()
+
+    def pct(v, q):
+        v = sorted(v)
+        return round(1000.0 * v[min(len(v) - 1, int(q * len(v)))], 2)
+    return {"metric": "generated tok/s, continuous batching, Qwen3-%s bf16" % args.shape.upper(), "unit": "tokens/s",
+            "value": round(n_req * new_tokens / wall, 1), "wall_s": round(wall, 3), "n_gpus": 1,
+            "requests": n_req, "prompt_tokens": sum(lens), "new_tokens": n_req * new_tokens,
+            "arrival_rate": args.arrival_rate, "pool_tokens": pool,
+            "ttft_ms": {"p50": pct(first.values(), 0.5), "p90": pct(first.values(), 0.9), "p99": pct(first.values(), 0.99)},
+            "itl_ms": {"p50": pct(gaps, 0.5), "p90": pct(gaps, 0.9), "p99": pct(gaps, 0.99)},
+            "steps": st["steps"], "preemptions": st["preemptions"], "layers": layers,
+            "data": "synthetic: random weights, uniform random token ids, seeded arrivals"}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -128,6 +192,12 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (recorded in config)")
     ap.add_argument("--batch", type=int, default=BATCH)
+    ap.add_argument("--workload", default="decode", choices=["decode", "stream"],
+                    help="decode: the benchmark (steady decoding at a fixed batch). stream: continuous batching "
+                         "under arrivals (64 requests, prompts of 128-4,096 tokens, 256 new tokens each, Poisson "
+                         "arrivals); prints its own JSON line")
+    ap.add_argument("--arrival-rate", type=float, default=16.0, help="stream: mean arrivals a second")
+    ap.add_argument("--pool-tokens", type=int, default=0, help="stream: cache pool in tokens (0: room for all)")
     ap.add_argument("--shape", default="8b", choices=sorted(SHAPES),
                     help="layer sizes: 8b is the benchmark's; 14b and 32b are Qwen3-14B / 32B")
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64 and prefill")
@@ -153,6 +223,9 @@ def main() -> int:
     raw = dict(model, num_hidden_layers=layers)
     cfg = Qwen3Config.from_dict(raw)
     pk = peaks()
+    if args.workload == "stream":
+        print(json.dumps(stream_workload(args, cfg, layers)))
+        return 0
     max_batch = 64 if not args.skip_points else args.batch
     engine = Engine(model_config=cfg, random_seed=SEED, config=EngineConfig(
         dtype="bfloat16", page_size=PAGE, num_pages=max_batch * (CONTEXT // PAGE + 1) + 8,
