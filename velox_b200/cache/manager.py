@@ -31,7 +31,6 @@ import ctypes
 from dataclasses import dataclass, field
 from typing import Dict, Iterator, List, Mapping, Optional, Sequence
 
-import numpy as np
 import torch
 
 from .. import native
@@ -140,13 +139,6 @@ class CacheManager:
         self._names: Dict[int, object] = {}
         self._next_handle = -1
         self.requests = _Requests(self)
-        # Views of the library's dense mirrors, for building a step's description
-        # without loops: per group the block table of every slot (-1 where no page is
-        # held), and every slot's length.
-        self.table_of_slot: List[np.ndarray] = [
-            np.ctypeslib.as_array(self._lib.vxh_cache_mirror(self._book, g), shape=(int(max_requests), self.max_blocks))
-            for g in range(len(self.groups))]
-        self.length_of_slot = np.ctypeslib.as_array(self._lib.vxh_cache_lengths(self._book), shape=(int(max_requests),))
         for g in self.groups:
             if device is not None:
                 shape = (len(g.layers), 2, num_pages, g.spec.num_kv_heads, self.page_size, g.spec.head_dim)
@@ -180,7 +172,6 @@ class CacheManager:
     def __del__(self):
         book = getattr(self, "_book", None)
         if book:
-            self.table_of_slot, self.length_of_slot = [], None  # views into the book
             self._lib.vxh_cache_destroy(book)
             self._book = None
 

@@ -44,8 +44,6 @@ void* vxh_cache_create(int n_groups, const int* windows, int page_size, int num_
 void vxh_cache_destroy(void* c) { delete (CacheBook*)c; }
 void* vxh_cache_pool(void* c, int g) { return &((CacheBook*)c)->group(g).pool; }
 void* vxh_cache_slots(void* c) { return &((CacheBook*)c)->slots(); }
-int32_t* vxh_cache_mirror(void* c, int g) { return ((CacheBook*)c)->group(g).mirror.data(); }
-int64_t* vxh_cache_lengths(void* c) { return ((CacheBook*)c)->lengths(); }
 int vxh_cache_add(void* c, int64_t rid) { return ((CacheBook*)c)->add(rid); }
 int vxh_cache_has(void* c, int64_t rid) { return ((CacheBook*)c)->find(rid) != nullptr; }
 long long vxh_cache_num_requests(void* c) { return (long long)((CacheBook*)c)->num_requests(); }

@@ -8,8 +8,8 @@
 // request ends, and in a group with a window as soon as every position of a page
 // lies before the window of the next query; the freed page is the next one
 // handed out.  Beside the tables the book keeps, per group, a dense mirror
-// [slot, block] (-1 where no page is held) and every slot's length, which the
-// step builders read without looking a request up.
+// [slot, block] (-1 where no page is held), from which the step builders copy
+// whole rows.
 //
 // The device storage (the pools of keys and values, the state tensors) is not
 // here: the book only knows ids.
@@ -40,8 +40,7 @@ struct CacheGroup {
 class CacheBook {
 public:
     CacheBook(int n_groups, const int* windows, int page_size, int num_pages, int max_requests, int max_blocks)
-        : page_size_(page_size), max_blocks_(max_blocks), max_requests_(max_requests), slots_(max_requests),
-          lengths_(max_requests, 0) {
+        : page_size_(page_size), max_blocks_(max_blocks), max_requests_(max_requests), slots_(max_requests) {
         groups_.reserve(n_groups);
         for (int g = 0; g < n_groups; ++g)
             groups_.emplace_back(windows[g], num_pages, (size_t)max_requests * max_blocks);
@@ -51,7 +50,6 @@ public:
     int num_groups() const { return (int)groups_.size(); }
     CacheGroup& group(int g) { return groups_[g]; }
     SlotPool& slots() { return slots_; }
-    int64_t* lengths() { return lengths_.data(); }
     size_t num_requests() const { return reqs_.size(); }
 
     RequestCache* find(int64_t rid) {
@@ -73,7 +71,6 @@ public:
         rc.slot = slot;
         rc.tables.resize(groups_.size());
         reqs_.emplace(rid, std::move(rc));
-        lengths_[slot] = 0;
         for (auto& g : groups_) std::fill_n(g.mirror.begin() + (size_t)slot * max_blocks_, max_blocks_, -1);
         return slot;
     }
@@ -123,7 +120,6 @@ public:
         RequestCache* rc = need(rid);
         if (!rc) return ERR_UNKNOWN_REQUEST;
         rc->length += new_tokens;
-        lengths_[rc->slot] = rc->length;
         for (size_t g = 0; g < groups_.size(); ++g) {
             auto& table = rc->tables[g];
             if ((int64_t)table.size() * page_size_ < rc->length)
@@ -196,7 +192,6 @@ private:
     std::vector<CacheGroup> groups_;
     SlotPool slots_;
     std::unordered_map<int64_t, RequestCache> reqs_;
-    std::vector<int64_t> lengths_;
 };
 
 }  // namespace vxh

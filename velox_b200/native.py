@@ -9,7 +9,7 @@ status into the Python exception its kind asks for, with the library's message.
 from __future__ import annotations
 
 import ctypes
-from ctypes import POINTER, c_char_p, c_int, c_int32, c_int64, c_longlong, c_void_p
+from ctypes import POINTER, c_char_p, c_int, c_int64, c_longlong, c_void_p
 
 from .csrc import build as _build
 
@@ -61,7 +61,7 @@ def check(status: int) -> int:
 
 def _declare(lib: ctypes.CDLL) -> None:
     P, I, L = c_void_p, c_int, c_longlong
-    PI, PI32, PI64 = POINTER(c_int), POINTER(c_int32), POINTER(c_int64)
+    PI, PI64 = POINTER(c_int), POINTER(c_int64)
     sig = {
         "vxh_last_error": (c_char_p, []),
         "vxh_pages_create": (P, [I]), "vxh_pages_destroy": (None, [P]), "vxh_pages_num_pages": (I, [P]),
@@ -70,8 +70,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "vxh_slots_create": (P, [I]), "vxh_slots_destroy": (None, [P]), "vxh_slots_num_slots": (I, [P]),
         "vxh_slots_num_free": (I, [P]), "vxh_slots_alloc": (I, [P]), "vxh_slots_free": (I, [P, I]),
         "vxh_cache_create": (P, [I, PI, I, I, I, I]), "vxh_cache_destroy": (None, [P]),
-        "vxh_cache_pool": (P, [P, I]), "vxh_cache_slots": (P, [P]), "vxh_cache_mirror": (PI32, [P, I]),
-        "vxh_cache_lengths": (PI64, [P]), "vxh_cache_add": (I, [P, c_int64]), "vxh_cache_has": (I, [P, c_int64]),
+        "vxh_cache_pool": (P, [P, I]), "vxh_cache_slots": (P, [P]), "vxh_cache_add": (I, [P, c_int64]), "vxh_cache_has": (I, [P, c_int64]),
         "vxh_cache_num_requests": (L, [P]), "vxh_cache_request_ids": (L, [P, PI64, L]),
         "vxh_cache_length": (L, [P, c_int64]), "vxh_cache_slot": (I, [P, c_int64]),
         "vxh_cache_table": (I, [P, c_int64, I, PI, I]), "vxh_cache_pages_needed": (I, [P, c_int64, L, PI]),
