@@ -31,7 +31,11 @@ TC_PREFILL_MIN_TOKENS = 32   # longest portion of a step from which the tcgen05 
 
 
 class PagedAttention(Mixer):
-    cuda_graph_safe = True  # reads nothing of a step but device tensors and sizes fixed per graph
+    @property
+    def cuda_graph_safe(self) -> bool:
+        # reads nothing of a step but device tensors and sizes fixed per graph; a position
+        # encoding of its own kind has to say the same of itself
+        return self.position is None or bool(self.position.cuda_graph_safe)
 
     def __init__(self, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  bias: bool = False, qk_norm: bool = True, eps: float = 1e-6, window: int = 0,
@@ -65,7 +69,12 @@ class PagedAttention(Mixer):
         if self.qk_norm:
             specs.append(TensorSpec(p + "q_norm.weight", (self.head_dim,), "norm"))
             specs.append(TensorSpec(p + "k_norm.weight", (self.head_dim,), "norm"))
+        if self.position is not None:
+            specs.extend(self.position.tensor_specs())
         return specs
+
+    def ignored_tensors(self) -> List[str]:
+        return self.position.ignored_tensors() if self.position is not None else []
 
     def bind(self, tensors: Dict[str, torch.Tensor], runtime: Runtime) -> None:
         super().bind(tensors, runtime)
@@ -76,6 +85,8 @@ class PagedAttention(Mixer):
         self.out = Linear(tensors[p + "o_proj.weight"], tensors[p + "o_proj.bias"] if self.bias else None)
         if self.qk_norm:
             self.q_norm_weight, self.k_norm_weight = tensors[p + "q_norm.weight"], tensors[p + "k_norm.weight"]
+        if self.position is not None:
+            self.position.bind(tensors, runtime)
 
     # -- cache ---------------------------------------------------------------
     def cache_spec(self):

@@ -21,6 +21,8 @@ from .base import Position
 
 
 class RotaryPosition(Position):
+    cuda_graph_safe = True
+
     def __init__(self, prefix: str = "", head_dim: int = 0, theta: float = 10000.0, rotary_dim: Optional[int] = None):
         super().__init__(prefix)
         self.head_dim = int(head_dim)
@@ -43,5 +45,7 @@ class RotaryPosition(Position):
 
 
 class NoPosition(Position):
+    cuda_graph_safe = True
+
     def __init__(self, prefix: str = "", **_ignored):
         super().__init__(prefix)
