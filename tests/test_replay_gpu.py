@@ -171,3 +171,43 @@ def test_a_context_of_4000_tokens(model_folders, tmp_path, dtype):
     got = run_trace(folder, dtype, tr.steps, 4032 + 64, str(tmp_path / "out"), page_size=16)
     for n in sorted(tr.expect):
         assert_close(got[n], tr.expect[n], dtype, "context of 4000, step %d" % n)
+
+
+ODD = {
+    # seven query heads per kv head, head size 112, three layers, a window on the last two
+    "odd_a": dict(seed=11, page_size=16, lens=[150, 45, 33, 90, 1, 2, 3, 64],
+                  config=dict(vocab_size=1000, hidden_size=200, intermediate_size=100, num_hidden_layers=3,
+                              num_attention_heads=14, head_dim=112, attention_bias=False, num_key_value_heads=2,
+                              max_position_embeddings=1024, tie_word_embeddings=True, rope_theta=10000.0,
+                              rms_norm_eps=1e-5, hidden_act="silu", use_sliding_window=True, sliding_window=150,
+                              max_window_layers=1)),
+    # head size 256, five query heads per kv head, a width of 50 and a vocabulary of 97, biases, pages of 8
+    "odd_b": dict(seed=12, page_size=8, lens=[130, 45, 33, 70, 1, 2, 3, 64],
+                  config=dict(vocab_size=97, hidden_size=50, intermediate_size=144, num_hidden_layers=1,
+                              num_attention_heads=10, head_dim=256, attention_bias=True, num_key_value_heads=2,
+                              max_position_embeddings=1024, tie_word_embeddings=False, rope_theta=500000.0,
+                              rms_norm_eps=1e-6, hidden_act="silu", use_sliding_window=True, sliding_window=33,
+                              max_window_layers=0)),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(ODD))
+def test_sizes_that_no_fast_kernel_takes(tmp_path, name, dtype):
+    """Head sizes, group sizes and widths outside what the tensor-core kernels take:
+    the engine has to find another kernel for each, or refuse; never a wrong result."""
+    from velox_b200.config import Qwen3Config
+    from velox_b200.weights import write_random_model
+
+    spec = ODD[name]
+    folder = write_random_model(str(tmp_path / "model"), Qwen3Config.from_dict(spec["config"]), seed=spec["seed"],
+                                dtype="bfloat16")
+    cfg, w = P.load_model_folder(folder)
+    seqs = {"r%d" % n: random_tokens(cfg["vocab_size"], L, 300 + n) for n, L in enumerate(spec["lens"])}
+    plain = {i: P.forward_logits(cfg, w, t) for i, t in seqs.items()}
+    tr = build_trace(seqs, plain)
+    pool = sum(-(-L // 64) * 64 for L in sorted(spec["lens"])[-4:])
+    got = run_trace(folder, dtype, tr.steps, pool, str(tmp_path / "out"), page_size=spec["page_size"])
+    assert sorted(got) == sorted(tr.expect)
+    for n in sorted(tr.expect):
+        assert_close(got[n], tr.expect[n], dtype, "%s %s step %d" % (name, dtype, n))
