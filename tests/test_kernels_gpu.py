@@ -144,6 +144,34 @@ def test_qk_norm_rope_kv(dtype, H, Hk, D, rot, S):
     assert torch.equal(work2[:, (H + Hk) * D :], qkv[:, (H + Hk) * D :])
 
 
+def test_qk_norm_rope_kv_for_many_tokens_gives_the_same_bits():
+    """From 64 tokens on the bfloat16 kernel for heads of 128 works row by row with the
+    token's cosines and sines shared by all heads; the result is the one of the
+    kernel for few tokens, bit for bit."""
+    H, Hk, D, S, T, pages, eps = 6, 2, 128, 16, 150, 12, 1e-6
+    qkv = rnd((T, (H + 2 * Hk) * D), torch.bfloat16, 6, 2.0)
+    qw, kw = (1 + 0.05 * torch.randn(D)).to(DEV), (1 + 0.05 * torch.randn(D)).to(DEV)
+    positions = torch.randint(0, 40000, (T,), dtype=torch.int32).to(DEV)
+    slots = torch.randperm(pages * S)[:T].to(torch.int32)
+    slots[17] = -1                                            # a row that writes nothing
+    slots = slots.to(DEV)
+    inv = torch.from_numpy(P.rope_inverse_frequencies(D, 1e6)).to(DEV)
+    outs = []
+    for step in (T, 50):                                      # all at once; in slices below 64 tokens
+        work = qkv.clone()
+        kp = torch.full((pages, Hk, S, D), float("nan"), dtype=torch.bfloat16, device=DEV)
+        vp = torch.full_like(kp, float("nan"))
+        for a in range(0, T, step):
+            part = work[a:a + step].contiguous()
+            ops().qk_norm_rope_kv(part, qw, kw, eps, inv, D, positions[a:a + step].contiguous(),
+                                  slots[a:a + step].contiguous(), kp, vp, H, Hk, D)
+            work[a:a + step] = part
+        outs.append((work, kp, vp))
+    for x, y in zip(*outs):
+        assert torch.equal(torch.nan_to_num(x.float(), nan=-7.0), torch.nan_to_num(y.float(), nan=-7.0))
+    assert int(torch.isnan(outs[0][1].float()).sum()) == (pages * S - (T - 1)) * Hk * D
+
+
 # ----------------------------------------------------------------------------
 def paged_case(dtype, seqs, H, Hk, D, S, window, seed, spike=None):
     """seqs: list of (kv_offset, new_tokens).  Builds whole sequences, scatters
