@@ -59,6 +59,15 @@ long long vxh_cache_length(void* c, int64_t rid) {
     RequestCache* rc = ((CacheBook*)c)->need(rid);
     return rc ? (long long)rc->length : (long long)ERR_UNKNOWN_REQUEST;
 }
+long long vxh_cache_max_length(void* c, int n, const int64_t* rids) {  // the longest of these requests
+    long long best = 0;
+    for (int i = 0; i < n; ++i) {
+        RequestCache* rc = ((CacheBook*)c)->need(rids[i]);
+        if (!rc) return ERR_UNKNOWN_REQUEST;
+        best = std::max<long long>(best, rc->length);
+    }
+    return best;
+}
 int vxh_cache_slot(void* c, int64_t rid) {
     RequestCache* rc = ((CacheBook*)c)->need(rid);
     return rc ? rc->slot : (int)ERR_UNKNOWN_REQUEST;

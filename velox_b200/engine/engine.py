@@ -135,12 +135,21 @@ class Engine:
         entries, _ended = self.scheduler.plan()
         if not entries:
             return []
-        reqs = [self.scheduler.request(e.request_id) for e in entries if e.want]
-        temps = [0.0 if r.params.greedy else r.params.temperature for r in reqs]
-        tops = [r.params.top_p if r.params.nucleus else 1.0 for r in reqs]
-        us = [0.0 if r.params.greedy else uniform(
-            r.params.seed if r.params.seed is not None else self.config.seed * 1000003 + r.request_id,
-            0, r.num_generated) for r in reqs]
+        temps, tops, us = [], [], []
+        for e in entries:
+            if not e.want:
+                continue
+            p = self.scheduler.params_of(e.request_id)
+            if p.greedy:
+                temps.append(0.0)
+                tops.append(1.0)
+                us.append(0.0)
+                continue
+            temps.append(p.temperature)
+            tops.append(p.top_p if p.nucleus else 1.0)
+            # one uniform number per (request, token): the same sequence whatever the batching
+            seed = p.seed if p.seed is not None else self.config.seed * 1000003 + e.request_id
+            us.append(uniform(seed, 0, self.scheduler.request(e.request_id).num_generated))
         _logits, ids = self.runner.step_and_sample(entries, temps, tops, us)
         sampled: List[int] = ids.tolist() if ids is not None else []
         if self.runner.pending_error_check:

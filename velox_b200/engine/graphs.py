@@ -21,6 +21,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
+from .. import native
 from ..csrc import ops
 from .batch import GroupContext, StepContext, StepEntry
 
@@ -82,14 +83,13 @@ class _Graph:
         self.launches = 0
         self.copied: Optional[torch.cuda.Event] = None  # the last copy out of the pinned buffer
 
-    def fill(self, entries: Sequence[StepEntry], cache, sampling, vocab_size: int = -1) -> None:
+    def fill(self, entries: Sequence[StepEntry], rids, cache, sampling, vocab_size: int = -1) -> None:
         if self.copied is not None:
             self.copied.synchronize()  # the pinned buffer is free once its last copy has run
-        from .. import native
         n = len(entries)
         max_kv = ctypes.c_int64(0)
         native.check(cache._lib.vxh_fill_decode(
-            cache._book, n, self.bucket, cache.handles(e.request_id for e in entries),
+            cache._book, n, self.bucket, rids,
             native.int_array(int(e.tokens[0]) for e in entries), int(vocab_size), self.host_ptr, self.starts_c,
             ctypes.byref(max_kv)))
         if sampling is None:
@@ -122,17 +122,18 @@ class DecodeGraphs:
     def eligible(self, entries: Sequence[StepEntry]) -> bool:
         return self.usable and len(entries) > 0 and all(len(e.tokens) == 1 for e in entries)
 
-    def step(self, entries: Sequence[StepEntry], sampling=None):
-        """Runs a decode-only step.  Returns (logits [bucket, vocab], ids [bucket]):
-        the first len(entries) rows are the entries'."""
+    def step(self, entries: Sequence[StepEntry], rids, sampling=None):
+        """Runs a decode-only step (`rids`: the entries' ids in the host library, a C
+        array).  Returns (logits [bucket, vocab], ids [bucket]): the first
+        len(entries) rows are the entries'."""
         cache = self.runner.cache
         n = len(entries)
-        max_kv = max(cache.length(e.request_id) for e in entries) + 1
+        max_kv = int(native.check(cache._lib.vxh_cache_max_length(cache._book, n, rids))) + 1
         key = (batch_bucket(n, self.has_state, self.cap), keys_bucket(max_kv))
         g = self.graphs.get(key)
         if g is None:
             g = self.graphs[key] = _Graph(self.runner, *key)
-        g.fill(entries, cache, sampling, self.runner.vocab_size)
+        g.fill(entries, rids, cache, sampling, self.runner.vocab_size)
         if g.graph is None:
             self._capture(g)
         g.graph.replay()

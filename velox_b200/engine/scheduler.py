@@ -203,6 +203,9 @@ class Scheduler:
         self._lib.vxh_sched_stats(self._sched, out)
         return SchedulerStats(*[int(x) for x in out])
 
+    def params_of(self, request_id: int) -> SamplingParams:
+        return self._params[request_id]
+
     def request(self, request_id: int) -> Request:
         """The request with that id, wherever it is (KeyError if there is none)."""
         r = Request(self, request_id)

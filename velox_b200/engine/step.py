@@ -41,8 +41,6 @@ class ModelRunner:
             seen.add(e.request_id)
             if len(e.tokens) == 0:
                 raise ValueError("request %r brings no tokens" % (e.request_id,))
-            if not self.cache.has_request(e.request_id):
-                raise KeyError("request %r holds no cache; add it first" % (e.request_id,))
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Runs one batch.  Returns float32 logits [wanted, vocab] on the device
@@ -62,9 +60,13 @@ class ModelRunner:
         self.validate(entries)
         cache = self.cache
         n = len(entries)
-        rids = cache.handles(e.request_id for e in entries)
-        counts = native.int_array(len(e.tokens) for e in entries)
-        got = native.check(cache._lib.vxh_cache_reserve_many(cache._book, n, rids, counts))
+        try:
+            rids = cache.handles(e.request_id for e in entries)
+            counts = native.int_array(len(e.tokens) for e in entries)
+            got = native.check(cache._lib.vxh_cache_reserve_many(cache._book, n, rids, counts))
+        except KeyError:
+            missing = next(e.request_id for e in entries if not cache.has_request(e.request_id))
+            raise KeyError("request %r holds no cache; add it first" % (missing,))
         if got < n:
             # give back nothing: pages already reserved stay with their
             # requests (they are theirs to use in a later step)
@@ -78,7 +80,7 @@ class ModelRunner:
                     raise ValueError("request %r: token id outside [0, %d)" % (e.request_id, self.vocab_size))
                 if any(w != 0 for w in e.want):
                     raise ValueError("request %r: wanted place is not among its 1 tokens" % (e.request_id,))
-            all_logits, all_ids = self.graphs.step(entries, sampling if sample else None)
+            all_logits, all_ids = self.graphs.step(entries, rids, sampling if sample else None)
             rows = [i for i, e in enumerate(entries) for _ in e.want]
             if not rows:
                 logits = None

@@ -72,7 +72,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "vxh_cache_create": (P, [I, PI, I, I, I, I]), "vxh_cache_destroy": (None, [P]),
         "vxh_cache_pool": (P, [P, I]), "vxh_cache_slots": (P, [P]), "vxh_cache_add": (I, [P, c_int64]), "vxh_cache_has": (I, [P, c_int64]),
         "vxh_cache_num_requests": (L, [P]), "vxh_cache_request_ids": (L, [P, PI64, L]),
-        "vxh_cache_length": (L, [P, c_int64]), "vxh_cache_slot": (I, [P, c_int64]),
+        "vxh_cache_length": (L, [P, c_int64]), "vxh_cache_max_length": (L, [P, I, PI64]), "vxh_cache_slot": (I, [P, c_int64]),
         "vxh_cache_table": (I, [P, c_int64, I, PI, I]), "vxh_cache_pages_needed": (I, [P, c_int64, L, PI]),
         "vxh_cache_can_reserve": (I, [P, c_int64, L]), "vxh_cache_reserve": (I, [P, c_int64, L]),
         "vxh_cache_commit": (I, [P, c_int64, L]), "vxh_cache_release": (I, [P, c_int64]),
