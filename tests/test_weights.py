@@ -2,11 +2,10 @@
 import json
 import os
 
-import numpy as np
 import pytest
 import torch
 
-from helpers import TINY, tiny_config, write_tiny
+from helpers import tiny_config, write_tiny
 from velox_b200.models import DecoderModel
 from velox_b200.models.qwen3 import qwen3_plan
 from velox_b200.parts.base import Runtime

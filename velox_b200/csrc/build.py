@@ -20,7 +20,7 @@ import subprocess
 import sys
 import tempfile
 import time
-from typing import List, Optional
+from typing import List
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_NAME = "libvelox_b200_kernels.so"

@@ -44,7 +44,6 @@ def main(argv: Optional[List[str]] = None) -> int:
     sys.stderr.flush()
     from ..csrc import ops
     ops.library()  # compiles at the first call of a fresh checkout; prints progress
-    import numpy as np
     from ..config.engine_config import EngineConfig
     from .batch import StepEntry
     from .engine import Engine

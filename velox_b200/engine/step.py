@@ -11,7 +11,7 @@ src/paged/scheduler.rs:416-418).
 """
 from __future__ import annotations
 
-from typing import List, Optional, Sequence
+from typing import Optional, Sequence
 
 import torch
 

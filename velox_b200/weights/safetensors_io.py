@@ -16,7 +16,7 @@ import mmap
 import os
 import struct
 import warnings
-from typing import Dict, Iterable, List, Tuple
+from typing import Dict, List, Tuple
 
 import torch
 
