@@ -109,6 +109,23 @@ __device__ __forceinline__ float pt_ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
 }
+// 2^x for x <= 8 on the multiply-add pipes: x = n + f with n the nearest integer,
+// 2^f by a cubic on [-0.5, 0.5] (relative error 1.4e-4, thirty times below the
+// rounding of a probability to bfloat16), 2^n by an add to the exponent bits.  The
+// special-function unit makes 16 exponentials a cycle per SM, which is as long as
+// the tile's tensor-core work; every PT_POLY_EVERY-th one goes this way instead.
+#ifndef PT_POLY_EVERY
+#define PT_POLY_EVERY 4
+#endif
+__device__ __forceinline__ float pt_ex2_poly(float x) {
+    x = fmaxf(x, -126.f);
+    const float t = x + 12582912.f;          // 1.5 * 2^23: the sum's low mantissa bits hold n
+    const float f = x - (t - 12582912.f);
+    float p = fmaf(f, 0.055029310f, 0.24225681f);
+    p = fmaf(p, f, 0.69325304f);
+    p = fmaf(p, f, 0.99995136f);
+    return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
 __device__ __forceinline__ void pt_commit(unsigned bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
 }
@@ -415,8 +432,10 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
                     if (whole) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 2) {
-                            const float p0 = pt_ex2(fmaf(__uint_as_float(v[c][j]), scale_log2, neg_m));
-                            const float p1 = pt_ex2(fmaf(__uint_as_float(v[c][j + 1]), scale_log2, neg_m));
+                            const float x0 = fmaf(__uint_as_float(v[c][j]), scale_log2, neg_m);
+                            const float x1 = fmaf(__uint_as_float(v[c][j + 1]), scale_log2, neg_m);
+                            const float p0 = (j % PT_POLY_EVERY == PT_POLY_EVERY - 1) ? pt_ex2_poly(x0) : pt_ex2(x0);
+                            const float p1 = ((j + 1) % PT_POLY_EVERY == PT_POLY_EVERY - 1) ? pt_ex2_poly(x1) : pt_ex2(x1);
                             ps += p0 + p1;
                             const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                             pk[j >> 1] = *reinterpret_cast<const unsigned*>(&h);
