@@ -95,3 +95,55 @@ def test_eos_and_refusal(model_folders):
         e.add_request(prompt, SamplingParams(max_tokens=1000))
     with pytest.raises(ValueError):
         e.add_request([cfg["vocab_size"]], SamplingParams(max_tokens=2))
+
+
+def test_a_single_token_that_wants_nothing_rides_in_a_captured_step(model_folders):
+    """A recomputed request may bring one token that is not its last: the step has the
+    shape of a decode step (and runs as a captured one), but that row is not sampled."""
+    from velox_b200.engine import StepEntry
+    cfg, w = P.load_model_folder(model_folders["tiny_a"])
+    e = engine(model_folders["tiny_a"], "tiny_a", "float32", num_pages=64)
+    a, b = random_tokens(cfg["vocab_size"], 9, 70), random_tokens(cfg["vocab_size"], 6, 71)
+    for rid, toks in (("a", a), ("b", b)):
+        e.cache.add_request(rid)
+        e.run_step([StepEntry(rid, toks[:-1], [])])
+    logits, ids = e.runner.step_and_sample([StepEntry("a", [a[-1]], []), StepEntry("b", [b[-1]], [0])], [0.0], [1.0], [0.0])
+    assert logits.shape[0] == 1 and ids.tolist() == [int(np.argmax(P.forward_logits(cfg, w, b)[-1]))]
+    assert e.cache.length("a") == 9 and e.cache.length("b") == 6
+    logits, ids = e.runner.step_and_sample([StepEntry("a", [3], []), StepEntry("b", [4], [])], [], [], [])
+    assert logits is None and ids is None
+
+
+def test_graphs_of_an_engine_that_is_gone_do_not_disturb_a_capture(model_folders, monkeypatch):
+    """Engines come and go in one process.  The graphs of a dead engine are destroyed
+    whenever the garbage collector gets to them; if that happened in the middle of
+    another engine's capture, the capture would be invalid.  So the collector runs
+    before a capture, and here it is also made to run in the middle of one: by then it
+    must find nothing of the kind left."""
+    import gc
+    import torch
+    from velox_b200 import SamplingParams
+    from velox_b200.engine import graphs
+    cfg, w = P.load_model_folder(model_folders["tiny_a"])
+    prompt = random_tokens(cfg["vocab_size"], 5, 72)
+    want = P.greedy_generate(cfg, w, prompt, 6)
+    gc.collect()
+    gc.disable()
+    try:
+        e = engine(model_folders["tiny_a"], "tiny_a", "float32", num_pages=32)
+        assert e.generate([prompt], SamplingParams(max_tokens=6)) == [want]
+        assert e.runner.graphs.graphs, "the first engine captured no graph"
+        ring = [e]
+        ring.append(ring)              # only the collector can free this engine and its graphs
+        del e, ring
+        run_model = graphs._Graph.run_model
+
+        def collecting(self, runner):
+            if torch.cuda.is_current_stream_capturing():
+                gc.collect()
+            return run_model(self, runner)
+        monkeypatch.setattr(graphs._Graph, "run_model", collecting)
+        e2 = engine(model_folders["tiny_a"], "tiny_a", "float32", num_pages=32)
+        assert e2.generate([prompt], SamplingParams(max_tokens=6)) == [want]
+    finally:
+        gc.enable()

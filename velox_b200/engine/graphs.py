@@ -16,6 +16,7 @@ fields of the step) do not use graphs at all.
 from __future__ import annotations
 
 import ctypes
+import gc
 from typing import Dict, Optional, Sequence, Tuple
 
 import numpy as np
@@ -149,11 +150,20 @@ class DecodeGraphs:
             g.run_model(self.runner)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
-        # ... then recorded; the keys and values of this step are simply written twice
+        # ... then recorded; the keys and values of this step are simply written twice.
+        # Garbage is collected before, not during, the recording: an older engine's
+        # graphs that happened to be destroyed in the middle of it would invalidate it.
         graph = torch.cuda.CUDAGraph()
         n0 = ops.launch_count()
-        with torch.cuda.graph(graph, pool=self.pool):
-            g.run_model(self.runner)
+        gc.collect()
+        gc_was_on = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph, pool=self.pool):
+                g.run_model(self.runner)
+        finally:
+            if gc_was_on:
+                gc.enable()
         g.launches = ops.launch_count() - n0
         if self.pool is None:
             self.pool = graph.pool()

@@ -80,7 +80,16 @@ class ModelRunner:
                     raise ValueError("request %r: token id outside [0, %d)" % (e.request_id, self.vocab_size))
                 if any(w != 0 for w in e.want):
                     raise ValueError("request %r: wanted place is not among its 1 tokens" % (e.request_id,))
-            all_logits, all_ids = self.graphs.step(entries, rids, sampling if sample else None)
+            per_entry = None
+            if sample:
+                # the sampling lists have one value per wanted place; the captured step
+                # samples every row (a row nobody wants is sampled greedily and dropped)
+                per_entry, k = ([], [], []), 0
+                for e in entries:
+                    for lst, src, default in zip(per_entry, sampling, (0.0, 1.0, 0.0)):
+                        lst.append(src[k] if e.want else default)
+                    k += 1 if e.want else 0
+            all_logits, all_ids = self.graphs.step(entries, rids, per_entry)
             rows = [i for i, e in enumerate(entries) for _ in e.want]
             if not rows:
                 logits = None
