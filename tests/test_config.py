@@ -97,3 +97,17 @@ def test_engine_config():
         EngineConfig(dtype="int8")
     with pytest.raises(ValueError):
         EngineConfig(page_size=0)
+
+
+def test_quantized_checkpoints_are_refused_and_the_registry_fills_itself(tmp_path):
+    import json
+    from velox_b200.config import ConfigError, Qwen3Config, load_config
+    raw = dict(TINY["tiny_a"]["config"], architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+               quantization={"group_size": 64, "bits": 4})
+    with pytest.raises(ConfigError, match="quantized weights are not supported"):
+        Qwen3Config.from_dict(raw)
+    raw["quantization"] = None                    # keys a config.json may carry and that mean nothing here
+    raw.update(rope_scaling=None, torch_dtype="bfloat16", use_cache=True, bos_token_id=1)
+    (tmp_path / "config.json").write_text(json.dumps(raw))
+    arch, cfg = load_config(str(tmp_path))        # (nothing but the configuration has been imported by this test)
+    assert arch.name == "Qwen3ForCausalLM" and cfg.vocab_size == 256

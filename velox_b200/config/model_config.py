@@ -39,10 +39,16 @@ class ModelConfig:
     architecture: ClassVar[str] = ""
     model_type: ClassVar[str] = ""
 
+    # keys that, when present and not null, name something this engine does not do
+    unsupported_keys: ClassVar[Dict[str, str]] = {}
+
     @classmethod
     def from_dict(cls, raw: Dict[str, Any]) -> "ModelConfig":
         faults: list = []
         values: Dict[str, Any] = {}
+        for key, why in cls.unsupported_keys.items():
+            if raw.get(key) is not None:
+                faults.append("key %r: %s" % (key, why))
         for f in dataclasses.fields(cls):
             required = f.default is dataclasses.MISSING and f.default_factory is dataclasses.MISSING
             if f.name not in raw or raw[f.name] is None:
@@ -99,6 +105,11 @@ class Qwen3Config(ModelConfig):
 
     architecture: ClassVar[str] = "Qwen3ForCausalLM"
     model_type: ClassVar[str] = "qwen3"
+    # the reference reads 4-bit checkpoints through these (src/paged/qwen3.rs:51-59)
+    unsupported_keys: ClassVar[Dict[str, str]] = {
+        "quantization": "quantized weights are not supported; the engine holds bfloat16 or float32",
+        "quantization_config": "quantized weights are not supported; the engine holds bfloat16 or float32",
+    }
 
     vocab_size: int = _field(int)
     hidden_size: int = _field(int)

@@ -46,8 +46,16 @@ def registered_architectures():
     return sorted(_BY_NAME)
 
 
+def _register_built_in() -> None:
+    """The package's own architectures register themselves when their modules are
+    imported; a caller that only imported the configuration gets them here."""
+    import importlib
+    importlib.import_module(__package__.rsplit(".", 1)[0] + ".models")
+
+
 def resolve_architecture(raw: Dict[str, Any]) -> Architecture:
     """The entry that a raw config.json names."""
+    _register_built_in()
     names = raw.get("architectures") or []
     if isinstance(names, str):
         names = [names]
