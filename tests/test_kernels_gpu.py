@@ -316,6 +316,13 @@ def test_sample_top_p_keeps_only_the_nucleus():
         seen.add(ops().sample(x, t(1.0), t(0.85), t(i / 64.0)).item())
     assert seen == {10, 20}  # p = .66, .24, .09: the first two reach 0.85
     assert {ops().sample(x, t(1.0), t(0.5), t(i / 64.0)).item() for i in range(64)} == {10}
+    # ties at the nucleus' edge stay together: p = .475, .175 x 3, the rest 0.002 in all; 0.6 is crossed inside the tie
+    y = torch.full((1, 5000), -12.0, device=DEV)
+    y[0, [7, 4000, 4500, 4999]] = torch.tensor([3.0, 2.0, 2.0, 2.0], device=DEV)
+    seen = {ops().sample(y, t(1.0), t(0.6), t(i / 256.0)).item() for i in range(256)}
+    assert seen == {7, 4000, 4500, 4999}
+    p = P.probabilities(f64(y)[0], 1.0, 0.6)
+    assert set(np.nonzero(p)[0].tolist()) == seen
 
 
 # ----------------------------------------------------------------------------
