@@ -214,3 +214,15 @@ def test_random_workloads_finish_and_free_everything():
             assert r.generated == expected(p, len(r.generated))
             assert len(r.generated) == n or r.finish_reason == "length"
         assert cache.free_pages() == total and cache.slots.num_free == 8
+
+
+def test_a_run_of_generated_tokens_can_end_a_request():
+    cache, s = make()
+    prompt = [3, 1, 4, 1, 5]
+    full = expected(prompt, 12)
+    stop = full[4:7]                                   # tokens 5 to 7 of what will be generated
+    rid = s.submit(prompt, SamplingParams(max_tokens=12, stop_sequences=[[250, 250], stop]))
+    other = s.submit(prompt, SamplingParams(max_tokens=12, stop_sequences=[stop[1:] + [stop[0]]]))  # never matches
+    Driver(cache, s).run()
+    assert s.finished[rid].generated == full[:7] and s.finished[rid].finish_reason == "stop"
+    assert s.finished[other].generated == full and s.finished[other].finish_reason == "length"

@@ -91,8 +91,10 @@ def cmd_generate(args) -> int:
                        chunk_size=args.chunk_size, max_model_len=args.max_model_len, seed=args.seed)
     limit = _memory_bytes(args.max_model_memory, torch.device(args.device))
     engine = Engine(folder, cfg, cache_memory_limit=limit)
+    stops = [[int(t) for t in q.split(",") if t.strip()] for q in (args.stop or [])]
     params = [SamplingParams(max_tokens=args.max_tokens, temperature=args.temperature, top_p=args.top_p,
-                             seed=None if args.seed is None else args.seed + i, ignore_eos=args.ignore_eos)
+                             seed=None if args.seed is None else args.seed + i, ignore_eos=args.ignore_eos,
+                             stop_sequences=[list(q) for q in stops])
               for i in range(len(prompts))]
     outs = engine.generate(prompts, params)
     for i, (p, o) in enumerate(zip(prompts, outs)):
@@ -129,6 +131,8 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--top-p", type=float, default=1.0)
     g.add_argument("--seed", type=int, default=0, help="sampling seed (request i uses seed + i)")
     g.add_argument("--ignore-eos", action="store_true")
+    g.add_argument("--stop", action="append", help="comma-separated token ids; generation stops after this run of "
+                                                    "tokens (may be given several times)")
     g.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     g.add_argument("--device", default="cuda:0")
     g.add_argument("--page-size", type=int, default=16)

@@ -125,8 +125,9 @@ void* vxh_sched_create(void* cache, int max_running, long long max_batch_tokens,
 void vxh_sched_destroy(void* s) { delete (Scheduler*)s; }
 long long vxh_sched_max_model_len(void* s) { return ((Scheduler*)s)->max_model_len(); }
 long long vxh_sched_submit(void* s, const int* prompt, long long n, long long max_tokens, int ignore_eos,
-                           const int* stop_ids, int n_stop) {
-    return ((Scheduler*)s)->submit(prompt, n, max_tokens, ignore_eos != 0, stop_ids, n_stop);
+                           const int* stop_ids, int n_stop, const int* stop_sequences, const int* seq_lens, int n_seqs) {
+    return ((Scheduler*)s)->submit(prompt, n, max_tokens, ignore_eos != 0, stop_ids, n_stop, stop_sequences, seq_lens,
+                                   n_seqs);
 }
 int vxh_sched_has_work(void* s) { return ((Scheduler*)s)->has_work(); }
 // Plans a step.  counts: entries, tokens of all entries, ended, admitted.

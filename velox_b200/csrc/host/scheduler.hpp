@@ -44,6 +44,7 @@ struct Request {
     int64_t max_tokens = 0;
     bool ignore_eos = false;
     std::vector<int> stop_ids;  // end-of-sequence and stop tokens alike end the request
+    std::vector<std::vector<int>> stop_sequences;  // so does a run of generated tokens that equals one of these
     int status = WAITING;
     int finish_reason = NOT_FINISHED;
     int64_t admitted_at = -1;  // admission counter: the latest is preempted first
@@ -85,7 +86,9 @@ public:
     bool has_work() const { return !waiting_.empty() || !running_.empty(); }
 
     // The new request's id, or ERR_REFUSED.
-    int64_t submit(const int* prompt, int64_t n, int64_t max_tokens, bool ignore_eos, const int* stop_ids, int n_stop) {
+    // stop_sequences: n_seqs runs of tokens, concatenated; seq_lens their lengths.
+    int64_t submit(const int* prompt, int64_t n, int64_t max_tokens, bool ignore_eos, const int* stop_ids, int n_stop,
+                   const int* stop_sequences = nullptr, const int* seq_lens = nullptr, int n_seqs = 0) {
         if (n <= 0) {  // the reference rejects an empty prompt too (src/paged/scheduler.rs:165-167)
             ++stats_.requests_refused;
             return fail(ERR_REFUSED, "empty prompt");
@@ -115,6 +118,10 @@ public:
         r->max_tokens = max_tokens;
         r->ignore_eos = ignore_eos;
         r->stop_ids.assign(stop_ids, stop_ids + n_stop);
+        for (int q = 0; q < n_seqs; ++q) {
+            if (seq_lens[q] > 0) r->stop_sequences.emplace_back(stop_sequences, stop_sequences + seq_lens[q]);
+            stop_sequences += seq_lens[q];
+        }
         Request* p = r.get();
         all_.emplace(p->id, std::move(r));
         waiting_.push_back(p);
@@ -171,6 +178,8 @@ public:
             int reason = NOT_FINISHED;
             if (!r->ignore_eos && std::find(r->stop_ids.begin(), r->stop_ids.end(), tok) != r->stop_ids.end())
                 reason = FINISH_STOP;
+            else if (ends_with_stop_sequence(*r))
+                reason = FINISH_STOP;
             else if ((int64_t)r->generated.size() >= r->max_tokens)
                 reason = FINISH_LENGTH;
             else if (r->num_tokens() >= max_model_len_)
@@ -204,6 +213,12 @@ public:
     }
 
 private:
+    static bool ends_with_stop_sequence(const Request& r) {
+        for (const auto& q : r.stop_sequences)
+            if (q.size() <= r.generated.size() && std::equal(q.begin(), q.end(), r.generated.end() - (long)q.size()))
+                return true;
+        return false;
+    }
     int64_t portion_cap() const { return chunk_size_ > 0 ? std::min(max_batch_tokens_, chunk_size_) : max_batch_tokens_; }
     int64_t remaining(const Request* r) { return r->num_tokens() - book_->find(r->id)->length; }
     Request* latest_admitted() {

@@ -217,8 +217,11 @@ class Scheduler:
         params = params or SamplingParams()
         toks = native.int_array(int(t) for t in prompt)
         stops = native.int_array(list(params.eos_token_ids) + list(params.stop_token_ids))
+        seqs = [[int(t) for t in q] for q in params.stop_sequences if len(q)]
+        flat, lens = native.int_array(t for q in seqs for t in q), native.int_array(len(q) for q in seqs)
         rid = native.check(self._lib.vxh_sched_submit(self._sched, toks, len(toks), int(params.max_tokens),
-                                                      1 if params.ignore_eos else 0, stops, len(stops)))
+                                                      1 if params.ignore_eos else 0, stops, len(stops),
+                                                      flat, lens, len(seqs)))
         self._params[rid] = params
         return rid
 

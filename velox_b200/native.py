@@ -81,7 +81,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "vxh_build_step": (I, [P, I, PI64, PI, PI, PI, PI, I, c_void_p, PI64, PI64]),
         "vxh_fill_decode": (I, [P, I, I, PI64, PI, I, c_void_p, PI64, PI64]),
         "vxh_sched_create": (P, [P, I, L, L, L]), "vxh_sched_destroy": (None, [P]),
-        "vxh_sched_max_model_len": (L, [P]), "vxh_sched_submit": (L, [P, PI, L, L, I, PI, I]),
+        "vxh_sched_max_model_len": (L, [P]), "vxh_sched_submit": (L, [P, PI, L, L, I, PI, I, PI, PI, I]),
         "vxh_sched_has_work": (I, [P]), "vxh_sched_plan": (I, [P, POINTER(c_longlong)]),
         "vxh_sched_plan_entries": (I, [P, PI64, PI64, PI64, PI, PI]), "vxh_sched_plan_ended": (I, [P, PI64]),
         "vxh_sched_plan_admitted": (I, [P, PI64, PI]),

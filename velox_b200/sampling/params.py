@@ -25,6 +25,11 @@ class SamplingParams:
     # reference: src/paged/scheduler.rs:426, 465-470)
     eos_token_ids: List[int] = field(default_factory=list)
     stop_token_ids: List[int] = field(default_factory=list)
+    # ... or after a run of generated tokens that equals one of these.  The
+    # reference's `stop_sequences` are strings searched in the decoded text
+    # (src/backend/traits.rs:39, src/backend/candle.rs:798-799); the engine sees
+    # token ids only, so these are runs of token ids.
+    stop_sequences: List[List[int]] = field(default_factory=list)
     ignore_eos: bool = False
 
     def __post_init__(self) -> None:
