@@ -147,3 +147,36 @@ def test_graphs_of_an_engine_that_is_gone_do_not_disturb_a_capture(model_folders
         assert e2.generate([prompt], SamplingParams(max_tokens=6)) == [want]
     finally:
         gc.enable()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_random_workloads_generate_what_the_plain_implementation_does(model_folders, dtype):
+    """Scheduler, portions, preemption and captured decode steps together: random
+    requests, pools from barely enough to ample, budgets from 8 tokens a step."""
+    import random
+    from velox_b200 import Engine, EngineConfig, SamplingParams
+    models = {n: P.load_model_folder(f) for n, f in model_folders.items()}
+    preemptions = 0
+    for seed in range(24):
+        rng = random.Random(seed)
+        name = rng.choice(sorted(model_folders))
+        cfg, w = models[name]
+        page = TINY[name]["page_size"]
+        prompts = [random_tokens(cfg["vocab_size"], rng.choice([1, 2, 5, 17, 40, 77, 130]), 1000 * seed + i)
+                   for i in range(rng.randint(1, 7))]
+        new = [rng.choice([1, 3, 9, 20]) for _ in prompts]
+        longest = max(len(p) + n for p, n in zip(prompts, new))
+        total = sum(len(p) + n for p, n in zip(prompts, new))
+        pool = rng.choice([longest + page, max(longest + page, total // 2), total + 64])
+        e = Engine(model_folders[name], EngineConfig(
+            dtype=dtype, page_size=page, num_pages=-(-pool // page), max_running_requests=rng.choice([2, 4, 8]),
+            max_batch_tokens=rng.choice([8, 32, 64, 256]), chunk_size=rng.choice([None, 3, 16, 50]),
+            max_model_len=longest + page))
+        outs = e.generate(prompts, [SamplingParams(max_tokens=n, ignore_eos=True) for n in new])
+        for p, n, o in zip(prompts, new, outs):
+            assert len(o) == n
+            check_greedy_path(cfg, w, p, o, dtype)
+        e.cache.check()
+        assert e.cache.free_pages() == [g.allocator.num_pages for g in e.cache.groups]
+        preemptions += e.stats()["preemptions"]
+    assert preemptions > 0, "no workload ran out of pages: the test lost its point"

@@ -211,3 +211,45 @@ def test_sizes_that_no_fast_kernel_takes(tmp_path, name, dtype):
     assert sorted(got) == sorted(tr.expect)
     for n in sorted(tr.expect):
         assert_close(got[n], tr.expect[n], dtype, "%s %s step %d" % (name, dtype, n))
+
+
+@pytest.mark.parametrize("seed", [3, 11, 26])
+def test_random_traces(model_folders, tmp_path, seed):
+    """Requests cut at random: which of up to four live requests go into a step, how
+    many tokens each brings (1 to all that is left), which places are wanted, and in
+    which order they stand in the step are all drawn; later requests start in the pages
+    earlier ones gave back."""
+    import random
+    rng = random.Random(seed)
+    name = rng.choice(sorted(TINY))
+    cfg, w = P.load_model_folder(model_folders[name])
+    lens = [rng.choice([1, 2, 3, 17, 40, 64, 65, 100, 130, 257, 300]) for _ in range(rng.randint(3, 8))]
+    seqs = {"q%d" % i: random_tokens(cfg["vocab_size"], L, 7000 * seed + i) for i, L in enumerate(lens)}
+    plain = {i: P.forward_logits(cfg, w, t) for i, t in seqs.items()}
+    waiting, live, steps, expect = list(seqs), {}, [], {}
+    while waiting or live:
+        while waiting and len(live) < 4 and (not live or rng.random() < 0.7):
+            live[waiting.pop(0)] = 0
+        entries, end, rows = [], [], []
+        order = list(live)
+        rng.shuffle(order)
+        for i in order:
+            if len(live) > 1 and rng.random() < 0.25:
+                continue  # sits this step out
+            k = min(len(seqs[i]) - live[i], rng.choice([1, 1, 1, 2, 3, 5, 8, 13, 31, 32, 33, 64, 100, 1000]))
+            want = sorted(rng.sample(range(k), rng.choice([0, 1, min(k, 3), k])))
+            entries.append({"id": i, "tokens": seqs[i][live[i]:live[i] + k], "want": want})
+            rows += [plain[i][live[i] + w_] for w_ in want]
+            live[i] += k
+            if live[i] == len(seqs[i]):
+                end.append(i)
+                del live[i]
+        steps.append({"step": len(steps), "entries": entries, "end": end})
+        if rows:
+            expect[len(steps) - 1] = np.stack(rows)
+    pool = sum(sorted(-(-L // 64) * 64 for L in lens)[-4:])
+    for dtype in ("float32", "bfloat16"):
+        got = run_trace(model_folders[name], dtype, steps, pool, str(tmp_path / dtype), page_size=TINY[name]["page_size"])
+        assert sorted(got) == sorted(expect)
+        for n in sorted(expect):
+            assert_close(got[n], expect[n], dtype, "%s %s seed %d step %d" % (name, dtype, seed, n))
