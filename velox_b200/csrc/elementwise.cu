@@ -115,15 +115,22 @@ add_rmsnorm_vec_kernel(const float* __restrict__ residual_in, const T* __restric
                        const int* __restrict__ row_index, float* __restrict__ residual_out,
                        const float* __restrict__ weight, T* __restrict__ out, int width, float eps) {
     __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int chunks = width >> 3;
+    // the norm's weights depend on no earlier kernel: they are asked for before the wait
+    float w[ITER][8];
+#pragma unroll
+    for (int i = 0; i < ITER; ++i) {
+        const int c = threadIdx.x + i * RN_THREADS;
+        if (c < chunks) load8(weight + c * 8, w[i]);
+    }
     pdl_wait();
     pdl_trigger();
-    const int r = blockIdx.x;
     const int s = row_index ? row_index[r] : r;
     const float* xin = residual_in + (size_t)s * width;
     const T* din = delta ? delta + (size_t)s * width : nullptr;
     float* xout = residual_out ? residual_out + (size_t)r * width : nullptr;
     T* o = out + (size_t)r * width;
-    const int chunks = width >> 3;
     float x[ITER][8];
     float ss = 0.f;
 #pragma unroll
@@ -148,10 +155,9 @@ add_rmsnorm_vec_kernel(const float* __restrict__ residual_in, const T* __restric
     for (int i = 0; i < ITER; ++i) {
         const int c = threadIdx.x + i * RN_THREADS;
         if (c < chunks) {
-            float w[8], y[8];
-            load8(weight + c * 8, w);
+            float y[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) y[j] = x[i][j] * rstd * w[j];
+            for (int j = 0; j < 8; ++j) y[j] = x[i][j] * rstd * w[i][j];
             store8(o + c * 8, y);
         }
     }

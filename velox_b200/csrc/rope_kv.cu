@@ -101,15 +101,29 @@ qk_norm_rope_kv_128_kernel(bf16* __restrict__ qkv, int row_stride, const float* 
                            const float* __restrict__ k_weight, float eps, const float* __restrict__ inv_freq,
                            const int* __restrict__ positions, const int* __restrict__ slot_mapping,
                            bf16* __restrict__ k_pool, bf16* __restrict__ v_pool, int H, int Hk, int S) {
-    pdl_wait();
-    pdl_trigger();
     constexpr int D = 128;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
     const int head = blockIdx.y * ROPE128_WARPS + warp;
-    if (head >= H + 2 * Hk) return;
+    // What depends on no earlier kernel is fetched before the wait: the norm's weights, the
+    // frequencies, and the step's description (copied to the device before the step's first kernel).
+    const bool in_range = head < H + 2 * Hk;
+    const bool is_q = head < H;
+    const float* w = is_q ? q_weight : k_weight;
+    float2 wl = make_float2(1.f, 1.f), wh = wl, f = make_float2(0.f, 0.f);
+    float pos = 0.f;
+    int slot = -1;
+    if (in_range) {
+        slot = slot_mapping ? slot_mapping[t] : -1;
+        if (head < H + Hk) {
+            if (w) { wl = reinterpret_cast<const float2*>(w)[lane]; wh = reinterpret_cast<const float2*>(w + 64)[lane]; }
+            if (inv_freq) { f = reinterpret_cast<const float2*>(inv_freq)[lane]; pos = (float)positions[t]; }
+        }
+    }
+    pdl_wait();
+    pdl_trigger();
+    if (!in_range) return;
     bf16* src = qkv + (size_t)t * row_stride + (size_t)head * D;
-    const int slot = slot_mapping ? slot_mapping[t] : -1;
     if (head >= H + Hk) {  // value head: copy into the cache (8 bytes per lane)
         if (slot < 0) return;
         const int hk = head - H - Hk;
@@ -117,21 +131,16 @@ qk_norm_rope_kv_128_kernel(bf16* __restrict__ qkv, int row_stride, const float* 
         reinterpret_cast<uint2*>(dst)[lane] = reinterpret_cast<const uint2*>(src)[lane];
         return;
     }
-    const bool is_q = head < H;
     if (!is_q && slot_mapping && slot < 0) return;
-    const float* w = is_q ? q_weight : k_weight;
     float2 lo = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(src)[lane]);
     float2 hi = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(src + 64)[lane]);
     if (w) {
         const float ss = warp_sum(head128_squares(lo, hi));
         const float rstd = rsqrtf(ss / (float)D + eps);
-        const float2 wl = reinterpret_cast<const float2*>(w)[lane], wh = reinterpret_cast<const float2*>(w + 64)[lane];
         lo.x = __fmul_rn(__fmul_rn(lo.x, rstd), wl.x); lo.y = __fmul_rn(__fmul_rn(lo.y, rstd), wl.y);
         hi.x = __fmul_rn(__fmul_rn(hi.x, rstd), wh.x); hi.y = __fmul_rn(__fmul_rn(hi.y, rstd), wh.y);
     }
     if (inv_freq) {
-        const float pos = (float)positions[t];
-        const float2 f = reinterpret_cast<const float2*>(inv_freq)[lane];
         float sn, cs, a0, b0, a1, b1;
         sincosf(__fmul_rn(pos, f.x), &sn, &cs);
         rotate_pair(lo.x, hi.x, cs, sn, a0, b0);
