@@ -19,6 +19,11 @@
 // what else is in the step.  Blocks are four warps = four consecutive pieces;
 // grid (pieces / 4, kv head, request).
 //
+// Launched programmatically (see common.cuh) a warp asks for its first tiles before it
+// waits for the kernel before it, unless they reach the request's newest position: the
+// only thing that kernel may write into the pools is the key and value at position
+// kv_len - 1 of each request (which is what writing the step's new tokens does).
+//
 // Sizes: head size 64 or 128; page size a multiple of 16; group size up to 16;
 // any number of heads; an optional window.  Other sizes are refused (the caller
 // then uses the general kernel).
@@ -65,8 +70,10 @@ paged_decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, cons
     if (lane < count) my_page = bt[((tile_begin + lane) << 4) / S];
 
     unsigned char* my_smem = smem_raw + (size_t)warp * DEC_STAGES * 2 * TILE_BYTES;
-    pdl_wait();
-    pdl_trigger();
+    // The tiles asked for first hold keys and values of earlier steps, unless they reach the
+    // request's newest position (which the kernel before this one has just written, or is
+    // still writing): only then do they have to wait for that kernel.
+    const bool early = ((tile_begin + DEC_STAGES - 1) << 4) <= kv_len - 1;
 
     auto issue = [&](int j) {
         const int key0 = (tile_begin + j) << 4;
@@ -85,10 +92,21 @@ paged_decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, cons
             cp_async16(vs + dst, vg + (size_t)c * 16);
         }
     };
+    if (early) {
 #pragma unroll
-    for (int s = 0; s < DEC_STAGES - 1; ++s) {
-        if (s < count) issue(s);
-        cp_async_commit();
+        for (int s = 0; s < DEC_STAGES - 1; ++s) {
+            if (s < count) issue(s);
+            cp_async_commit();
+        }
+    }
+    pdl_wait();
+    pdl_trigger();
+    if (!early) {
+#pragma unroll
+        for (int s = 0; s < DEC_STAGES - 1; ++s) {
+            if (s < count) issue(s);
+            cp_async_commit();
+        }
     }
 
     // queries of the group: rows of the A operand, kept in registers
