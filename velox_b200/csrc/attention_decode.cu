@@ -254,6 +254,7 @@ paged_decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, cons
 // Joins the pieces of requests that have several: one block per (request, head),
 // pieces added in piece order.
 #define JOIN_MAX_PIECES 1024
+#define JOIN_EARLY 16   // pieces whose values a thread asks for before it knows their weights
 template <int D>
 __global__ void paged_decode_join_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          int max_pieces, const int* __restrict__ token_rows,
@@ -269,6 +270,12 @@ __global__ void paged_decode_join_kernel(const float* __restrict__ part_o, const
     pdl_trigger();
     if (npieces <= 1) return;  // written by the first pass
     const size_t p0 = ((size_t)b * H + h) * max_pieces;
+    // this thread's element of the first pieces is on its way while the weights are formed
+    const int d0 = threadIdx.x;
+    float first[JOIN_EARLY];
+#pragma unroll
+    for (int u = 0; u < JOIN_EARLY; ++u)
+        first[u] = (d0 < D && u < npieces) ? part_o[(p0 + u) * D + d0] : 0.f;
     // weights of the pieces, once per block: w_s = 2^(m_s - M), and L = sum w_s l_s
     // in piece order (so the result does not depend on the number of threads)
     __shared__ float wgt[JOIN_MAX_PIECES];
@@ -295,6 +302,12 @@ __global__ void paged_decode_join_kernel(const float* __restrict__ part_o, const
         const float* po = part_o + p0 * D + d;
         float O = 0.f;
         int s = 0;
+        if (d == d0) {  // (always, for a block as wide as the head)
+#pragma unroll
+            for (int u = 0; u < JOIN_EARLY; ++u)
+                if (u < npieces) O += wgt[u] * first[u];
+            s = min(npieces, JOIN_EARLY);
+        }
         for (; s + 8 <= npieces; s += 8) {  // eight independent loads at a time, added in piece order
             float v[8];
 #pragma unroll

@@ -124,25 +124,36 @@ add_rmsnorm_vec_kernel(const float* __restrict__ residual_in, const T* __restric
         const int c = threadIdx.x + i * RN_THREADS;
         if (c < chunks) load8(weight + c * 8, w[i]);
     }
-    pdl_wait();
-    pdl_trigger();
-    const int s = row_index ? row_index[r] : r;
+    const int s = row_index ? row_index[r] : r;   // (the step's description: on the device before the step's first kernel)
     const float* xin = residual_in + (size_t)s * width;
     const T* din = delta ? delta + (size_t)s * width : nullptr;
     float* xout = residual_out ? residual_out + (size_t)r * width : nullptr;
     T* o = out + (size_t)r * width;
     float x[ITER][8];
+    // With a delta, the delta is what the kernel before this one wrote; the residual is older
+    // (the delta was computed from it) and is read before the wait.  Without one the residual
+    // itself may be that kernel's output (the embedding), and everything waits.
+    if (din) {
+#pragma unroll
+        for (int i = 0; i < ITER; ++i) {
+            const int c = threadIdx.x + i * RN_THREADS;
+            if (c < chunks) load8(xin + c * 8, x[i]);
+        }
+    }
+    pdl_wait();
+    pdl_trigger();
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < ITER; ++i) {
         const int c = threadIdx.x + i * RN_THREADS;
         if (c < chunks) {
-            load8(xin + c * 8, x[i]);
             if (din) {
                 float d[8];
                 load8(din + c * 8, d);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) x[i][j] += d[j];
+            } else {
+                load8(xin + c * 8, x[i]);
             }
             if (xout) store8(xout + c * 8, x[i]);
 #pragma unroll

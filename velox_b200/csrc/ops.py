@@ -157,6 +157,11 @@ def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: t
                 residual_out: Optional[torch.Tensor] = None, update_residual: bool = True) -> torch.Tensor:
     """normed = rmsnorm(residual (+ delta)) rounded to `out_dtype`.
 
+    With a delta, the residual must be older than the delta: not something the
+    kernel launched just before this one writes (the kernel reads it before it
+    waits for that kernel; in a decoder the delta is computed from the residual,
+    so this holds by itself).
+
     Without `rows` the sum is written back into `residual` (if there is a delta
     and `update_residual`).  With `rows` (int32 indices) only those rows are
     read, and the sums go to `residual_out` if given."""
