@@ -180,3 +180,29 @@ def test_random_workloads_generate_what_the_plain_implementation_does(model_fold
         assert e.cache.free_pages() == [g.allocator.num_pages for g in e.cache.groups]
         preemptions += e.stats()["preemptions"]
     assert preemptions > 0, "no workload ran out of pages: the test lost its point"
+
+
+def test_an_engine_ends_when_it_is_dropped(model_folders):
+    """No reference cycle holds an engine: its cache pool, graphs and host-side books
+    are gone when the last reference is, without waiting for the garbage collector."""
+    import gc
+    import weakref
+    import torch
+    from velox_b200 import SamplingParams
+    gc.collect()
+    gc.disable()
+    try:
+        torch.cuda.synchronize()
+        before = torch.cuda.memory_allocated()
+        e = engine(model_folders["tiny_a"], "tiny_a", "bfloat16", num_pages=4096)
+        e.generate([[1, 2, 3]], SamplingParams(max_tokens=4))
+        assert torch.cuda.memory_allocated() > before
+        alive = [weakref.ref(e), weakref.ref(e.cache), weakref.ref(e.scheduler), weakref.ref(e.runner)]
+        pool = e.cache.groups[0].allocator
+        del e
+        assert [r() for r in alive] == [None] * 4
+        with pytest.raises(ReferenceError):
+            pool.num_free                      # a pool of a manager that is gone says so
+        assert torch.cuda.memory_allocated() <= before
+    finally:
+        gc.enable()

@@ -28,6 +28,7 @@ books.
 from __future__ import annotations
 
 import ctypes
+import weakref
 from dataclasses import dataclass, field
 from typing import Dict, Iterator, List, Mapping, Optional, Sequence
 
@@ -74,7 +75,7 @@ class _Requests(Mapping):
     """`manager.requests`: request id -> `RequestCache` (a copy made at the lookup)."""
 
     def __init__(self, manager: "CacheManager"):
-        self._m = manager
+        self._m = weakref.proxy(manager)  # (the manager holds this view: no cycle, so it ends when dropped)
 
     def __getitem__(self, request_id) -> RequestCache:
         m = self._m
@@ -130,9 +131,9 @@ class CacheManager:
                                                                 int(num_pages), int(max_requests), self.max_blocks))
         if not self._book:
             raise ValueError("page size, pages, requests and blocks per request must be positive")
-        self.slots = SlotAllocator(0, _borrowed=self._lib.vxh_cache_slots(self._book))
+        self.slots = SlotAllocator(0, _borrowed=self._lib.vxh_cache_slots(self._book), _owner=self)
         for g, (spec, layers) in enumerate(zip(specs_of_groups, layers_of_groups)):
-            self.groups.append(CacheGroup(spec, layers, PageAllocator(0, _borrowed=self._lib.vxh_cache_pool(self._book, g))))
+            self.groups.append(CacheGroup(spec, layers, PageAllocator(0, _borrowed=self._lib.vxh_cache_pool(self._book, g), _owner=self)))
         # request ids: non-negative integers are their own handle in the library
         # (the scheduler's ids are such), anything else gets a negative one
         self._handles: Dict[object, int] = {}

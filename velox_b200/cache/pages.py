@@ -13,6 +13,7 @@ classes own one, or look into one that a `CacheManager` owns.
 from __future__ import annotations
 
 import ctypes
+import weakref
 from typing import Iterable, List, Optional
 
 from .. import native
@@ -20,8 +21,11 @@ from ..native import CacheAccountingError  # noqa: F401  (part of this module's 
 
 
 class PageAllocator:
-    def __init__(self, num_pages: int, _borrowed: Optional[int] = None):
+    def __init__(self, num_pages: int, _borrowed: Optional[int] = None, _owner=None):
         self._lib = native.library()
+        # a pool inside a cache manager's books lives as long as that manager: a weak
+        # proxy to it turns a use after its end into a ReferenceError, not a bad pointer
+        self._owner = weakref.proxy(_owner) if _owner is not None else None
         if _borrowed is not None:
             self._pool, self._owned = ctypes.c_void_p(_borrowed), False
         else:
@@ -35,30 +39,40 @@ class PageAllocator:
             self._lib.vxh_pages_destroy(self._pool)
             self._pool = None
 
+    def _alive(self) -> None:
+        if self._owner is not None:
+            self._owner.page_size  # raises ReferenceError once the manager is gone
+
     @property
     def num_free(self) -> int:
+        self._alive()
         return self._lib.vxh_pages_num_free(self._pool)
 
     def alloc(self, n: int) -> Optional[List[int]]:
         """n pages with count 1, or None (and nothing taken) if fewer are free."""
+        self._alive()
         if n < 0:
             raise ValueError("cannot allocate %d pages" % n)
         out = (ctypes.c_int * max(n, 1))()
         return list(out[:n]) if native.check(self._lib.vxh_pages_alloc(self._pool, n, out)) else None
 
     def incref(self, pages: Iterable[int]) -> None:
+        self._alive()
         arr = native.int_array(pages)
         native.check(self._lib.vxh_pages_incref(self._pool, arr, len(arr)))
 
     def free(self, pages: Iterable[int]) -> None:
+        self._alive()
         arr = native.int_array(pages)
         native.check(self._lib.vxh_pages_free(self._pool, arr, len(arr)))
 
     def refcount(self, page: int) -> int:
+        self._alive()
         return native.check(self._lib.vxh_pages_refcount(self._pool, int(page)))
 
     def free_list(self) -> List[int]:
         """The free ids, the next one handed out last."""
+        self._alive()
         out = (ctypes.c_int * self.num_pages)()
         n = self._lib.vxh_pages_free_list(self._pool, out, self.num_pages)
         return list(out[:n])
@@ -67,8 +81,9 @@ class PageAllocator:
 class SlotAllocator:
     """Slots for per-request state of fixed size; the lowest free slot first."""
 
-    def __init__(self, num_slots: int, _borrowed: Optional[int] = None):
+    def __init__(self, num_slots: int, _borrowed: Optional[int] = None, _owner=None):
         self._lib = native.library()
+        self._owner = weakref.proxy(_owner) if _owner is not None else None
         if _borrowed is not None:
             self._pool, self._owned = ctypes.c_void_p(_borrowed), False
         else:
@@ -82,13 +97,20 @@ class SlotAllocator:
             self._lib.vxh_slots_destroy(self._pool)
             self._pool = None
 
+    def _alive(self) -> None:
+        if self._owner is not None:
+            self._owner.page_size
+
     @property
     def num_free(self) -> int:
+        self._alive()
         return self._lib.vxh_slots_num_free(self._pool)
 
     def alloc(self) -> Optional[int]:
+        self._alive()
         s = self._lib.vxh_slots_alloc(self._pool)
         return None if s < 0 else s
 
     def free(self, slot: int) -> None:
+        self._alive()
         native.check(self._lib.vxh_slots_free(self._pool, int(slot)))

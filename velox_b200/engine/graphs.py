@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import ctypes
 import gc
+import weakref
 from typing import Dict, Optional, Sequence, Tuple
 
 import numpy as np
@@ -112,7 +113,7 @@ class _Graph:
 
 class DecodeGraphs:
     def __init__(self, runner):
-        self.runner = runner
+        self.runner = weakref.proxy(runner)  # (the runner holds these graphs: no cycle, they end with it)
         self.graphs: Dict[Tuple[int, int], _Graph] = {}
         self.pool = None
         cache = runner.cache

@@ -35,6 +35,7 @@ shows requests and queues as views that ask the library when they are read.
 from __future__ import annotations
 
 import ctypes
+import weakref
 from dataclasses import dataclass
 from typing import Dict, Iterator, List, Mapping, Optional, Sequence, Tuple
 
@@ -112,7 +113,8 @@ class Request:
         return info[0] + info[1]
 
     def __eq__(self, other) -> bool:
-        return isinstance(other, Request) and other._s is self._s and other.request_id == self.request_id
+        return (isinstance(other, Request) and other.request_id == self.request_id
+                and other._s._sched.value == self._s._sched.value)
 
     def __hash__(self) -> int:
         return hash(self.request_id)
@@ -137,7 +139,7 @@ class _Queue(Mapping):
     """`scheduler.running` / `scheduler.finished`: request id -> `Request`, by id."""
 
     def __init__(self, scheduler: "Scheduler", which: int):
-        self._s, self._which = scheduler, which
+        self._s, self._which = weakref.proxy(scheduler), which  # (the scheduler holds this view: no cycle)
 
     def _ids(self) -> List[int]:
         s = self._s
