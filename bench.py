@@ -245,7 +245,7 @@ def main() -> int:
         torch.cuda.synchronize()
         return a.elapsed_time(b) / steps
 
-    def decode_run(batch, steps, warmup):
+    def decode_run(batch, steps, warmup, context=CONTEXT):
         """`batch` requests prefilled so that the timed steps end at the context
         length.  Times `steps` steps through the public entry point (host ids in,
         sampled ids out, every step), then `steps` steps of the step function and
@@ -256,8 +256,8 @@ def main() -> int:
         # are still going in (2,048 new tokens a step), so the first one decodes
         # `stagger` tokens more than the last; it is the one that ends at CONTEXT.
         budget = 2 * steps + warmup + 1
-        stagger = -(-batch * CONTEXT // 2048) + 2 if batch > 1 else 0
-        start = CONTEXT - budget - stagger
+        stagger = -(-batch * context // 2048) + 2 if batch > 1 else 0
+        start = context - budget - stagger
         sp = SamplingParams(max_tokens=budget + stagger, ignore_eos=True)
         for p in prompts(batch, start):
             engine.add_request(p, SamplingParams(**vars(sp)))
@@ -277,7 +277,7 @@ def main() -> int:
         n0 = ops.launch_count()
         dev_ms = timed(device_step, steps)
         launches = (ops.launch_count() - n0) // steps
-        assert max(engine.cache.length(r) for r in engine.scheduler.running) <= CONTEXT
+        assert max(engine.cache.length(r) for r in engine.scheduler.running) <= context
         for r in list(engine.scheduler.running.values()):
             engine.scheduler._finish(r, "length")
         return e2e_ms, dev_ms, launches, held + steps / 2.0
@@ -316,10 +316,13 @@ def main() -> int:
         out["prefill"] = {"value": round(PROMPT * 1000.0 / pms, 1), "tokens": PROMPT, "ms": round(pms, 3),
                           "frac": round(fl / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
         pts = {}
+        steps = min(K, 32)
         for b in (1, 64):
-            steps = min(K, 32)
             _, m, _, _ = decode_run(b, steps, 4)
             pts["decode_b%d" % b] = round(b * 1000.0 / m, 1)
+        for b in (1, args.batch, 64):  # the same with half the context behind each request
+            _, m, _, _ = decode_run(b, steps, 4, context=CONTEXT // 2)
+            pts["decode_b%d_ctx%d" % (b, CONTEXT // 2)] = round(b * 1000.0 / m, 1)
         out["points"] = pts
 
     out["config"] = {"model": "Qwen3-%s shape" % args.shape.upper(), "layers": layers,
