@@ -16,12 +16,22 @@
 //
 // Piece boundaries depend only on the request's own key range (fixed number of
 // keys per piece), never on the batch, so a request's output does not depend on
-// what else is in the step.  Blocks are four warps = four consecutive pieces;
-// grid (pieces / 4, kv head, request).  A warp keeps two tiles in flight (three
-// stages), so that two blocks fit on an SM; a step with no more blocks than SMs
-// keeps five (six stages): with one block on an SM, two tiles per warp do not cover
-// the memory's latency (batch 8 at 1,900 keys: a step of 6 layers 0.770 instead of
-// 0.819 ms).  The stages change nothing in what a warp computes.
+// what else is in the step.
+//
+// How the pieces are spread over blocks changes nothing in what a warp computes, so
+// it is chosen per launch.  The pieces of the step are numbered (request, kv head,
+// piece); a block of W warps takes W consecutive numbers.  What bounds the kernel is
+// how many tiles are in flight against the memory's latency, so the shapes are made
+// to fill the SMs' shared memory:
+//   - up to 4 pieces per SM: blocks of 4 warps with 6 stages (5 tiles in flight per
+//     warp), one block an SM (batch 8 at 1,900 keys: a step of 6 layers 0.770
+//     instead of 0.819 ms with 3 stages);
+//   - up to 5 or 6 pieces per SM: one wave of blocks of 5 warps with 5 stages or 6
+//     warps with 4, so that every SM holds the same number of pieces, give or take
+//     one (batch 5 and 6 at 4,000 keys: 2 and 3 % faster steps);
+//   - more: blocks of 4 warps with 3 stages, two blocks an SM.  One wave of 7 warps
+//     with 4 stages (224 KB, which leaves no room on the SM for a block of the
+//     kernel before or after) made a step at batch 8 and 4,000 keys 14 % slower.
 //
 // Launched programmatically (see common.cuh) a warp asks for its first tiles before it
 // waits for the kernel before it, unless they reach the request's newest position: the
@@ -34,13 +44,12 @@
 #include "common.cuh"
 #include "mma_helpers.cuh"
 
-#define DEC_WARPS 4
 #define LOG2E 1.4426950408889634f
 
-// Shared memory of a block: per warp, DEC_STAGES (3 or 6) stages of a K tile and a V tile
+// Shared memory of a block: per warp, DEC_STAGES (3 to 6) stages of a K tile and a V tile
 // [16 keys][D] bf16, 16-byte chunks of a row XOR-swizzled with the row index so
 // that ldmatrix reads hit distinct banks.
-template <int D, int DEC_STAGES>
+template <int D, int DEC_STAGES, int DEC_WARPS>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 paged_decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __restrict__ k_pool,
                               const bf16* __restrict__ v_pool, const int* __restrict__ block_table,
@@ -48,12 +57,14 @@ paged_decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, cons
                               const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                               float* __restrict__ part_o, float* __restrict__ part_ml, int max_pieces,
                               bf16* __restrict__ out, int out_row_stride, float scale_log2, int window,
-                              int H, int Hk, int S, int piece_tiles) {
+                              int H, int Hk, int S, int piece_tiles, int requests) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     constexpr int TILE_BYTES = 16 * D * 2;
     constexpr int CHUNKS_PER_ROW = D / 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int piece = blockIdx.x * DEC_WARPS + warp, hk = blockIdx.y, b = blockIdx.z;
+    const int number = (int)blockIdx.x * DEC_WARPS + warp, per_request = Hk * max_pieces;
+    if (number >= requests * per_request) return;  // (no barrier follows: a warp may leave alone)
+    const int b = number / per_request, hk = (number % per_request) / max_pieces, piece = number % max_pieces;
     const int G = H / Hk;
     // The step's description was copied to the device before any kernel of the
     // step ran, so it may be read before the wait on earlier kernels.
@@ -64,7 +75,7 @@ paged_decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, cons
     const int tile_first = start >> 4;
     const int tile_last = (kv_len + 15) >> 4;  // exclusive
     const int npieces = (tile_last - tile_first + piece_tiles - 1) / piece_tiles;
-    if (piece >= npieces) return;  // (no barrier follows: a warp may leave alone)
+    if (piece >= npieces) return;
     const int tile_begin = tile_first + piece * piece_tiles;
     const int count = min(piece_tiles, tile_last - tile_begin);
     const int* bt = block_table + (size_t)seq * max_blocks;
@@ -340,23 +351,23 @@ static int dec_sm_count() {
     return sms;
 }
 
-template <int D, int STAGES>
-static int launch_decode_pieces(dim3 grid, const bf16* q, int q_row_stride, const bf16* k_pool, const bf16* v_pool,
+template <int D, int STAGES, int WARPS>
+static int launch_decode_pieces(int blocks, const bf16* q, int q_row_stride, const bf16* k_pool, const bf16* v_pool,
                                 const int* block_table, int max_blocks, const int* token_rows,
                                 const int* seq_of_token, const int* positions, float* part_o, float* part_ml,
-                                int max_pieces, bf16* out, int out_row_stride, float scale, int window, int H, int Hk,
-                                int S, int piece_tiles, cudaStream_t stream) {
-    const size_t smem = (size_t)DEC_WARPS * STAGES * 2 * 16 * D * 2;
+                                int max_pieces, bf16* out, int out_row_stride, float scale, int window, int requests,
+                                int H, int Hk, int S, int piece_tiles, cudaStream_t stream) {
+    const size_t smem = (size_t)WARPS * STAGES * 2 * 16 * D * 2;
     static bool configured = false;  // per process and instantiation; the attribute is per device function
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(paged_decode_attention_kernel<D, STAGES>,
+        cudaError_t e = cudaFuncSetAttribute(paged_decode_attention_kernel<D, STAGES, WARPS>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    VX_LAUNCH_K(VX_K_ATTENTION, (paged_decode_attention_kernel<D, STAGES>), grid, DEC_WARPS * 32, smem, stream, q,
-                q_row_stride, k_pool, v_pool, block_table, max_blocks, token_rows, seq_of_token, positions, part_o,
-                part_ml, max_pieces, out, out_row_stride, scale * LOG2E, window, H, Hk, S, piece_tiles);
+    VX_LAUNCH_K(VX_K_ATTENTION, (paged_decode_attention_kernel<D, STAGES, WARPS>), dim3(blocks), WARPS * 32, smem, stream,
+                q, q_row_stride, k_pool, v_pool, block_table, max_blocks, token_rows, seq_of_token, positions, part_o,
+                part_ml, max_pieces, out, out_row_stride, scale * LOG2E, window, H, Hk, S, piece_tiles, requests);
     VX_LAUNCH_CHECK();
     return VX_OK;
 }
@@ -369,18 +380,21 @@ static int launch_decode(const bf16* q, int q_row_stride, const bf16* k_pool, co
                          int S, int piece_tiles, cudaStream_t stream) {
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)requests * H * max_pieces * D : nullptr;
-    dim3 grid((max_pieces + DEC_WARPS - 1) / DEC_WARPS, Hk, requests);
-    // A step with no more blocks than SMs has one block (four warps) on an SM: two tiles in
-    // flight per warp do not cover the memory's latency then, five do.  Larger steps keep three
-    // stages, so that two blocks fit on an SM.
-    const bool deep = (long long)grid.x * grid.y * grid.z <= dec_sm_count();
-    const int rc = deep
-        ? launch_decode_pieces<D, 6>(grid, q, q_row_stride, k_pool, v_pool, block_table, max_blocks, token_rows,
-                                     seq_of_token, positions, part_o, part_ml, max_pieces, out, out_row_stride, scale,
-                                     window, H, Hk, S, piece_tiles, stream)
-        : launch_decode_pieces<D, 3>(grid, q, q_row_stride, k_pool, v_pool, block_table, max_blocks, token_rows,
-                                     seq_of_token, positions, part_o, part_ml, max_pieces, out, out_row_stride, scale,
-                                     window, H, Hk, S, piece_tiles, stream);
+    const long long pieces = (long long)requests * Hk * max_pieces, sms = dec_sm_count();
+    int warps = 4, stages = 3;
+    if (pieces <= 4 * sms) stages = 6;
+    else if (pieces <= 5 * sms) warps = 5, stages = 5;
+    else if (pieces <= 6 * sms) warps = 6, stages = 4;
+    const int blocks = (int)((pieces + warps - 1) / warps);
+#define DEC_LAUNCH(ST, W)                                                                                            \
+    launch_decode_pieces<D, ST, W>(blocks, q, q_row_stride, k_pool, v_pool, block_table, max_blocks, token_rows,       \
+                                   seq_of_token, positions, part_o, part_ml, max_pieces, out, out_row_stride, scale, \
+                                   window, requests, H, Hk, S, piece_tiles, stream)
+    int rc;
+    if (warps == 5) rc = DEC_LAUNCH(5, 5);
+    else if (warps == 6) rc = DEC_LAUNCH(4, 6);
+    else rc = stages == 6 ? DEC_LAUNCH(6, 4) : DEC_LAUNCH(3, 4);
+#undef DEC_LAUNCH
     if (rc != VX_OK) return rc;
     if (max_pieces > 1) {
         dim3 jgrid(requests, H);
@@ -406,6 +420,7 @@ extern "C" int vx_paged_decode_attention(const void* q, int q_row_stride, const 
     if (H <= 0 || Hk <= 0 || H % Hk || H / Hk > 16 || S <= 0 || S % 16 || window < 0) return VX_ERR_SHAPE;
     if (piece_tiles <= 0 || piece_tiles > 32 || max_pieces <= 0 || (max_pieces > 1 && !scratch)) return VX_ERR_SHAPE;
     if (Hk > 65535 || requests > 65535 || max_pieces > JOIN_MAX_PIECES) return VX_ERR_LIMIT;
+    if ((long long)requests * Hk * max_pieces > (1ll << 30)) return VX_ERR_LIMIT;   // pieces are numbered in an int
     if ((q_row_stride & 1) || (((uintptr_t)q) & 3) || (out_row_stride & 1) || (((uintptr_t)out) & 3)) return VX_ERR_ALIGN;
     if (D == 128)
         return launch_decode<128>((const bf16*)q, q_row_stride, (const bf16*)k_pool, (const bf16*)v_pool,
