@@ -334,6 +334,10 @@ DECODE_CASES = [
     ([900, 64, 257], 16, 1, 64, 16, 0),              # 16 query heads share one kv head
     ([1300, 40, 590, 5], 4, 2, 128, 16, 540),        # a window that crosses split boundaries
     ([3000], 32, 8, 128, 16, 0),                     # the flagship's head layout, 12 pieces
+    # the kernel's other block shapes, chosen from requests x kv heads x pieces against 148 SMs:
+    ([1000] + [(i * 97) % 1000 + 1 for i in range(19)], 16, 8, 128, 16, 0),   # 640 pieces: blocks of 5 warps
+    ([1000] + [(i * 61) % 1000 + 1 for i in range(25)], 16, 8, 128, 16, 0),   # 832 pieces: blocks of 6 warps
+    ([1000] + [(i * 43) % 1000 + 1 for i in range(29)], 16, 8, 64, 16, 300),  # 960 pieces: several waves, a window
 ]
 
 
