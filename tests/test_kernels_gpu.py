@@ -337,7 +337,7 @@ DECODE_CASES = [
     # the kernel's other block shapes, chosen from requests x kv heads x pieces against 148 SMs:
     ([1000] + [(i * 97) % 1000 + 1 for i in range(19)], 16, 8, 128, 16, 0),   # 640 pieces: blocks of 5 warps
     ([1000] + [(i * 61) % 1000 + 1 for i in range(25)], 16, 8, 128, 16, 0),   # 832 pieces: blocks of 6 warps
-    ([1000] + [(i * 43) % 1000 + 1 for i in range(29)], 16, 8, 64, 16, 300),  # 960 pieces: several waves, a window
+    ([1000] + [(i * 43) % 1000 + 1 for i in range(29)], 16, 8, 64, 16, 0),    # 960 pieces: blocks of 4 warps, two an SM
 ]
 
 
@@ -380,6 +380,19 @@ def test_decode_attention_token_rows_and_batch_independence():
     ops().paged_decode_attention(q, H * D, kp, vp, bt, sot, pos, 1 / math.sqrt(D), 0, H, Hk, D, 1, 500,
                                  token_rows=rows[:1], out=alone)
     assert torch.equal(alone[5], out[5])  # bit-identical alone and in company
+
+
+def test_decode_attention_gives_the_same_bits_in_every_block_shape():
+    """The kernel picks warps per block and stages from the step's size; a request's
+    output must not notice (1, 20, 26 and 30 requests reach its four shapes on 148 SMs)."""
+    H, Hk, D, S = 16, 8, 128, 16
+    lens = [1000] + [(i * 43) % 1000 + 1 for i in range(29)]
+    q, kp, vp, bt, sot, pos, want = paged_case(torch.bfloat16, [(n - 1, 1) for n in lens], H, Hk, D, S, 0, seed=15)
+    full = ops().paged_decode_attention(q, H * D, kp, vp, bt, sot, pos, 1 / math.sqrt(D), 0, H, Hk, D, 30, 1000)
+    close(full, want, torch.bfloat16)
+    for n in (1, 20, 26):
+        part = ops().paged_decode_attention(q, H * D, kp, vp, bt, sot, pos, 1 / math.sqrt(D), 0, H, Hk, D, n, 1000)
+        assert torch.equal(part[:n], full[:n]), n
 
 
 def test_decode_attention_refuses_what_it_cannot_do():
