@@ -146,7 +146,11 @@ def stream_workload(args, cfg, layers):
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist() for n in lens]
     # warm-up: kernels, graphs of a few batch sizes, the library's handles
     engine.generate([prompts[0][:300], prompts[1][:40]], SamplingParams(max_tokens=4, ignore_eos=True))
+    # as a server does before it listens: the decode steps' graphs are captured now, not under load
+    t_cap = time.perf_counter()
+    captured = 0 if args.lazy_graphs else engine.capture_decode_graphs()
     torch.cuda.synchronize()
+    t_cap = time.perf_counter() - t_cap
     first, last, gaps, submitted_at = {}, {}, [], {}
     nxt, done = 0, 0
     t0 = time.perf_counter()
@@ -181,6 +185,7 @@ def stream_workload(args, cfg, layers):
             "ttft_ms": {"p50": pct(first.values(), 0.5), "p90": pct(first.values(), 0.9), "p99": pct(first.values(), 0.99)},
             "itl_ms": {"p50": pct(gaps, 0.5), "p90": pct(gaps, 0.9), "p99": pct(gaps, 0.99)},
             "steps": st["steps"], "preemptions": st["preemptions"], "layers": layers,
+            "graphs_captured_before": captured, "capture_s": round(t_cap, 2),
             "data": "synthetic: random weights, uniform random token ids, seeded arrivals"}
 
 
@@ -197,6 +202,8 @@ def main() -> int:
                          "under arrivals (64 requests, prompts of 128-4,096 tokens, 256 new tokens each, Poisson "
                          "arrivals); prints its own JSON line")
     ap.add_argument("--arrival-rate", type=float, default=16.0, help="stream: mean arrivals a second")
+    ap.add_argument("--lazy-graphs", action="store_true",
+                    help="stream: capture each decode graph when a step first needs it, inside the run")
     ap.add_argument("--pool-tokens", type=int, default=0, help="stream: cache pool in tokens (0: room for all)")
     ap.add_argument("--shape", default="8b", choices=sorted(SHAPES),
                     help="layer sizes: 8b is the benchmark's; 14b and 32b are Qwen3-14B / 32B")

@@ -114,6 +114,26 @@ def test_a_single_token_that_wants_nothing_rides_in_a_captured_step(model_folder
     assert logits is None and ids is None
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_graphs_captured_ahead_are_the_ones_the_steps_use(model_folders, dtype):
+    """`capture_decode_graphs` records every decode step's graph on padding rows before a
+    request exists: it leaves the cache as it found it, generation afterwards gives the
+    plain implementation's tokens, and no step has to capture a graph of its own."""
+    from velox_b200 import SamplingParams
+    cfg, w = P.load_model_folder(model_folders["tiny_b"])
+    e = engine(model_folders["tiny_b"], "tiny_b", dtype, num_pages=64, max_running_requests=4)
+    n = e.capture_decode_graphs()
+    assert n >= 4 and n == len(e.runner.graphs.graphs)
+    assert e.capture_decode_graphs() == 0          # all there already
+    assert set(e.cache.free_pages()) == {64}       # (every group of layers has its own pages)
+    e.cache.check()
+    prompts = [random_tokens(cfg["vocab_size"], k, 300 + k) for k in (3, 20, 9, 33)]
+    outs = e.generate(prompts, SamplingParams(max_tokens=10, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        check_greedy_path(cfg, w, p, o, dtype)
+    assert len(e.runner.graphs.graphs) == n, "a step captured a graph that was not captured ahead"
+
+
 def test_graphs_of_an_engine_that_is_gone_do_not_disturb_a_capture(model_folders, monkeypatch):
     """Engines come and go in one process.  The graphs of a dead engine are destroyed
     whenever the garbage collector gets to them; if that happened in the middle of

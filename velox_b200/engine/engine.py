@@ -157,6 +157,16 @@ class Engine:
             ops.check_device_errors()
         return self.scheduler.update(entries, sampled)
 
+    def capture_decode_graphs(self, max_batch: Optional[int] = None, max_tokens: Optional[int] = None) -> int:
+        """Captures the decode steps' graphs for up to `max_batch` requests (default:
+        `max_running_requests`) of up to `max_tokens` tokens each (default: the longest
+        a request may get) before the first request comes, instead of one by one
+        when a step first needs them.  Returns how many were captured."""
+        if self.runner.graphs is None:
+            return 0
+        return self.runner.graphs.capture_all(max_batch or self.scheduler.max_running_requests,
+                                              max_tokens or self.scheduler.max_model_len)
+
     def run_step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """The raw step function, for callers that schedule themselves."""
         return self.runner.step(entries)

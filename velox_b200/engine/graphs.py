@@ -120,6 +120,35 @@ class DecodeGraphs:
         self.has_state = bool(cache._state_layers)
         self.usable = all(getattr(p, "cuda_graph_safe", False) for p in runner.model.parts())
         self.cap = cache.slots.num_slots
+        self._collected = False
+
+    def capture_all(self, max_batch: int, max_kv: int) -> int:
+        """Captures, ahead of the first request, the graph of every (batch bucket,
+        key-range bucket) that decode steps of up to `max_batch` requests with up to
+        `max_kv` keys can ask for, so that no step has to wait for a capture (some
+        tens of milliseconds each).  The captured steps run on padding rows only.
+        Returns how many graphs were captured.  Nothing is captured for a model
+        with per-request state (its steps are never padded)."""
+        if not self.usable or self.has_state:
+            return 0
+        cache = self.runner.cache
+        batches = sorted({batch_bucket(n, False, self.cap) for n in range(1, min(max_batch, self.cap) + 1)})
+        keys, k = [], SPLIT_KEYS
+        while True:
+            keys.append(k)
+            if k >= keys_bucket(max_kv):
+                break
+            k *= 2
+        done = 0
+        for b in batches:
+            for kv in keys:
+                if (b, kv) in self.graphs:
+                    continue
+                g = self.graphs[(b, kv)] = _Graph(self.runner, b, kv)
+                g.fill([], cache.handles([]), cache, None, self.runner.vocab_size)
+                self._capture(g)
+                done += 1
+        return done
 
     def eligible(self, entries: Sequence[StepEntry]) -> bool:
         return self.usable and len(entries) > 0 and all(len(e.tokens) == 1 for e in entries)
@@ -154,9 +183,14 @@ class DecodeGraphs:
         # ... then recorded; the keys and values of this step are simply written twice.
         # Garbage is collected before, not during, the recording: an older engine's
         # graphs that happened to be destroyed in the middle of it would invalidate it.
+        # A full collection (tens of milliseconds) is made before this engine's first
+        # recording only: what was garbage before the engine's time is gone then, and
+        # engines themselves are freed by their reference counts, without the collector.
         graph = torch.cuda.CUDAGraph()
         n0 = ops.launch_count()
-        gc.collect()
+        if not self._collected:
+            gc.collect()
+            self._collected = True
         gc_was_on = gc.isenabled()
         gc.disable()
         try:
