@@ -116,7 +116,16 @@ def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
 
+_RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_GET_DEVICE = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream():
+    """The current stream's handle (the capture stream while a graph is recorded).
+    Asked of torch's C layer directly: the Python route costs 15 microseconds a call,
+    and every kernel launch asks."""
+    if _RAW_STREAM is not None and _GET_DEVICE is not None:
+        return _RAW_STREAM(_GET_DEVICE())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -424,6 +433,7 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias=None, gated_activation: 
 
 
 SKINNY_MAX_ROWS = 8
+_MATMUL_SET = False
 
 
 def skinny_supported(m: int, k: int, a: torch.Tensor, w: torch.Tensor) -> bool:
@@ -460,7 +470,10 @@ def gemm_bf16(a: torch.Tensor, w: torch.Tensor, bias=None, out_dtype: Optional[t
     if skinny_supported(a.shape[0], a.shape[1], a, w):
         return gemm_skinny(a, w, bias, out_dtype)
     # library product (cuBLAS through torch); reductions stay in float32
-    torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+    global _MATMUL_SET
+    if not _MATMUL_SET:
+        torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+        _MATMUL_SET = True
     if out_dtype == torch.float32:
         out = torch.mm(a, w.t(), out_dtype=torch.float32)
     else:
