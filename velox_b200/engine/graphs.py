@@ -18,7 +18,7 @@ from __future__ import annotations
 import ctypes
 import gc
 import weakref
-from typing import Dict, Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -43,6 +43,20 @@ def keys_bucket(max_kv: int) -> int:
     while b < pieces:
         b *= 2
     return b * SPLIT_KEYS
+
+
+def all_buckets(max_batch: int, cap: int, max_kv: int) -> List[Tuple[int, int]]:
+    """Every (batch bucket, key-range bucket) that a padded decode step of 1 to
+    `max_batch` requests (at most `cap`, the number of slots) with up to `max_kv` keys
+    can ask for."""
+    batches = sorted({batch_bucket(n, False, cap) for n in range(1, min(max_batch, cap) + 1)})
+    keys, k = [], SPLIT_KEYS
+    while True:
+        keys.append(k)
+        if k >= keys_bucket(max_kv):
+            break
+        k *= 2
+    return [(b, kv) for b in batches for kv in keys]
 
 
 class _Graph:
@@ -132,22 +146,14 @@ class DecodeGraphs:
         if not self.usable or self.has_state:
             return 0
         cache = self.runner.cache
-        batches = sorted({batch_bucket(n, False, self.cap) for n in range(1, min(max_batch, self.cap) + 1)})
-        keys, k = [], SPLIT_KEYS
-        while True:
-            keys.append(k)
-            if k >= keys_bucket(max_kv):
-                break
-            k *= 2
         done = 0
-        for b in batches:
-            for kv in keys:
-                if (b, kv) in self.graphs:
-                    continue
-                g = self.graphs[(b, kv)] = _Graph(self.runner, b, kv)
-                g.fill([], cache.handles([]), cache, None, self.runner.vocab_size)
-                self._capture(g)
-                done += 1
+        for b, kv in all_buckets(max_batch, self.cap, max_kv):
+            if (b, kv) in self.graphs:
+                continue
+            g = self.graphs[(b, kv)] = _Graph(self.runner, b, kv)
+            g.fill([], cache.handles([]), cache, None, self.runner.vocab_size)
+            self._capture(g)
+            done += 1
         return done
 
     def eligible(self, entries: Sequence[StepEntry]) -> bool:
