@@ -358,17 +358,32 @@ static int launch_decode_pieces(int blocks, const bf16* q, int q_row_stride, con
                                 int max_pieces, bf16* out, int out_row_stride, float scale, int window, int requests,
                                 int H, int Hk, int S, int piece_tiles, cudaStream_t stream) {
     const size_t smem = (size_t)WARPS * STAGES * 2 * 16 * D * 2;
-    static bool configured = false;  // per process and instantiation; the attribute is per device function
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(paged_decode_attention_kernel<D, STAGES, WARPS>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
     VX_LAUNCH_K(VX_K_ATTENTION, (paged_decode_attention_kernel<D, STAGES, WARPS>), dim3(blocks), WARPS * 32, smem, stream,
                 q, q_row_stride, k_pool, v_pool, block_table, max_blocks, token_rows, seq_of_token, positions, part_o,
                 part_ml, max_pieces, out, out_row_stride, scale * LOG2E, window, H, Hk, S, piece_tiles, requests);
     VX_LAUNCH_CHECK();
+    return VX_OK;
+}
+
+template <int D, int STAGES, int WARPS>
+static cudaError_t configure_decode_pieces() {
+    return cudaFuncSetAttribute(paged_decode_attention_kernel<D, STAGES, WARPS>,
+                                cudaFuncAttributeMaxDynamicSharedMemorySize, WARPS * STAGES * 2 * 16 * D * 2);
+}
+
+// All four shapes of a head size at its first call (per process; the attribute is per
+// device function), whichever shape that call needs: a later call may come from inside a
+// stream capture with a step of another size.
+template <int D>
+static int configure_decode() {
+    static bool configured = false;
+    if (configured) return VX_OK;
+    cudaError_t e = configure_decode_pieces<D, 6, 4>();
+    if (e == cudaSuccess) e = configure_decode_pieces<D, 3, 4>();
+    if (e == cudaSuccess) e = configure_decode_pieces<D, 5, 5>();
+    if (e == cudaSuccess) e = configure_decode_pieces<D, 4, 6>();
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
     return VX_OK;
 }
 
@@ -378,6 +393,8 @@ static int launch_decode(const bf16* q, int q_row_stride, const bf16* k_pool, co
                          const int* seq_of_token, const int* positions, float* scratch, int max_pieces,
                          bf16* out, int out_row_stride, float scale, int window, int requests, int H, int Hk,
                          int S, int piece_tiles, cudaStream_t stream) {
+    const int ready = configure_decode<D>();
+    if (ready != VX_OK) return ready;
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)requests * H * max_pieces * D : nullptr;
     const long long pieces = (long long)requests * Hk * max_pieces, sms = dec_sm_count();

@@ -22,7 +22,7 @@
 //     the limit.
 //   * The first call on each device looks up the array's device address
 //     (cudaGetSymbolAddress, with that device current) and configures the
-//     kernel.  Make that first call before any stream capture begins.
+//     kernel (every block shape it may pick for later steps).  Make that first call before any stream capture begins.
 //   * All calls share the one array, and it keeps whatever the previous call
 //     left in it.  The kernels write every scratch element before reading it,
 //     so nothing needs clearing; but two calls that overlap on the GPU (on
