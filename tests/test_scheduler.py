@@ -226,3 +226,102 @@ def test_a_run_of_generated_tokens_can_end_a_request():
     Driver(cache, s).run()
     assert s.finished[rid].generated == full[:7] and s.finished[rid].finish_reason == "stop"
     assert s.finished[other].generated == full and s.finished[other].finish_reason == "length"
+
+
+def test_cancel_while_waiting_in_prompt_in_decode_and_after_preemption():
+    # (src/paged/scheduler.rs:440-452: a request whose caller is gone ends with "cancelled" and frees its pages)
+    cache, s = make(num_pages=12, page=4, max_batch_tokens=8, max_running_requests=2)
+    d = Driver(cache, s)
+    a = s.submit([1] * 20, SamplingParams(max_tokens=8))   # its prompt takes three steps
+    b = s.submit([2] * 3, SamplingParams(max_tokens=30))
+    c = s.submit([3] * 5, SamplingParams(max_tokens=4))    # waits: two requests run at most
+    d.step()
+    assert s.running[a].status == "running" and cache.length(a) == 8   # in the middle of its prompt
+    assert s.cancel(c) is True                                          # while it waits
+    assert s.finished[c].finish_reason == "cancelled" and s.finished[c].generated == []
+    assert [r.request_id for r in s.waiting] == [b]
+    held = 12 - cache.free_pages()[0]
+    assert held == 2
+    assert s.cancel(a) is True                                          # in the middle of its prompt
+    assert cache.free_pages() == [12] and not cache.has_request(a)
+    cache.check()
+    assert s.finished[a].finish_reason == "cancelled" and s.cancel(a) is False
+    for _ in range(4):
+        d.step()
+    got = list(s.running[b].generated)
+    assert len(got) >= 2                                                # b decodes
+    assert s.cancel(b) is True
+    assert s.finished[b].generated == got == expected([2] * 3, len(got))  # what it had stays readable
+    assert not s.has_work() and cache.free_pages() == [12] and cache.slots.num_free == 8
+    cache.check()
+    st = s.stats
+    assert st.requests_aborted == 3 and st.requests_completed == 0
+    with pytest.raises(KeyError):
+        s.cancel(12345)
+    # after a preemption: the victim waits at the front without cache; cancelling it leaves the others as they were
+    cache, s = make(num_pages=12, page=4)
+    d = Driver(cache, s)
+    ids = [s.submit([i] * 8, SamplingParams(max_tokens=16)) for i in range(3)]
+    while not s.stats.preemptions:
+        d.step()
+    victim = s.waiting[0].request_id
+    assert s.waiting[0].preemptions == 1 and s.cancel(victim)
+    d.run()
+    for i, rid in enumerate(ids):
+        r = s.finished[rid]
+        if rid == victim:
+            assert r.finish_reason == "cancelled" and r.generated == expected([i] * 8, len(r.generated))
+        else:
+            assert r.finish_reason == "length" and r.generated == expected([i] * 8, 16)
+    assert cache.free_pages() == [12] and cache.slots.num_free == 8
+    assert s.stats.requests_aborted == 1 and s.stats.requests_completed == 2
+
+
+def test_cancel_in_random_workloads_loses_no_page():
+    import random
+    rng = random.Random(11)
+    for trial in range(10):
+        cache, s = make(num_pages=rng.randint(10, 30), page=rng.choice([2, 4, 8]), window=rng.choice([0, 7]),
+                        max_batch_tokens=rng.choice([4, 16, 64]), max_running_requests=rng.choice([2, 4, 8]))
+        d = Driver(cache, s)
+        total = cache.free_pages()
+        want, cancelled = {}, set()
+        for i in range(rng.randint(4, 10)):
+            p = [rng.randrange(250) for _ in range(rng.randint(1, 20))]
+            try:
+                want[s.submit(p, SamplingParams(max_tokens=rng.randint(1, 12)))] = p
+            except RequestRefused:
+                pass
+            if rng.random() < 0.6 and s.has_work():
+                d.step()
+            if want and rng.random() < 0.4:
+                rid = rng.choice(sorted(want))
+                if s.cancel(rid):
+                    cancelled.add(rid)
+                cache.check()
+        d.run()
+        for rid, p in want.items():
+            r = s.finished[rid]
+            assert r.generated == expected(p, len(r.generated))
+            assert (r.finish_reason == "cancelled") == (rid in cancelled)
+        assert cache.free_pages() == total and cache.slots.num_free == 8
+        assert s.stats.requests_aborted == len(cancelled)
+
+
+def test_step_time_is_kept():
+    import time
+    cache, s = make()
+    d = Driver(cache, s)
+    s.submit([1, 2, 3], SamplingParams(max_tokens=3))
+    assert s.stats.last_step_us == 0 and s.stats.mean_step_us == 0.0
+    entries, _ = s.plan()
+    time.sleep(0.02)   # the device's work would pass here
+    for e in entries:
+        cache.commit(e.request_id, len(e.tokens))
+    s.update(entries, [next_token([1, 2, 3])])
+    d.held[(0, 0)] = [1, 2, 3]
+    st = s.stats
+    assert 20000 <= st.last_step_us < 2000000 and st.total_step_us == st.last_step_us and st.steps == 1
+    d.run()
+    st = s.stats
+    assert st.steps == 3 and st.total_step_us >= 20000 and abs(st.mean_step_us - st.total_step_us / 3) < 1e-9

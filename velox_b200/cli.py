@@ -96,11 +96,20 @@ def cmd_generate(args) -> int:
                              seed=None if args.seed is None else args.seed + i, ignore_eos=args.ignore_eos,
                              stop_sequences=[list(q) for q in stops])
               for i in range(len(prompts))]
+    dumped, dump_index = [], []
+    if args.dump_logits:
+        def keep_logits(request_ids, logits):
+            dumped.append(logits.detach().to("cpu").numpy().astype("<f4"))
+            dump_index.extend(int(r) for r in request_ids)
+        engine.on_logits = keep_logits
     outs = engine.generate(prompts, params)
-    for i, (p, o) in enumerate(zip(prompts, outs)):
-        r = engine.scheduler.finished[i] if i in engine.scheduler.finished else None
-        print(json.dumps({"request": i, "prompt_tokens": len(p), "tokens": o,
-                          "finish_reason": r.finish_reason if r else None}))
+    if args.dump_logits:
+        # rows in the order the tokens were sampled; FILE.json says whose each row is
+        (np.concatenate(dumped) if dumped else np.zeros((0, 0), "<f4")).tofile(args.dump_logits)
+        with open(args.dump_logits + ".json", "w") as f:
+            json.dump({"dtype": "<f4", "rows": len(dump_index), "request_of_row": dump_index}, f)
+    for i, (p, o, why) in enumerate(zip(prompts, outs, engine.last_finish_reasons)):
+        print(json.dumps({"request": i, "prompt_tokens": len(p), "tokens": o, "finish_reason": why}))
     if args.stats:
         sys.stderr.write(json.dumps(engine.stats()) + "\n")
     return 0
@@ -140,6 +149,9 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--max-batch-tokens", type=int, default=2048)
     g.add_argument("--chunk-size", type=int, default=None)
     g.add_argument("--max-model-len", type=int, default=None)
+    g.add_argument("--dump-logits", default=None, metavar="FILE",
+                   help="write the float32 logits every token was sampled from to FILE ([rows, vocab], in sampling "
+                        "order) and the request of each row to FILE.json")
     g.add_argument("--stats", action="store_true", help="print the scheduler's counters to stderr at the end")
     g.set_defaults(fn=cmd_generate)
     return ap

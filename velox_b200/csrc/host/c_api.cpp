@@ -180,6 +180,7 @@ int vxh_sched_finish(void* s, int64_t id, int reason) {
     if (!r) return fail(ERR_UNKNOWN_REQUEST, "no request " + std::to_string(id));
     return sc->finish(r, reason);
 }
+int vxh_sched_cancel(void* s, int64_t id) { return ((Scheduler*)s)->cancel(id); }
 void vxh_sched_forget(void* s, int64_t id) { ((Scheduler*)s)->forget(id); }
 // which: 0 waiting (queue order), 1 running, 2 finished (by id).  The number of ids; copied up to cap.
 long long vxh_sched_list(void* s, int which, int64_t* out, long long cap) {
@@ -226,8 +227,9 @@ int vxh_sched_request_tokens(void* s, int64_t id, int generated, long long start
 }
 int vxh_sched_stats(void* s, int64_t* out) {
     const SchedulerStats& st = ((Scheduler*)s)->stats();
-    const int64_t v[8] = {st.steps, st.tokens_generated, st.prompt_tokens, st.requests_completed,
-                          st.requests_refused, st.preemptions, st.last_batch_size, st.last_batch_tokens};
+    const int64_t v[11] = {st.steps, st.tokens_generated, st.prompt_tokens, st.requests_completed,
+                           st.requests_refused, st.preemptions, st.last_batch_size, st.last_batch_tokens,
+                           st.requests_aborted, st.last_step_us, st.total_step_us};
     std::memcpy(out, v, sizeof(v));
     return OK;
 }

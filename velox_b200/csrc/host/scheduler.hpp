@@ -6,7 +6,8 @@
 // holding cache (:239), requests in a step ordered by id (:311-312), one new token
 // per decoding request per step (:337-343), the first token sampled from the step
 // that completes the prompt (:407-421), an end-of-sequence token kept and counted
-// (:426), finish reasons "stop" and "length" (:465-484), and its counters (:95-105).
+// (:426), finish reasons "stop", "length" and "cancelled" (:440-452, :465-484), and
+// its counters with the last step's wall time (:95-105, :528-532).
 //
 // What differs, on purpose:
 //   * Prompts are really cut.  The reference offers a request's whole remaining
@@ -27,6 +28,7 @@
 // The scheduler decides and keeps books; it runs nothing on the device.  plan()
 // reserves the pages of the step it returns; update() takes the sampled tokens.
 #pragma once
+#include <chrono>
 #include <deque>
 #include <map>
 #include <memory>
@@ -36,7 +38,7 @@
 namespace vxh {
 
 enum RequestStatus : int { WAITING = 0, RUNNING = 1, FINISHED = 2 };
-enum FinishReason : int { NOT_FINISHED = 0, FINISH_STOP = 1, FINISH_LENGTH = 2 };
+enum FinishReason : int { NOT_FINISHED = 0, FINISH_STOP = 1, FINISH_LENGTH = 2, FINISH_CANCELLED = 3 };
 
 struct Request {
     int64_t id = 0;
@@ -58,6 +60,11 @@ struct Request {
 struct SchedulerStats {
     int64_t steps = 0, tokens_generated = 0, prompt_tokens = 0, requests_completed = 0, requests_refused = 0,
             preemptions = 0, last_batch_size = 0, last_batch_tokens = 0;
+    // requests withdrawn by their caller (not counted as completed)
+    int64_t requests_aborted = 0;
+    // wall time from the start of plan() to the end of the update() that took the
+    // step's tokens: planning, the device's work and the copy back of the sampled ids
+    int64_t last_step_us = 0, total_step_us = 0;
 };
 
 struct PlanEntry {
@@ -132,6 +139,7 @@ public:
     // ended while planning (alone and out of pages), and those admitted (their
     // state slots are fresh).
     int plan() {
+        plan_started_ = std::chrono::steady_clock::now();
         entries_.clear();
         ended_.clear();
         admitted_.clear();
@@ -191,6 +199,9 @@ public:
             out_finished[k] = reason != NOT_FINISHED;
             ++k;
         }
+        stats_.last_step_us = std::chrono::duration_cast<std::chrono::microseconds>(
+                                  std::chrono::steady_clock::now() - plan_started_).count();
+        stats_.total_step_us += stats_.last_step_us;
         return k;
     }
 
@@ -201,8 +212,21 @@ public:
         r->status = FINISHED;
         r->finish_reason = reason;
         finished_[r->id] = r;
-        ++stats_.requests_completed;
+        ++(reason == FINISH_CANCELLED ? stats_.requests_aborted : stats_.requests_completed);
         return OK;
+    }
+    // Withdraws a request, waiting or running: what it holds of the cache is given
+    // back at once, its tokens so far are kept, its reason is "cancelled"
+    // (src/paged/scheduler.rs:440-452 ends a request whose client is gone so).
+    // 1 if it was withdrawn, 0 if it had finished already.  To be called between
+    // steps: a step that was planned with the request must have been taken by update().
+    int cancel(int64_t id) {
+        Request* r = find(id);
+        if (!r) return fail(ERR_UNKNOWN_REQUEST, "no request " + std::to_string(id));
+        if (r->status == FINISHED) return 0;
+        if (r->status == WAITING) waiting_.erase(std::find(waiting_.begin(), waiting_.end(), r));
+        if (int e = finish(r, FINISH_CANCELLED)) return e;
+        return 1;
     }
     // Drops a finished request's record (its tokens have been read).
     void forget(int64_t id) {
@@ -350,6 +374,7 @@ private:
     std::unordered_map<int64_t, std::unique_ptr<Request>> all_;
     SchedulerStats stats_;
     int64_t next_id_ = 0, admissions_ = 0;
+    std::chrono::steady_clock::time_point plan_started_ = std::chrono::steady_clock::now();
     std::vector<PlanEntry> entries_;
     std::vector<int64_t> ended_;
     std::vector<std::pair<int64_t, int>> admitted_;

@@ -86,6 +86,10 @@ class Engine:
         else:
             bind_random_weights(self.model, self.runtime, int(random_seed))
         self.eos_token_ids = _eos_ids(model_dir, raw)
+        self.last_finish_reasons: List[Optional[str]] = []  # of the latest `generate`, per prompt
+        # called after every step that sampled, with (request ids, float32 logits [sampled, vocab]
+        # on the device): the rows the step's tokens were drawn from
+        self.on_logits = None
 
         cfg = self.config
         self.max_model_len = int(cfg.max_model_len or self.plan.max_positions or 4096)
@@ -150,8 +154,11 @@ class Engine:
             # one uniform number per (request, token): the same sequence whatever the batching
             seed = p.seed if p.seed is not None else self.config.seed * 1000003 + e.request_id
             us.append(uniform(seed, 0, self.scheduler.request(e.request_id).num_generated))
-        _logits, ids = self.runner.step_and_sample(entries, temps, tops, us)
+        logits, ids = self.runner.step_and_sample(entries, temps, tops, us)
         sampled: List[int] = ids.tolist() if ids is not None else []
+        if self.on_logits is not None and logits is not None:
+            # (a captured step's logits live in the graph's buffer until the next step only)
+            self.on_logits([e.request_id for e in entries if e.want], logits[:len(sampled)])
         if self.runner.pending_error_check:
             self.runner.pending_error_check = False
             ops.check_device_errors()
@@ -183,7 +190,22 @@ class Engine:
         ids = [self.add_request(p, sp) for p, sp in zip(prompts, plist)]
         while self.scheduler.has_work():
             self.step()
-        return [list(self.scheduler.finished[i].generated) for i in ids]
+        outs, self.last_finish_reasons = [], []
+        for i in ids:
+            r = self.scheduler.finished[i]
+            outs.append(list(r.generated))
+            self.last_finish_reasons.append(r.finish_reason)
+            # the record is dropped once its tokens are read (the reference drops a
+            # request when it finishes, src/paged/scheduler.rs:505-520), so an engine
+            # that lives long does not grow
+            self.scheduler.forget(i)
+        return outs
+
+    def cancel(self, request_id: int) -> bool:
+        """Withdraws a request that waits or runs (between two calls of `step`): what
+        it holds of the cache is free at once, its finish reason is "cancelled".
+        False if it had finished already."""
+        return self.scheduler.cancel(request_id)
 
     def request(self, request_id: int) -> Request:
         return self.scheduler.request(request_id)

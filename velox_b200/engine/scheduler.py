@@ -6,7 +6,8 @@ first come first served from a queue (:220-295), at most `max_running_requests`
 holding cache (:239), requests in a step ordered by id (:311-312), one new token
 per decoding request per step (:337-343), the first token sampled from the step
 that completes the prompt (:407-421), an end-of-sequence token kept and counted
-(:426), finish reasons "stop" and "length" (:465-484), and its counters (:95-105).
+(:426), finish reasons "stop", "length" and "cancelled" (:440-452, :465-484), and
+its counters with the last step's wall time (:95-105, :528-532).
 
 What differs, on purpose:
   * Prompts are really cut.  The reference offers a request's whole remaining
@@ -47,7 +48,7 @@ from .batch import StepEntry
 
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
 _STATUS = (WAITING, RUNNING, FINISHED)
-_REASON = (None, "stop", "length")
+_REASON = (None, "stop", "length", "cancelled")
 
 
 class Request:
@@ -133,6 +134,13 @@ class SchedulerStats:
     preemptions: int = 0
     last_batch_size: int = 0
     last_batch_tokens: int = 0
+    requests_aborted: int = 0   # withdrawn with `cancel`; not among the completed
+    last_step_us: int = 0       # wall time of the last step, from its planning to its tokens
+    total_step_us: int = 0
+
+    @property
+    def mean_step_us(self) -> float:
+        return self.total_step_us / self.steps if self.steps else 0.0
 
 
 class _Queue(Mapping):
@@ -201,7 +209,7 @@ class Scheduler:
 
     @property
     def stats(self) -> SchedulerStats:
-        out = (ctypes.c_int64 * 8)()
+        out = (ctypes.c_int64 * 11)()
         self._lib.vxh_sched_stats(self._sched, out)
         return SchedulerStats(*[int(x) for x in out])
 
@@ -278,6 +286,13 @@ class Scheduler:
         """Ends a request from outside (its cache is given back)."""
         rid = request.request_id if isinstance(request, Request) else int(request)
         native.check(self._lib.vxh_sched_finish(self._sched, rid, _REASON.index(reason)))
+
+    def cancel(self, request_id: int) -> bool:
+        """Withdraws a waiting or running request between two steps: its pages and
+        slot are given back at once, its tokens so far stay readable, its finish
+        reason is "cancelled" (src/paged/scheduler.rs:440-452).  False if it had
+        finished already; KeyError if there is no such request."""
+        return bool(native.check(self._lib.vxh_sched_cancel(self._sched, int(request_id))))
 
     def forget(self, request_id: int) -> None:
         """Drops the record of a finished request whose tokens have been read."""

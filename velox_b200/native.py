@@ -87,6 +87,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "vxh_sched_plan_admitted": (I, [P, PI64, PI]),
         "vxh_sched_update": (I, [P, I, PI64, PI64, PI, PI, I, PI64, PI, PI]),
         "vxh_sched_finish": (I, [P, c_int64, I]), "vxh_sched_forget": (None, [P, c_int64]),
+        "vxh_sched_cancel": (I, [P, c_int64]),
         "vxh_sched_list": (L, [P, I, PI64, L]), "vxh_sched_contains": (I, [P, I, c_int64]),
         "vxh_sched_request": (I, [P, c_int64, PI64]), "vxh_sched_request_tokens": (I, [P, c_int64, I, L, L, PI]),
         "vxh_sched_stats": (I, [P, PI64]),
