@@ -130,3 +130,15 @@ def test_no_fifth_request_without_a_slot():
     assert m.add_request(0) == 0 and m.add_request(1) == 1 and m.add_request(2) is None
     with pytest.raises(CacheAccountingError):
         m.add_request(0)
+
+
+def test_a_cache_need_of_unknown_kind_is_refused():
+    from dataclasses import dataclass
+    from velox_b200.cache import CacheManager
+
+    @dataclass(frozen=True)
+    class Unheard:
+        size: int
+
+    with pytest.raises(TypeError, match="unknown kind"):
+        CacheManager([Unheard(3)], [None], 8, 4, 2, 4)

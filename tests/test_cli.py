@@ -118,7 +118,9 @@ def test_generate_greedy_tiny_a_tokens_logits_and_stop(tmp_path):
     recs, _ = _generate(root, "tiny_a", "--prompt-tokens", ",".join(map(str, prompts[1])), "--dtype", "float32",
                         "--max-tokens", "8", "--page-size", "4", "--num-pages", "64", "--max-model-len", "64",
                         "--ignore-eos", "--stop", "%d,%d" % (want[1][3], want[1][4]), "--stop", "9999")
-    assert recs[0]["tokens"] == want[1][:5] and recs[0]["finish_reason"] == "stop"
+    pair = want[1][3:5]
+    first = next(n for n in range(2, 9) if want[1][n - 2:n] == pair)   # (a tiny model may repeat itself earlier)
+    assert recs[0]["tokens"] == want[1][:first] and recs[0]["finish_reason"] == "stop"
 
 
 @pytest.mark.gpu

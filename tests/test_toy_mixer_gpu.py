@@ -69,7 +69,7 @@ def register_toy():
         for i, kind in enumerate(["sum", "att", "att_shared"]):
             p = "toy.%d." % i
             mixer = PartSpec("toy_running_sum", p, dict(hidden_size=E)) if kind == "sum" else att(p + "a.")
-            layers.append(LayerSpec(mixer, ff(p + "ff."), norm(p + "n1."), norm(p + "n2."),
+            layers.append(LayerSpec(mixer, ff(p + "ff."), {"mixer": norm(p + "n1."), "feed_forward": norm(p + "n2.")},
                                     cache_of=1 if kind == "att_shared" else None))
         return ModelPlan(cfg.vocab_size, E, PartSpec("token_embedding", "toy.embed.", dict(vocab_size=cfg.vocab_size, hidden_size=E)),
                          layers, norm("toy.norm."), PartSpec("linear_head", "toy.head.", dict(vocab_size=cfg.vocab_size, hidden_size=E)),
@@ -147,3 +147,97 @@ def test_toy_mixer_with_state_runs_in_the_engine(tmp_path):
     finally:
         unregister_architecture("ToyStateLM")
         unregister_part("mixer", "toy_running_sum")
+
+
+def register_graph_safe_toy():
+    """The running sum again, written so that it reads nothing of a step but device
+    tensors: such a mixer may say `cuda_graph_safe`, and decode steps of its model are
+    then captured in CUDA graphs (never padded: a padding row would touch a real slot)."""
+    from velox_b200.config import ModelConfig, register_architecture
+    from velox_b200.config.model_config import _field
+    from velox_b200.parts import FixedState, LayerSpec, Mixer, ModelPlan, PartSpec, TensorSpec, matmul, register_mixer
+
+    class DeviceRunningSum(Mixer):
+        cuda_graph_safe = True
+
+        def __init__(self, prefix, hidden_size):
+            super().__init__(prefix)
+            self.hidden_size = hidden_size
+
+        def tensor_specs(self):
+            return [TensorSpec(self.prefix + "mix.weight", (self.hidden_size, self.hidden_size), "matrix")]
+
+        def bind(self, tensors, runtime):
+            super().bind(tensors, runtime)
+            self.weight = tensors[self.prefix + "mix.weight"]
+
+        def cache_spec(self):
+            return FixedState((self.hidden_size,), "float32")
+
+        def forward(self, h, ctx, cache):
+            seq = ctx.seq_of_token.long()
+            first = ctx.cu_seqlens[:-1].long()[seq]                    # first row of each token's request
+            c = torch.cumsum(h.float(), 0)
+            before = torch.where((first > 0)[:, None], c[(first - 1).clamp(min=0)], torch.zeros_like(c))
+            slots = ctx.state_slots.long()
+            sums = c - before + cache.state[slots[seq]]
+            cache.state[slots] = sums[ctx.cu_seqlens[1:].long() - 1]    # each request's last row
+            return matmul(sums.to(h.dtype), self.weight)
+
+    @dataclass(frozen=True)
+    class ToyConfig(ModelConfig):
+        architecture: ClassVar[str] = "ToyGraphStateLM"
+        model_type: ClassVar[str] = "toy_graph_state"
+        vocab_size: int = _field(int)
+        hidden_size: int = _field(int)
+
+    def plan(cfg):
+        E = cfg.hidden_size
+        norm = lambda p: PartSpec("rms_norm", p, dict(size=E, eps=1e-5))
+        layers = [LayerSpec(PartSpec("toy_device_running_sum", "toy.%d." % i, dict(hidden_size=E)),
+                            PartSpec("gated_mlp", "toy.%d.ff." % i, dict(hidden_size=E, intermediate_size=2 * E)),
+                            {"mixer": norm("toy.%d.n1." % i), "feed_forward": norm("toy.%d.n2." % i)}) for i in range(2)]
+        return ModelPlan(cfg.vocab_size, E, PartSpec("token_embedding", "toy.embed.", dict(vocab_size=cfg.vocab_size, hidden_size=E)),
+                         layers, norm("toy.norm."), PartSpec("linear_head", "toy.head.", dict(vocab_size=cfg.vocab_size, hidden_size=E)),
+                         max_positions=128)
+
+    register_mixer("toy_device_running_sum", DeviceRunningSum)
+    register_architecture("ToyGraphStateLM", "toy_graph_state", ToyConfig, plan)
+    return ToyConfig
+
+
+def test_a_stateful_mixer_in_captured_decode_steps_advances_its_state_once(tmp_path):
+    """With graphs on, the step that first needs a graph captures it: that step must run
+    the model once, not once eagerly and once more as a replay, or every request's state
+    would be advanced twice.  Tokens and logits equal those of an engine without graphs."""
+    from velox_b200 import Engine, EngineConfig, SamplingParams
+    from velox_b200.config import unregister_architecture
+    from velox_b200.parts import unregister_part
+    from velox_b200.weights import write_random_model
+
+    ToyConfig = register_graph_safe_toy()
+    try:
+        cfg = ToyConfig.from_dict(dict(vocab_size=100, hidden_size=32))
+        folder = write_random_model(str(tmp_path / "toy"), cfg, seed=4)
+        rng = np.random.default_rng(8)
+        prompts = [[int(t) for t in rng.integers(0, 100, n)] for n in (3, 9, 14)]
+        runs = {}
+        for graphs in (False, True):
+            e = Engine(folder, EngineConfig(dtype="float32", page_size=8, num_pages=8, max_model_len=64,
+                                            max_running_requests=4, cuda_graphs=graphs))
+            rows = []
+            e.on_logits = lambda ids, logits: rows.append((list(ids), logits.cpu().numpy().copy()))
+            # different lengths: requests finish at different steps, so several batch sizes get a graph
+            outs = e.generate(prompts, [SamplingParams(max_tokens=n, ignore_eos=True) for n in (12, 5, 9)])
+            runs[graphs] = (outs, rows)
+            if graphs:
+                g = e.runner.graphs
+                assert g.usable and g.has_state and len(g.graphs) >= 3, "no decode step was captured"
+        (outs_a, rows_a), (outs_b, rows_b) = runs[False], runs[True]
+        assert outs_a == outs_b
+        assert len(rows_a) == len(rows_b)
+        for (ids_a, la), (ids_b, lb) in zip(rows_a, rows_b):
+            assert ids_a == ids_b and np.abs(la - lb).max() < 1e-5
+    finally:
+        unregister_architecture("ToyGraphStateLM")
+        unregister_part("mixer", "toy_device_running_sum")

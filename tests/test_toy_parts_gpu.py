@@ -96,7 +96,7 @@ def register_toy():
                 hidden_size=E, num_heads=HEADS, num_kv_heads=KV_HEADS, head_dim=D, qk_norm=True, eps=cfg.eps,
                 position=PartSpec("toy_learned_offsets", p + "a.pos.", dict(head_dim=D, max_positions=128))))
             ff = PartSpec("toy_routed", p + "ff.", dict(hidden_size=E, inner_size=cfg.inner_size, experts=EXPERTS))
-            layers.append(LayerSpec(att, ff, norm(p + "n1."), norm(p + "n2.")))
+            layers.append(LayerSpec(att, ff, {"mixer": norm(p + "n1."), "feed_forward": norm(p + "n2.")}))
         return ModelPlan(cfg.vocab_size, E, PartSpec("token_embedding", "toy.embed.", dict(vocab_size=cfg.vocab_size, hidden_size=E)),
                          layers, norm("toy.norm."), PartSpec("linear_head", "toy.head.", dict(vocab_size=cfg.vocab_size, hidden_size=E)),
                          order=list(range(cfg.layers)), max_positions=128)

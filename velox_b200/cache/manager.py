@@ -3,11 +3,11 @@ in groups of layers with the same needs, and slots for fixed-size state.
 
 The manager is told, for every place of the model's running order, what the
 mixer there needs (a layer that runs twice has two places and two caches).
-Places that ask for the same `PagedKV` (kv heads, head size, window) form a
-group.  A group has its own page pool, storage
-[layer, K|V, page, kv head, offset in page, head_dim] (the reference keeps a K
-and a V pool [page, kv head, offset, head_dim] per layer,
-src/paged/pages.rs:62-74, 101-109), and its own block table per request: entry i
+What lies in a page or a slot is the business of the need's `CacheKind`
+(`cache/kinds.py`: keys and values in pages, fixed-size state, and whatever kind
+is registered besides).  Places that ask for the same paged need (for keys and
+values: kv heads, head size, window) form a group.  A group has its own page
+pool, storage laid out by its kind, and its own block table per request: entry i
 is the page that holds positions [i*S, (i+1)*S), or -1.  Pages are taken when a
 step needs them (`reserve`), not for the worst case at admission as the
 reference does (src/paged/scheduler.rs:255).  They are given back when the
@@ -15,7 +15,7 @@ request ends, and in a group with a window as soon as every position of a page
 lies before the window of the next query; the freed page is the next one handed
 out.
 
-Layers whose mixers ask for `FixedState` get one tensor [slots, *shape] each;
+Layers whose mixers ask for a slot kind (`FixedState`) get one tensor [slots, *shape] each;
 a request holds one slot id from admission to its end, in every such layer.
 Qwen3 has no such layer; the slot is assigned all the same.
 
@@ -36,31 +36,21 @@ import torch
 
 from .. import native
 from ..native import OutOfPages  # noqa: F401  (part of this module's interface)
-from ..parts.base import FixedState, PagedKV
+from .kinds import CacheKind, LayerCache, cache_kind
 from .pages import CacheAccountingError, PageAllocator, SlotAllocator
 
 
 @dataclass
-class LayerCache:
-    """What a layer's mixer gets: its group (index into the step context's
-    groups, -1 for none), whether it writes, and its storage."""
-    group: int = -1
-    writes: bool = True
-    k_pool: Optional[torch.Tensor] = None
-    v_pool: Optional[torch.Tensor] = None
-    state: Optional[torch.Tensor] = None
-
-
-@dataclass
 class CacheGroup:
-    spec: PagedKV
+    spec: object               # the paged need that the group's layers share
+    kind: CacheKind
     layers: List[int]
     allocator: PageAllocator
-    storage: Optional[torch.Tensor] = None  # [layers, 2, pages, Hk, S, D]
+    storage: Optional[torch.Tensor] = None  # laid out by the kind; first dimension: the group's layers
 
     @property
     def window(self) -> int:
-        return self.spec.window
+        return self.kind.window(self.spec)
 
 
 @dataclass
@@ -109,13 +99,14 @@ class CacheManager:
         self.groups: List[CacheGroup] = []
         self._layers: List[LayerCache] = []
         self._state_layers: List[int] = []
-        by_spec: Dict[PagedKV, int] = {}
+        by_spec: Dict[object, int] = {}
         n_layers = len(cache_specs)
         layer_group = [-1] * n_layers
-        specs_of_groups: List[PagedKV] = []
+        specs_of_groups: List[object] = []
         layers_of_groups: List[List[int]] = []
+        kinds = [None if spec is None else cache_kind(spec) for spec in cache_specs]
         for i, spec in enumerate(cache_specs):
-            if isinstance(spec, PagedKV):
+            if spec is not None and kinds[i].paged:
                 if spec not in by_spec:
                     by_spec[spec] = len(specs_of_groups)
                     specs_of_groups.append(spec)
@@ -126,14 +117,15 @@ class CacheManager:
         self._lib = native.library()
         if num_pages <= 0:
             raise ValueError("a page pool needs at least one page")
-        windows = native.int_array([s.window for s in specs_of_groups])
+        windows = native.int_array([cache_kind(s).window(s) for s in specs_of_groups])
         self._book = ctypes.c_void_p(self._lib.vxh_cache_create(len(specs_of_groups), windows, self.page_size,
                                                                 int(num_pages), int(max_requests), self.max_blocks))
         if not self._book:
             raise ValueError("page size, pages, requests and blocks per request must be positive")
         self.slots = SlotAllocator(0, _borrowed=self._lib.vxh_cache_slots(self._book), _owner=self)
         for g, (spec, layers) in enumerate(zip(specs_of_groups, layers_of_groups)):
-            self.groups.append(CacheGroup(spec, layers, PageAllocator(0, _borrowed=self._lib.vxh_cache_pool(self._book, g), _owner=self)))
+            self.groups.append(CacheGroup(spec, cache_kind(spec), layers,
+                                          PageAllocator(0, _borrowed=self._lib.vxh_cache_pool(self._book, g), _owner=self)))
         # request ids: non-negative integers are their own handle in the library
         # (the scheduler's ids are such), anything else gets a negative one
         self._handles: Dict[object, int] = {}
@@ -142,33 +134,27 @@ class CacheManager:
         self.requests = _Requests(self)
         for g in self.groups:
             if device is not None:
-                shape = (len(g.layers), 2, num_pages, g.spec.num_kv_heads, self.page_size, g.spec.head_dim)
-                g.storage = torch.empty(shape, dtype=dtype, device=device)
-                if poison:
+                g.storage = g.kind.allocate(g.spec, len(g.layers), num_pages, self.page_size, dtype, device)
+                if poison and g.storage.is_floating_point():
                     g.storage.fill_(float("nan"))
                 else:
                     g.storage.zero_()
+        self._state_kinds: Dict[int, CacheKind] = {}
         for i, spec in enumerate(cache_specs):
-            if isinstance(spec, PagedKV):
+            if spec is None:
+                self._layers.append(LayerCache())
+            elif kinds[i].paged:
                 g = self.groups[layer_group[i]]
-                j = g.layers.index(i)
-                k = g.storage[j, 0] if g.storage is not None else None
-                v = g.storage[j, 1] if g.storage is not None else None
-                self._layers.append(LayerCache(layer_group[i], True, k, v, None))
-            elif isinstance(spec, FixedState):
-                st = None
-                if device is not None:
-                    st = torch.zeros((max_requests,) + tuple(spec.shape), dtype=getattr(torch, spec.dtype), device=device)
+                self._layers.append(g.kind.layer_cache(g.storage, g.layers.index(i), layer_group[i]))
+            else:
+                st = kinds[i].allocate_state(spec, max_requests, device) if device is not None else None
                 self._layers.append(LayerCache(-1, True, None, None, st))
                 self._state_layers.append(i)
-            elif spec is None:
-                self._layers.append(LayerCache())
-            else:
-                raise TypeError("layer %d asks for a cache of unknown kind %r" % (i, spec))
+                self._state_kinds[i] = kinds[i]
         for i, j in enumerate(cache_of):
             if j is not None:
                 src = self._layers[j]
-                self._layers[i] = LayerCache(src.group, False, src.k_pool, src.v_pool, src.state)
+                self._layers[i] = LayerCache(src.group, False, src.k_pool, src.v_pool, src.state, src.pages)
 
     def __del__(self):
         book = getattr(self, "_book", None)
@@ -200,7 +186,7 @@ class CacheManager:
         for i in self._state_layers:
             st = self._layers[i].state
             if st is not None:
-                st[slot].zero_()
+                self._state_kinds[i].clear_slot(st, slot)
 
     # -- what layers see -------------------------------------------------------
     def layer(self, i: int) -> LayerCache:

@@ -74,7 +74,9 @@ paged_decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, cons
     const int start = (window > 0 && kv_len > window) ? kv_len - window : 0;
     const int tile_first = start >> 4;
     const int tile_last = (kv_len + 15) >> 4;  // exclusive
-    const int npieces = (tile_last - tile_first + piece_tiles - 1) / piece_tiles;
+    // (a caller whose max_pieces is too small for this request loses keys, but nothing is
+    // read or written outside the scratch)
+    const int npieces = min((tile_last - tile_first + piece_tiles - 1) / piece_tiles, max_pieces);
     if (piece >= npieces) return;
     const int tile_begin = tile_first + piece * piece_tiles;
     const int count = min(piece_tiles, tile_last - tile_begin);
@@ -279,7 +281,7 @@ __global__ void paged_decode_join_kernel(const float* __restrict__ part_o, const
     const int kv_len = positions[row_tok] + 1;
     const int start = (window > 0 && kv_len > window) ? kv_len - window : 0;
     const int ntiles = ((kv_len + 15) >> 4) - (start >> 4);
-    const int npieces = (ntiles + piece_tiles - 1) / piece_tiles;
+    const int npieces = min((ntiles + piece_tiles - 1) / piece_tiles, max_pieces);
     pdl_wait();  // on every path: a grid that ends without waiting would let its successor run ahead of its predecessor
     pdl_trigger();
     if (npieces <= 1) return;  // written by the first pass
@@ -342,13 +344,8 @@ extern "C" long long vx_paged_decode_scratch_floats(int requests, int H, int D, 
 }
 
 static int dec_sm_count() {
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    }
-    return sms;
+    static int sms[VX_MAX_DEVICES];
+    return vx_sm_count(sms);
 }
 
 template <int D, int STAGES, int WARPS>
@@ -371,19 +368,22 @@ static cudaError_t configure_decode_pieces() {
                                 cudaFuncAttributeMaxDynamicSharedMemorySize, WARPS * STAGES * 2 * 16 * D * 2);
 }
 
-// All four shapes of a head size at its first call (per process; the attribute is per
-// device function), whichever shape that call needs: a later call may come from inside a
-// stream capture with a step of another size.
+// All four shapes of a head size at its first call on a device (the attribute belongs
+// to a device's copy of the function), whichever shape that call needs: a later call
+// may come from inside a stream capture with a step of another size.  First calls are
+// not made from several host threads at once.
 template <int D>
 static int configure_decode() {
-    static bool configured = false;
-    if (configured) return VX_OK;
+    static bool configured[VX_MAX_DEVICES];
+    const int dev = vx_current_device();
+    if (dev < 0) return VX_ERR_LIMIT;
+    if (configured[dev]) return VX_OK;
     cudaError_t e = configure_decode_pieces<D, 6, 4>();
     if (e == cudaSuccess) e = configure_decode_pieces<D, 3, 4>();
     if (e == cudaSuccess) e = configure_decode_pieces<D, 5, 5>();
     if (e == cudaSuccess) e = configure_decode_pieces<D, 4, 6>();
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured[dev] = true;
     return VX_OK;
 }
 
@@ -461,8 +461,7 @@ extern "C" int vx_paged_decode_attention(const void* q, int q_row_stride, const 
 // cudaGetSymbolAddress below.
 static __device__ __align__(256) float g_decode_static_scratch[VX_DECODE_STATIC_SCRATCH_FLOATS];
 
-#define VX_STATIC_MAX_DEVICES 64
-static float* g_decode_static_ptr[VX_STATIC_MAX_DEVICES];  // device address of the array, per device
+static float* g_decode_static_ptr[VX_MAX_DEVICES];  // device address of the array, per device
 
 extern "C" long long vx_paged_decode_static_max_floats(void) { return VX_DECODE_STATIC_SCRATCH_FLOATS; }
 
@@ -480,7 +479,7 @@ extern "C" int vx_paged_decode_attention_static(const void* q, int q_row_stride,
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
-    if (dev < 0 || dev >= VX_STATIC_MAX_DEVICES) return VX_ERR_LIMIT;
+    if (dev < 0 || dev >= VX_MAX_DEVICES) return VX_ERR_LIMIT;
     if (!g_decode_static_ptr[dev]) {
         // set-up, once per device, with that device current
         float* p = nullptr;
@@ -489,7 +488,13 @@ extern "C" int vx_paged_decode_attention_static(const void* q, int q_row_stride,
         if (!p) return VX_ERR_ALIGN;
         g_decode_static_ptr[dev] = p;
     }
-    return vx_paged_decode_attention(q, q_row_stride, k_pool, v_pool, block_table, max_blocks, token_rows,
-                                     seq_of_token, positions, g_decode_static_ptr[dev], max_splits, out,
-                                     out_row_stride, scale, window, requests, H, Hk, D, S, chunk_tiles, stream);
+    // The kernel before this one in the stream is the caller's, not this library's: it may
+    // write what these kernels read ahead of their wait on it when launched programmatically
+    // (the step's description, keys and values of earlier positions).  So: plain stream order.
+    vx_pdl_suppress(1);
+    const int rc = vx_paged_decode_attention(q, q_row_stride, k_pool, v_pool, block_table, max_blocks, token_rows,
+                                             seq_of_token, positions, g_decode_static_ptr[dev], max_splits, out,
+                                             out_row_stride, scale, window, requests, H, Hk, D, S, chunk_tiles, stream);
+    vx_pdl_suppress(0);
+    return rc;
 }

@@ -33,7 +33,8 @@ __global__ void __launch_bounds__(PF_WARPS * 32)
 paged_prefill_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* __restrict__ k_pool,
                                const bf16* __restrict__ v_pool, const int* __restrict__ block_table,
                                int max_blocks, const int* __restrict__ cu_seqlens,
-                               const int* __restrict__ kv_offsets, bf16* __restrict__ out, int out_row_stride,
+                               const int* __restrict__ kv_offsets, const int* __restrict__ seq_list,
+                               bf16* __restrict__ out, int out_row_stride,
                                float scale_log2, int window, int H, int Hk, int S, int share_log2) {
     extern __shared__ __align__(128) unsigned char pf_smem[];
     constexpr int CHUNKS_PER_ROW = D / 8;
@@ -42,7 +43,8 @@ paged_prefill_attention_kernel(const bf16* __restrict__ q, int q_row_stride, con
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // the longest tiles (the last tokens of a prompt) are handed out first
-    const int qt = gridDim.x - 1 - blockIdx.x, seq = blockIdx.z;
+    // (the list of requests is part of the step's description, copied before the step's kernels)
+    const int qt = gridDim.x - 1 - blockIdx.x, seq = seq_list ? seq_list[blockIdx.z] : (int)blockIdx.z;
     const int share = 1 << share_log2;                  // query heads of one kv head that share this tile
     const int toks_per_tile = PF_BM >> share_log2;
     const int row_base = cu_seqlens[seq];
@@ -257,16 +259,11 @@ paged_prefill_attention_kernel(const bf16* __restrict__ q, int q_row_stride, con
 template <int D>
 static int launch_prefill(const bf16* q, int q_row_stride, const bf16* k_pool, const bf16* v_pool,
                           const int* block_table, int max_blocks, const int* cu_seqlens, const int* kv_offsets,
-                          bf16* out, int out_row_stride, float scale, int window, int requests, int max_new,
-                          int H, int Hk, int S, cudaStream_t stream) {
+                          const int* seq_list, bf16* out, int out_row_stride, float scale, int window, int requests,
+                          int max_new, int H, int Hk, int S, cudaStream_t stream) {
     const size_t smem = (size_t)PF_BM * D * 2 + 2 * 2 * (size_t)PF_BN * D * 2;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(paged_prefill_attention_kernel<D>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static bool configured[VX_MAX_DEVICES];
+    if (int rc = vx_configure_smem(paged_prefill_attention_kernel<D>, smem, configured)) return rc;
     // Query heads of one kv head share a tile (and so its key/value traffic) when
     // their number is a power of two up to 16; otherwise every head has its own tiles.
     const int G = H / Hk;
@@ -276,18 +273,20 @@ static int launch_prefill(const bf16* q, int q_row_stride, const bf16* k_pool, c
     const int toks_per_tile = PF_BM >> share_log2;
     dim3 grid((max_new + toks_per_tile - 1) / toks_per_tile, share_log2 ? Hk : H, requests);
     VX_LAUNCH_K(VX_K_ATTENTION, (paged_prefill_attention_kernel<D>), grid, PF_WARPS * 32, smem, stream, q,
-                q_row_stride, k_pool, v_pool, block_table, max_blocks, cu_seqlens, kv_offsets, out, out_row_stride,
-                scale * PF_LOG2E, window, H, Hk, S, share_log2);
+                q_row_stride, k_pool, v_pool, block_table, max_blocks, cu_seqlens, kv_offsets, seq_list, out,
+                out_row_stride, scale * PF_LOG2E, window, H, Hk, S, share_log2);
     VX_LAUNCH_CHECK();
     return VX_OK;
 }
 
 // Request i brings the token rows [cu_seqlens[i], cu_seqlens[i+1]) at positions
 // kv_offsets[i], kv_offsets[i] + 1, ...; its keys and values (these new ones
-// included) are in the pools.  `max_new` bounds the tokens of any request.
+// included) are in the pools.  `max_new` bounds the tokens of any request.  With
+// `seq_list` (device, `requests` entries) only the requests it names are worked on:
+// a mixed step gives its single decoded tokens to the decode kernel instead.
 extern "C" int vx_paged_prefill_attention(const void* q, int q_row_stride, const void* k_pool,
                                           const void* v_pool, const int* block_table, int max_blocks,
-                                          const int* cu_seqlens, const int* kv_offsets, void* out,
+                                          const int* cu_seqlens, const int* kv_offsets, const int* seq_list, void* out,
                                           int out_row_stride, float scale, int window, int requests,
                                           int max_new, int H, int Hk, int D, int S, cudaStream_t stream) {
     if (requests <= 0 || max_new <= 0) return VX_OK;
@@ -297,11 +296,11 @@ extern "C" int vx_paged_prefill_attention(const void* q, int q_row_stride, const
         return VX_ERR_ALIGN;
     if (D == 128)
         return launch_prefill<128>((const bf16*)q, q_row_stride, (const bf16*)k_pool, (const bf16*)v_pool,
-                                   block_table, max_blocks, cu_seqlens, kv_offsets, (bf16*)out, out_row_stride,
+                                   block_table, max_blocks, cu_seqlens, kv_offsets, seq_list, (bf16*)out, out_row_stride,
                                    scale, window, requests, max_new, H, Hk, S, stream);
     if (D == 64)
         return launch_prefill<64>((const bf16*)q, q_row_stride, (const bf16*)k_pool, (const bf16*)v_pool,
-                                  block_table, max_blocks, cu_seqlens, kv_offsets, (bf16*)out, out_row_stride,
+                                  block_table, max_blocks, cu_seqlens, kv_offsets, seq_list, (bf16*)out, out_row_stride,
                                   scale, window, requests, max_new, H, Hk, S, stream);
     return VX_ERR_SHAPE;
 }

@@ -185,7 +185,8 @@ __global__ void __launch_bounds__(PT_THREADS)
 paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                   const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
                                   int max_blocks, const int* __restrict__ cu_seqlens,
-                                  const int* __restrict__ kv_offsets, bf16* __restrict__ out, int out_row_stride,
+                                  const int* __restrict__ kv_offsets, const int* __restrict__ seq_list,
+                                  bf16* __restrict__ out, int out_row_stride,
                                   float scale_log2, int window, int H, int Hk, int S, int share_log2,
                                   int* __restrict__ error) {
     extern __shared__ unsigned char pt_smem_raw[];
@@ -202,7 +203,8 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // the longest tiles (the last tokens of a prompt) are handed out first
-    const int qt = gridDim.x - 1 - blockIdx.x, hk = blockIdx.y, seq = blockIdx.z;
+    const int qt = gridDim.x - 1 - blockIdx.x, hk = blockIdx.y;
+    const int seq = seq_list ? seq_list[blockIdx.z] : (int)blockIdx.z;
     const int share = 1 << share_log2;
     const int toks_per_tile = PT_ROWS >> share_log2;
     const int row_base = cu_seqlens[seq];
@@ -552,10 +554,11 @@ static bool pt_make_map(CUtensorMap* map, const void* base, long long rows, int 
 // Request i brings the token rows [cu_seqlens[i], cu_seqlens[i+1]) of q (`tokens` rows
 // in all, row stride q_row_stride, query head h at columns h * 128) at positions
 // kv_offsets[i] onward; pools are [pages, Hk, S, 128].  `error`: a device int a block
-// sets if one of its bounded waits runs out.
+// sets if one of its bounded waits runs out.  With `seq_list` (device, `requests`
+// entries) only the requests it names are worked on.
 extern "C" int vx_paged_prefill_attention_tc(const void* q, int q_row_stride, int tokens, const void* k_pool,
                                              const void* v_pool, int pages, const int* block_table, int max_blocks,
-                                             const int* cu_seqlens, const int* kv_offsets, void* out,
+                                             const int* cu_seqlens, const int* kv_offsets, const int* seq_list, void* out,
                                              int out_row_stride, float scale, int window, int requests, int max_new,
                                              int H, int Hk, int D, int S, int* error, cudaStream_t stream) {
     if (requests <= 0 || max_new <= 0 || tokens <= 0) return VX_OK;
@@ -575,16 +578,11 @@ extern "C" int vx_paged_prefill_attention_tc(const void* q, int q_row_stride, in
         !pt_make_map(&mv, v_pool, (long long)pages * Hk * S, D, D, 16))
         return VX_ERR_DRIVER;
     const size_t smem = 5 * (size_t)PT_TILE_BYTES + 1024;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(paged_prefill_attention_tc_kernel,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static bool configured[VX_MAX_DEVICES];
+    if (int rc = vx_configure_smem(paged_prefill_attention_tc_kernel, smem, configured)) return rc;
     dim3 grid((max_new + toks_per_tile - 1) / toks_per_tile, Hk, requests);
     VX_LAUNCH_K(VX_K_ATTENTION, paged_prefill_attention_tc_kernel, grid, PT_THREADS, smem, stream, mq, mk, mv,
-                block_table, max_blocks, cu_seqlens, kv_offsets, (bf16*)out, out_row_stride, scale * PT_LOG2E, window, H,
+                block_table, max_blocks, cu_seqlens, kv_offsets, seq_list, (bf16*)out, out_row_stride, scale * PT_LOG2E, window, H,
                 Hk, S, share_log2, error);
     VX_LAUNCH_CHECK();
     return VX_OK;

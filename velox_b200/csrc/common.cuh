@@ -47,7 +47,41 @@ typedef __nv_bfloat16 bf16;
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// Set-up that belongs to a device's copy of a kernel (the opt-in to more dynamic
+// shared memory, the SM count) is remembered per device: a process may hold engines
+// on several GPUs.  The index of the current device, or -1 if it cannot be had or
+// is beyond VX_MAX_DEVICES.
+#define VX_MAX_DEVICES 64
+static inline int vx_current_device() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= VX_MAX_DEVICES) return -1;
+    return dev;
+}
+// Sets a kernel's dynamic shared-memory limit once per device (`done`: VX_MAX_DEVICES flags).
+template <typename K>
+static inline int vx_configure_smem(K kernel, size_t smem, bool* done) {
+    const int dev = vx_current_device();
+    if (dev < 0) return VX_ERR_LIMIT;
+    if (done[dev]) return VX_OK;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    done[dev] = true;
+    return VX_OK;
+}
+// Multiprocessors of the current device (`cache`: VX_MAX_DEVICES ints, zero at first).
+static inline int vx_sm_count(int* cache) {
+    const int dev = vx_current_device();
+    if (dev < 0) return 148;
+    if (!cache[dev] && (cudaDeviceGetAttribute(&cache[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+                        cache[dev] <= 0))
+        cache[dev] = 148;
+    return cache[dev];
+}
+
 extern "C" int vx_pdl_is_enabled(void);
+// While set (per host thread), kernels are launched in plain stream order whatever
+// vx_set_pdl says: for entry points whose predecessor in the stream is not this library's.
+extern "C" void vx_pdl_suppress(int on);
 extern "C" int vx_pdl_mask(void);
 
 // Kernel classes, for switching programmatic dependent launch on and off per class

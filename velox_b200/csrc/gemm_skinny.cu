@@ -161,15 +161,8 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, const
 // 10240x5120 23/23/22/19.  Variant 1 fills the register file, which keeps the
 // next kernel's blocks out until it ends.
 static int sm_count() {
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0, n = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-            n = 148;
-        sms = n;
-    }
-    return sms;
+    static int sms[VX_MAX_DEVICES];
+    return vx_sm_count(sms);
 }
 
 static int pick_variant(int N, int K) {

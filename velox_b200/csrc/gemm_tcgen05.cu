@@ -307,20 +307,11 @@ template <int BN, int STAGES, bool GATED>
 static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mw, const float* bias, bf16* C, int M, int N, int K,
                      int ldc, int act, int* error, cudaStream_t stream) {
     const size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 1024;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, GATED>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static bool configured[VX_MAX_DEVICES];
+    if (int rc = vx_configure_smem(gemm_tcgen05_kernel<BN, STAGES, GATED>, smem, configured)) return rc;
     // persistent: one block per SM (its shared memory fills one), fewer if there are fewer tiles
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    }
+    static int sm_counts[VX_MAX_DEVICES];
+    const int sms = vx_sm_count(sm_counts);
     const int tiles = ((M + TC_BM - 1) / TC_BM) * ((N + BN - 1) / BN);
     dim3 grid(tiles < sms ? tiles : sms);
     VX_LAUNCH_K(VX_K_GEMM, (gemm_tcgen05_kernel<BN, STAGES, GATED>), grid, TC_THREADS, smem, stream, ma, mw, bias, C, M,

@@ -2,8 +2,12 @@
 // buffer of 32-bit words whose sections start at the given offsets:
 //   0 token_ids [tokens]      1 positions [tokens]     2 seq_of_token [tokens]
 //   3 cu_seqlens [requests+1] 4 kv_offsets [requests]  5 state_slots [requests]
-//   6 wanted_rows [wanted]    then per group: block_table [requests, max_blocks],
-//   slot_mapping [tokens] (page * page_size + offset of each new position).
+//   6 wanted_rows [wanted]    7 single_rows [requests]  8 portion_seqs [requests]
+//   then per group: block_table [requests, max_blocks], slot_mapping [tokens] (page *
+//   page_size + offset of each new position).
+// single_rows lists the token rows of the requests that bring exactly one token,
+// portion_seqs the requests (rows of the step) that bring more: a mixed step hands
+// the first to the decode attention and the second to the prompt attention.
 // The reference rebuilds and uploads block tables and offsets inside every layer
 // (src/paged/qwen3.rs:584-627); here the description is built once per step and
 // shared by all layers.
@@ -17,7 +21,8 @@ namespace vxh {
 // A general step: request i brings lens[i] tokens (concatenated in `tokens`) and
 // asks for want_counts[i] places among them (concatenated in `wants`).  The pages
 // must have been reserved.  summary: total tokens, wanted rows, longest portion,
-// largest number of keys any request will have.
+// largest number of keys any request will have, requests that bring one token, the
+// largest number of keys among those, requests that bring more, (unused).
 inline int build_step(CacheBook& book, int n, const int64_t* rids, const int* lens, const int* tokens,
                       const int* want_counts, const int* wants, int vocab, int32_t* dst, const int64_t* starts,
                       int64_t* summary) {
@@ -29,7 +34,9 @@ inline int build_step(CacheBook& book, int n, const int64_t* rids, const int* le
     int32_t* offsets = dst + starts[4];
     int32_t* slots = dst + starts[5];
     int32_t* wanted = dst + starts[6];
-    int64_t row = 0, nw = 0, max_new = 0, max_kv = 0;
+    int32_t* single_rows = dst + starts[7];
+    int32_t* portion_seqs = dst + starts[8];
+    int64_t row = 0, nw = 0, max_new = 0, max_kv = 0, n_single = 0, n_portions = 0, max_kv_single = 0;
     const int* tok = tokens;
     const int* want = wants;
     cu[0] = 0;
@@ -59,8 +66,8 @@ inline int build_step(CacheBook& book, int n, const int64_t* rids, const int* le
                 return fail(ERR_VALUE, "entry " + std::to_string(i) + ": block table too short (" +
                                            std::to_string(table.size()) + " pages for " + std::to_string(rc->length + k) +
                                            " positions)");
-            int32_t* bt = dst + starts[7 + 2 * g] + (int64_t)i * MB;
-            int32_t* sm = dst + starts[8 + 2 * g] + row;
+            int32_t* bt = dst + starts[9 + 2 * g] + (int64_t)i * MB;
+            int32_t* sm = dst + starts[10 + 2 * g] + row;
             std::memcpy(bt, book.group(g).mirror.data() + (size_t)rc->slot * MB, sizeof(int32_t) * MB);
             for (int j = 0; j < k; ++j) {
                 const int64_t pos = rc->length + j;
@@ -69,6 +76,12 @@ inline int build_step(CacheBook& book, int n, const int64_t* rids, const int* le
                     return fail(ERR_VALUE, "entry " + std::to_string(i) + ": a new position falls into a page that was given back");
                 sm[j] = (int32_t)(page * S + pos % S);
             }
+        }
+        if (k == 1) {
+            single_rows[n_single++] = (int32_t)row;
+            max_kv_single = std::max<int64_t>(max_kv_single, rc->length + 1);
+        } else {
+            portion_seqs[n_portions++] = i;
         }
         row += k;
         tok += k;
@@ -80,13 +93,17 @@ inline int build_step(CacheBook& book, int n, const int64_t* rids, const int* le
     summary[1] = nw;
     summary[2] = max_new;
     summary[3] = max_kv;
+    summary[4] = n_single;
+    summary[5] = max_kv_single;
+    summary[6] = n_portions;
+    summary[7] = 0;
     return OK;
 }
 
 // A step of decoded tokens only (one per request), padded to `bucket` rows that
 // read page 0 at position 0 and write nothing (slot -1).  Only the columns of the
 // block tables that these requests can reach are written.  The sections for
-// seq_of_token, cu_seqlens and wanted_rows are constant and left alone.
+// seq_of_token, cu_seqlens, wanted_rows, single_rows and portion_seqs are constant and left alone.
 inline int fill_decode(CacheBook& book, int n, int bucket, const int64_t* rids, const int* tokens, int vocab,
                        int32_t* dst, const int64_t* starts, int64_t* max_kv_out) {
     const int S = book.page_size(), MB = book.max_blocks(), G = book.num_groups();
@@ -109,8 +126,8 @@ inline int fill_decode(CacheBook& book, int n, int bucket, const int64_t* rids, 
     for (int i = n; i < bucket; ++i) token_ids[i] = positions[i] = offsets[i] = slots[i] = 0;
     const int cols = (int)std::min<int64_t>(MB, max_pos / S + 1);
     for (int g = 0; g < G; ++g) {
-        int32_t* bt = dst + starts[7 + 2 * g];
-        int32_t* sm = dst + starts[8 + 2 * g];
+        int32_t* bt = dst + starts[9 + 2 * g];
+        int32_t* sm = dst + starts[10 + 2 * g];
         const int32_t* mirror = book.group(g).mirror.data();
         for (int i = 0; i < n; ++i) {
             const int32_t* src = mirror + (size_t)rcs[i]->slot * MB;

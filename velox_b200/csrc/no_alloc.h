@@ -15,6 +15,14 @@
 // Contract:
 //   * Same arguments and same results as vx_paged_decode_attention, minus the
 //     scratch pointer.  Inputs and outputs are still the caller's.
+//   * max_splits must bound the pieces of every request in the call:
+//     ceil(ceil(keys / 16) / chunk_tiles) for the request with the most keys, one
+//     more if there is a window.  The device cannot tell the host that it was too
+//     small: a request with more pieces than that loses its last keys (the result
+//     is wrong), though nothing outside the scratch is read or written.
+//   * The kernels run in plain stream order after whatever the caller launched
+//     before (no programmatic dependent launch), so the caller's previous kernel
+//     may write any of the inputs.
 //   * Allocates nothing: no cudaMalloc, cudaFree or allocating library call.
 //   * requests * H * max_splits * (D + 2) must not exceed
 //     VX_DECODE_STATIC_SCRATCH_FLOATS; otherwise nothing runs and the call
@@ -22,7 +30,8 @@
 //     the limit.
 //   * The first call on each device looks up the array's device address
 //     (cudaGetSymbolAddress, with that device current) and configures the
-//     kernel (every block shape it may pick for later steps).  Make that first call before any stream capture begins.
+//     kernel (every block shape it may pick for later steps).  Make that first
+//     call before any stream capture begins, and from one host thread.
 //   * All calls share the one array, and it keeps whatever the previous call
 //     left in it.  The kernels write every scratch element before reading it,
 //     so nothing needs clearing; but two calls that overlap on the GPU (on

@@ -73,8 +73,8 @@ def _declare(lib) -> None:
         "vx_gemm_nt_simt": [P, P, P, P, I, I, I, I, I, I, I, I, P],
         "vx_gemm_tcgen05": [P, P, P, P, I, I, I, I, I, I, I, I, I, P, P],
         "vx_gemm_skinny": [P, P, P, P, I, I, I, I, I, I, I, I, I, I, P],
-        "vx_paged_prefill_attention_tc": [P, I, I, P, P, I, P, I, P, P, P, I, F, I, I, I, I, I, I, I, P, P],
-        "vx_paged_prefill_attention": [P, I, P, P, P, I, P, P, P, I, F, I, I, I, I, I, I, I, P],
+        "vx_paged_prefill_attention_tc": [P, I, I, P, P, I, P, I, P, P, P, P, I, F, I, I, I, I, I, I, I, P, P],
+        "vx_paged_prefill_attention": [P, I, P, P, P, I, P, P, P, P, I, F, I, I, I, I, I, I, I, P],
         "vx_paged_decode_attention": [P, I, P, P, P, I, P, P, P, P, I, P, I, F, I, I, I, I, I, I, I, P],
         "vx_sample": [P, I, I, I, P, P, P, P, P],
     }
@@ -322,19 +322,23 @@ def prefill_attention_supported(dtype, head_dim: int, page_size: int) -> bool:
 
 def paged_prefill_attention(q: torch.Tensor, q_row_stride: int, k_pool, v_pool, block_table: torch.Tensor,
                             cu_seqlens, kv_offsets, scale: float, window: int, num_heads: int, num_kv_heads: int,
-                            head_dim: int, requests: int, max_new: int, tokens: int) -> torch.Tensor:
+                            head_dim: int, requests: int, max_new: int, tokens: int, seq_list=None,
+                            out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of prompt portions over the pages (bfloat16, tensor cores):
     request i brings token rows [cu_seqlens[i], cu_seqlens[i+1]) at positions
-    kv_offsets[i] onward; `max_new` bounds the tokens of any request."""
-    _dev(q, k_pool, v_pool, block_table, cu_seqlens, kv_offsets)
+    kv_offsets[i] onward; `max_new` bounds the tokens of any request.  With `seq_list`
+    (int32, on the device) only its first `requests` entries' requests are worked on,
+    and only their rows of `out` are written."""
+    _dev(q, k_pool, v_pool, block_table, cu_seqlens, kv_offsets, seq_list, out)
     _need(q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and v_pool.dtype == torch.bfloat16,
           "paged_prefill_attention: bfloat16 only")
     _need(block_table.dtype == torch.int32 and block_table.is_contiguous() and block_table.dim() == 2,
           "paged_prefill_attention: int32 block table [requests, blocks]")
-    out = torch.empty((tokens, num_heads * head_dim), dtype=q.dtype, device=q.device)
+    if out is None:
+        out = torch.empty((tokens, num_heads * head_dim), dtype=q.dtype, device=q.device)
     _check(library().vx_paged_prefill_attention(
         _ptr(q), q_row_stride, _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1],
-        _ptr(cu_seqlens), _ptr(kv_offsets), _ptr(out), num_heads * head_dim, float(scale), int(window), requests,
+        _ptr(cu_seqlens), _ptr(kv_offsets), _ptr(seq_list), _ptr(out), num_heads * head_dim, float(scale), int(window), requests,
         int(max_new), num_heads, num_kv_heads, head_dim, k_pool.shape[2], _stream()), "paged_prefill_attention")
     return out
 
@@ -345,21 +349,24 @@ def prefill_attention_tc_supported(dtype, head_dim: int, page_size: int, group: 
 
 def paged_prefill_attention_tc(q: torch.Tensor, q_row_stride: int, k_pool, v_pool, block_table: torch.Tensor,
                                cu_seqlens, kv_offsets, scale: float, window: int, num_heads: int, num_kv_heads: int,
-                               head_dim: int, requests: int, max_new: int, tokens: int) -> torch.Tensor:
+                               head_dim: int, requests: int, max_new: int, tokens: int, seq_list=None,
+                               out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The same as `paged_prefill_attention` on the tcgen05 tensor cores (head size
     128, accumulators in tensor memory, operands by TMA)."""
-    _dev(q, k_pool, v_pool, block_table, cu_seqlens, kv_offsets)
+    _dev(q, k_pool, v_pool, block_table, cu_seqlens, kv_offsets, seq_list, out)
     _need(q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and v_pool.dtype == torch.bfloat16,
           "paged_prefill_attention_tc: bfloat16 only")
     _need(block_table.dtype == torch.int32 and block_table.is_contiguous() and block_table.dim() == 2,
           "paged_prefill_attention_tc: int32 block table [requests, blocks]")
     _need(k_pool.is_contiguous() and v_pool.is_contiguous(), "paged_prefill_attention_tc: contiguous pools")
-    out = torch.empty((tokens, num_heads * head_dim), dtype=q.dtype, device=q.device)
+    if out is None:
+        out = torch.empty((tokens, num_heads * head_dim), dtype=q.dtype, device=q.device)
     _check(library().vx_paged_prefill_attention_tc(
         _ptr(q), q_row_stride, tokens, _ptr(k_pool), _ptr(v_pool), k_pool.shape[0], _ptr(block_table),
-        block_table.shape[1], _ptr(cu_seqlens), _ptr(kv_offsets), _ptr(out), num_heads * head_dim, float(scale),
+        block_table.shape[1], _ptr(cu_seqlens), _ptr(kv_offsets), _ptr(seq_list), _ptr(out), num_heads * head_dim, float(scale),
         int(window), requests, int(max_new), num_heads, num_kv_heads, head_dim, k_pool.shape[2],
         _ptr(_error_word(q.device)), _stream()), "paged_prefill_attention_tc")
+    note_bounded_wait()
     return out
 
 
@@ -390,9 +397,40 @@ def _error_word(device) -> torch.Tensor:
     return _ERROR_WORDS[key]
 
 
+_BOUNDED_WAIT_LAUNCHES = 0   # launches of kernels with bounded waits, ever
+_BOUNDED_WAIT_CHECKED = 0    # ... at the last check of the error word
+
+
+def bounded_wait_launches() -> int:
+    return _BOUNDED_WAIT_LAUNCHES
+
+
+def note_bounded_wait(n: int = 1) -> None:
+    """A kernel whose waits are bounded was launched (by the wrappers below, or by
+    the replay of a graph that holds such kernels): the error word has to be read
+    before the step's results are trusted."""
+    global _BOUNDED_WAIT_LAUNCHES
+    _BOUNDED_WAIT_LAUNCHES += n
+
+
+def bounded_wait_pending() -> bool:
+    """True if a kernel with bounded waits was launched since the error word was last read."""
+    return _BOUNDED_WAIT_LAUNCHES != _BOUNDED_WAIT_CHECKED
+
+
+def check_pending_device_errors() -> None:
+    """`check_device_errors()` if a kernel with bounded waits ran since the last check,
+    else nothing (and no synchronisation).  What steps a model calls this before it
+    hands out a step's results; it does not have to know which kernels a part chose."""
+    if bounded_wait_pending():
+        check_device_errors()
+
+
 def check_device_errors() -> None:
     """Raises if a kernel has reported that one of its bounded waits ran out since
     the last check (its results are then missing).  Synchronises the device."""
+    global _BOUNDED_WAIT_CHECKED
+    _BOUNDED_WAIT_CHECKED = _BOUNDED_WAIT_LAUNCHES
     for key, word in _ERROR_WORDS.items():
         code = int(word.item())
         if code:
@@ -429,6 +467,7 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias=None, gated_activation: 
     _check(library().vx_gemm_tcgen05(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), m, n, k, a.stride(0), w.stride(0), cols,
                                      1 if gated_activation else 0, ACTIVATIONS.get(gated_activation, 0),
                                      1 if wide else 0, _ptr(_error_word(a.device)), _stream()), "gemm_tcgen05")
+    note_bounded_wait()
     return out
 
 

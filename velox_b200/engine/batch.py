@@ -43,6 +43,8 @@ class StepContext:
     kv_offsets: torch.Tensor     # int32 [requests], positions already cached before the step
     state_slots: torch.Tensor    # int32 [requests], the request's state slot
     wanted_rows: torch.Tensor    # int32 [wanted], token rows whose logits are asked for
+    single_rows: torch.Tensor    # int32 [requests]: token rows of the requests that bring one token (first n_single)
+    portion_seqs: torch.Tensor   # int32 [requests]: the requests that bring more than one (first n_portions)
     groups: List[GroupContext]
     # host copies for decisions that need no device round trip
     new_lens: List[int] = field(default_factory=list)
@@ -50,16 +52,23 @@ class StepContext:
     slots: List[int] = field(default_factory=list)
     max_new: int = 0
     max_kv: int = 0
+    n_single: int = 0        # requests that bring exactly one token
+    max_kv_single: int = 0   # most keys of any of those after the step
+    n_portions: int = 0      # requests that bring more
 
     @property
     def decode_only(self) -> bool:
         return self.max_new == 1
 
 
+SECTION_NAMES = ["token_ids", "positions", "seq_of_token", "cu_seqlens", "kv_offsets", "state_slots", "wanted_rows",
+                 "single_rows", "portion_seqs"]
+
+
 def _sections(n: int, total: int, wanted: int, n_groups: int, max_blocks: int):
     """Sizes and starts (in 32-bit words, every section on a 16-byte boundary) of the
     sections of a step's description, in the host library's order."""
-    sizes = [total, total, total, n + 1, n, n, wanted]
+    sizes = [total, total, total, n + 1, n, n, wanted, n, n]
     for _ in range(n_groups):
         sizes += [n * max_blocks, total]
     starts, cur = [], 0
@@ -73,7 +82,8 @@ def build_step_arrays(entries: Sequence[StepEntry], cache, vocab_size: Optional[
     """The step's description after the cache has reserved the pages, written by the
     host library into `out` (a writable int32 numpy array, made if not given).
     Returns (out, sizes, starts, summary) with summary = (tokens, wanted rows,
-    longest portion, most keys of any request after the step)."""
+    longest portion, most keys of any request after the step, requests that bring
+    one token, most keys among those, requests that bring more, unused)."""
     from .. import native
 
     n = len(entries)
@@ -95,7 +105,7 @@ def build_step_arrays(entries: Sequence[StepEntry], cache, vocab_size: Optional[
         for w in e.want:
             if not 0 <= w < k:
                 raise ValueError("request %r: wanted place %r is not among its %d tokens" % (e.request_id, w, k))
-    summary = (ctypes.c_int64 * 4)()
+    summary = (ctypes.c_int64 * 8)()
     native.check(cache._lib.vxh_build_step(
         cache._book, n, rids, native.int_array(lens), tokens.ctypes.data_as(ctypes.POINTER(ctypes.c_int)),
         native.int_array(len(e.want) for e in entries), native.int_array(w for e in entries for w in e.want),
@@ -113,12 +123,12 @@ def build_step_context(entries: Sequence[StepEntry], cache, device, vocab_size: 
     hv, sizes, starts, summary = build_step_arrays(entries, cache, vocab_size, out=host.numpy())
     dev = host.to(device, non_blocking=True)
     views = [dev[st:st + s] for st, s in zip(starts, sizes)]
-    names = ["token_ids", "positions", "seq_of_token", "cu_seqlens", "kv_offsets", "state_slots", "wanted_rows"]
-    named = dict(zip(names, views[:7]))
-    gviews = views[7:]
+    named = dict(zip(SECTION_NAMES, views[:len(SECTION_NAMES)]))
+    gviews = views[len(SECTION_NAMES):]
     MB = cache.max_blocks
     gctx = [GroupContext(gviews[2 * i].view(n, MB), gviews[2 * i + 1]) for i in range(len(cache.groups))]
     offs = [int(x) for x in hv[starts[4]:starts[4] + n]]
     return StepContext(
         n_tokens=summary[0], n_seqs=n, groups=gctx, new_lens=lens, offsets=offs,
-        slots=[int(x) for x in hv[starts[5]:starts[5] + n]], max_new=summary[2], max_kv=summary[3], **named)
+        slots=[int(x) for x in hv[starts[5]:starts[5] + n]], max_new=summary[2], max_kv=summary[3],
+        n_single=summary[4], max_kv_single=summary[5], n_portions=summary[6], **named)

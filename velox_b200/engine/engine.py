@@ -24,7 +24,8 @@ from ..config.engine_config import EngineConfig
 from ..config.model_config import ModelConfig
 from ..config.registry import load_config, resolve_architecture
 from ..models.decoder import DecoderModel
-from ..parts.base import PagedKV, Runtime
+from ..cache.kinds import cache_kind
+from ..parts.base import Runtime
 from ..sampling.params import SamplingParams
 from ..sampling.rng import uniform
 from ..weights.loader import load_weights
@@ -112,7 +113,8 @@ class Engine:
         if cfg.max_cache_tokens:
             return -(-int(cfg.max_cache_tokens) // cfg.page_size)
         elt = 2 if self.runtime.dtype == torch.bfloat16 else 4
-        per_page = sum(2 * s.num_kv_heads * s.head_dim * cfg.page_size * elt for s in specs if isinstance(s, PagedKV))
+        kinds = [(cache_kind(s), s) for s in specs if s is not None]
+        per_page = sum(k.page_bytes(s, cfg.page_size, elt) for k, s in kinds if k.paged)
         wanted = cfg.max_running_requests * max_blocks
         if per_page == 0:
             return max(1, min(wanted, 1024))
@@ -159,9 +161,7 @@ class Engine:
         if self.on_logits is not None and logits is not None:
             # (a captured step's logits live in the graph's buffer until the next step only)
             self.on_logits([e.request_id for e in entries if e.want], logits[:len(sampled)])
-        if self.runner.pending_error_check:
-            self.runner.pending_error_check = False
-            ops.check_device_errors()
+        self.runner.check_errors()
         return self.scheduler.update(entries, sampled)
 
     def capture_decode_graphs(self, max_batch: Optional[int] = None, max_tokens: Optional[int] = None) -> int:
@@ -176,7 +176,9 @@ class Engine:
 
     def run_step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """The raw step function, for callers that schedule themselves."""
-        return self.runner.step(entries)
+        logits = self.runner.step(entries)
+        self.runner.check_errors()
+        return logits
 
     def generate(self, prompts: Sequence[Sequence[int]], params=None) -> List[List[int]]:
         """Generates for every prompt (host token ids in, host token ids out).

@@ -9,7 +9,8 @@ graph; embedding, all layers, the head and the sampling kernel run from there.
 
 Padding: a batch is padded up to its bucket with rows that read page 0 at
 position 0 and write nothing (slot -1); their tokens are dropped.  Models with
-per-request state are never padded (a padded row would touch a real slot), and
+per-request state are never padded (a padded row would touch a real slot) and
+capture a graph in the step that first needs it (that step runs eagerly, once), and
 models with a part that is not marked `cuda_graph_safe` (it reads host-side
 fields of the step) do not use graphs at all.
 """
@@ -25,7 +26,7 @@ import torch
 
 from .. import native
 from ..csrc import ops
-from .batch import GroupContext, StepContext, StepEntry
+from .batch import SECTION_NAMES, GroupContext, StepContext, StepEntry
 
 SPLIT_KEYS = ops.DECODE_CHUNK_TILES * 16
 
@@ -65,8 +66,8 @@ class _Graph:
         self.bucket, self.max_kv = bucket, max_kv
         MB, G = cache.max_blocks, len(cache.groups)
         B = bucket
-        names = ["token_ids", "positions", "seq_of_token", "cu_seqlens", "kv_offsets", "state_slots", "wanted_rows"]
-        sizes = [B, B, B, B + 1, B, B, B]
+        names, F = SECTION_NAMES, len(SECTION_NAMES)
+        sizes = [B, B, B, B + 1, B, B, B, B, B]
         for _ in range(G):
             sizes += [B * MB, B]
         sizes += [B, B, B]  # temperature, top_p, uniform (float32 bit patterns)
@@ -82,21 +83,24 @@ class _Graph:
         self.dev = torch.zeros(cur, dtype=torch.int32, device=device)
         v = [self.dev[st:st + s] for st, s in zip(self.starts, sizes)]
         hvv = [self.hv[st:st + s] for st, s in zip(self.starts, sizes)]
-        self.h = dict(zip(names, hvv[:7]))
-        self.h_groups = [(hvv[7 + 2 * g].reshape(B, MB), hvv[8 + 2 * g]) for g in range(G)]
-        self.h_temp, self.h_top_p, self.h_uniform = (x.view(np.float32) for x in hvv[7 + 2 * G:])
-        groups = [GroupContext(v[7 + 2 * g].view(B, MB), v[8 + 2 * g]) for g in range(G)]
-        f = [x.view(torch.float32) for x in v[7 + 2 * G:]]
+        self.h = dict(zip(names, hvv[:F]))
+        self.h_groups = [(hvv[F + 2 * g].reshape(B, MB), hvv[F + 1 + 2 * g]) for g in range(G)]
+        self.h_temp, self.h_top_p, self.h_uniform = (x.view(np.float32) for x in hvv[F + 2 * G:])
+        groups = [GroupContext(v[F + 2 * g].view(B, MB), v[F + 1 + 2 * g]) for g in range(G)]
+        f = [x.view(torch.float32) for x in v[F + 2 * G:]]
         self.d_temp, self.d_top_p, self.d_uniform = f
         self.ctx = StepContext(n_tokens=B, n_seqs=B, groups=groups, new_lens=[1] * B, offsets=[0] * B,
-                               slots=[0] * B, max_new=1, max_kv=max_kv, **dict(zip(names, v[:7])))
+                               slots=[0] * B, max_new=1, max_kv=max_kv, n_single=B, max_kv_single=max_kv,
+                               n_portions=0, **dict(zip(names, v[:F])))
         # constant sections
         self.h["seq_of_token"][:] = np.arange(B)
         self.h["cu_seqlens"][:] = np.arange(B + 1)
         self.h["wanted_rows"][:] = np.arange(B)
+        self.h["single_rows"][:] = np.arange(B)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits = self.ids = None
         self.launches = 0
+        self.bounded_wait_launches = 0  # of those, kernels whose waits are bounded
         self.copied: Optional[torch.cuda.Event] = None  # the last copy out of the pinned buffer
 
     def fill(self, entries: Sequence[StepEntry], rids, cache, sampling, vocab_size: int = -1) -> None:
@@ -172,9 +176,17 @@ class DecodeGraphs:
             g = self.graphs[key] = _Graph(self.runner, *key)
         g.fill(entries, rids, cache, sampling, self.runner.vocab_size)
         if g.graph is None:
+            # The capture runs the step once, eagerly, on this step's real rows (a recording
+            # runs nothing).  That run IS this step: its results are handed out and the graph
+            # is replayed from the next step on.  Replaying it now as well would only write
+            # the same keys and values again, but it would advance a mixer's per-request
+            # state a second time.
             self._capture(g)
+            return g.logits, g.ids
         g.graph.replay()
         ops.add_launches(g.launches)
+        if g.bounded_wait_launches:
+            ops.note_bounded_wait(g.bounded_wait_launches)
         return g.logits, g.ids
 
     def _capture(self, g: _Graph) -> None:
@@ -186,14 +198,15 @@ class DecodeGraphs:
             g.run_model(self.runner)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
-        # ... then recorded; the keys and values of this step are simply written twice.
+        eager_logits, eager_ids = g.logits, g.ids
+        # ... then recorded (nothing runs while recording).
         # Garbage is collected before, not during, the recording: an older engine's
         # graphs that happened to be destroyed in the middle of it would invalidate it.
         # A full collection (tens of milliseconds) is made before this engine's first
         # recording only: what was garbage before the engine's time is gone then, and
         # engines themselves are freed by their reference counts, without the collector.
         graph = torch.cuda.CUDAGraph()
-        n0 = ops.launch_count()
+        n0, b0 = ops.launch_count(), ops.bounded_wait_launches()
         if not self._collected:
             gc.collect()
             self._collected = True
@@ -206,6 +219,11 @@ class DecodeGraphs:
             if gc_was_on:
                 gc.enable()
         g.launches = ops.launch_count() - n0
+        ops.add_launches(-g.launches)  # (recorded, not run)
+        g.bounded_wait_launches = ops.bounded_wait_launches() - b0
         if self.pool is None:
             self.pool = graph.pool()
         g.graph = graph
+        # the eager run's results, in the buffers that the graph's replays will fill
+        g.logits.copy_(eager_logits)
+        g.ids.copy_(eager_ids)

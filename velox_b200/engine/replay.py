@@ -80,9 +80,7 @@ def main(argv: Optional[List[str]] = None) -> int:
         for rid in rec.get("end", []):
             if cache.has_request(rid):
                 cache.release(rid)
-        if runner.pending_error_check:
-            runner.pending_error_check = False
-            ops.check_device_errors()
+        runner.check_errors()
         sys.stdout.write("done %s\n" % step)
         sys.stdout.flush()
     return 0

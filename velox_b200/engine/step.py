@@ -27,7 +27,6 @@ class ModelRunner:
     def __init__(self, model, cache: CacheManager, device, vocab_size: int, cuda_graphs: bool = False):
         self.model, self.cache, self.device, self.vocab_size = model, cache, torch.device(device), int(vocab_size)
         self.steps = 0
-        self.pending_error_check = False
         self.graphs = None
         if cuda_graphs:
             from .graphs import DecodeGraphs
@@ -45,8 +44,10 @@ class ModelRunner:
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Runs one batch.  Returns float32 logits [wanted, vocab] on the device
         in the order of the entries and of their `want`, or None if nothing is
-        wanted.  Raises `OutOfPages` (and changes nothing) if the cache cannot
-        hold the new positions."""
+        wanted.  Raises `OutOfPages` if the cache cannot hold the new positions:
+        nothing is run or written then, and the pages that the step's earlier
+        entries had taken already stay with their requests, to be used by their
+        next step or given back with them."""
         logits, _ = self._step(entries, None, False)
         return logits
 
@@ -101,16 +102,23 @@ class ModelRunner:
         else:
             ctx = build_step_context(entries, self.cache, self.device, self.vocab_size)
             logits = self.run(ctx)
-            if ctx.max_new >= 32:
-                # large steps use kernels whose waits are bounded: a wait that ran out
-                # must not pass for a result
-                self.pending_error_check = True
             if sample and logits is not None:
                 t = torch.tensor([sampling[0], sampling[1], sampling[2]], dtype=torch.float32).to(self.device, non_blocking=True)
                 ids = ops.sample(logits, t[0], t[1], t[2]) if any(x > 0 for x in sampling[0]) else ops.sample(logits)
         native.check(cache._lib.vxh_cache_commit_many(cache._book, n, rids, counts))
         self.steps += 1
         return logits, (ids if sample else None)
+
+    @property
+    def pending_error_check(self) -> bool:
+        """True if a kernel whose waits are bounded has run since the error word was last
+        read: a wait that ran out must not pass for a result, so whoever hands out a
+        step's results calls `check_errors()` first.  Which kernels those are is the
+        kernel library's knowledge (`ops.note_bounded_wait`), not the step's."""
+        return ops.bounded_wait_pending()
+
+    def check_errors(self) -> None:
+        ops.check_pending_device_errors()
 
     def run(self, ctx: StepContext) -> Optional[torch.Tensor]:
         residual, delta = self.model.forward_hidden(ctx, self.cache)

@@ -22,8 +22,9 @@ class DecoderModel:
         for spec in plan.layers:
             block_cls = part_class("block", spec.block)
             self.blocks.append(block_cls(
-                build_part("mixer", spec.mixer), build_part("feed_forward", spec.feed_forward),
-                build_part("norm", spec.mixer_norm), build_part("norm", spec.feed_forward_norm)))
+                build_part("mixer", spec.mixer) if spec.mixer is not None else None,
+                build_part("feed_forward", spec.feed_forward) if spec.feed_forward is not None else None,
+                {name: build_part("norm", n) for name, n in spec.norms.items()}))
         self.final_norm = build_part("norm", plan.final_norm)
         self.head = build_part("head", plan.head)
         self.order = plan.running_order()
@@ -58,8 +59,8 @@ class DecoderModel:
     def cache_specs(self) -> list:
         """Per place of the running order: the mixer's cache need, or None for a
         place without a cache of its own (none at all, or another's)."""
-        return [None if self.plan.layers[i].cache_of is not None else self.blocks[i].mixer.cache_spec()
-                for i in self.order]
+        return [None if self.plan.layers[i].cache_of is not None or self.blocks[i].mixer is None
+                else self.blocks[i].mixer.cache_spec() for i in self.order]
 
     def cache_sources(self) -> list:
         """Per place of the running order: None, or the earlier place whose cache
@@ -80,7 +81,7 @@ class DecoderModel:
     def forward_hidden(self, ctx, cache):
         """Runs the step's tokens through every layer; returns (residual, delta),
         whose sum is the last layer's output [tokens, hidden]."""
-        residual = self.embedding.forward(ctx.token_ids)
+        residual = self.embedding.forward(ctx)
         delta = None
         for place, i in enumerate(self.order):
             residual, delta = self.blocks[i].forward(residual, delta, ctx, cache.layer(place))

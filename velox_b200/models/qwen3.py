@@ -25,9 +25,9 @@ def qwen3_plan(cfg: Qwen3Config) -> ModelPlan:
             feed_forward=PartSpec("gated_mlp", p + "mlp.", dict(
                 hidden_size=cfg.hidden_size, intermediate_size=cfg.intermediate_size,
                 activation=cfg.hidden_act)),
-            mixer_norm=PartSpec("rms_norm", p + "input_layernorm.", dict(size=cfg.hidden_size, eps=cfg.rms_norm_eps)),
-            feed_forward_norm=PartSpec("rms_norm", p + "post_attention_layernorm.",
-                                       dict(size=cfg.hidden_size, eps=cfg.rms_norm_eps)),
+            norms={"mixer": PartSpec("rms_norm", p + "input_layernorm.", dict(size=cfg.hidden_size, eps=cfg.rms_norm_eps)),
+                   "feed_forward": PartSpec("rms_norm", p + "post_attention_layernorm.",
+                                            dict(size=cfg.hidden_size, eps=cfg.rms_norm_eps))},
             block="pre_norm"))
     return ModelPlan(
         vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size,

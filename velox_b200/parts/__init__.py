@@ -1,5 +1,5 @@
 from .attention import PagedAttention
-from .base import (Block, FeedForward, FixedState, Mixer, Norm, PagedKV, Part, Position, Runtime, TensorSpec)
+from .base import (Block, Embedding, FeedForward, FixedState, Mixer, Norm, PagedKV, Part, Position, Runtime, TensorSpec)
 from .block import PreNormBlock
 from .embedding import OutputHead, TokenEmbedding
 from .linear import Linear, matmul

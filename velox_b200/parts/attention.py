@@ -130,16 +130,24 @@ class PagedAttention(Mixer):
             return ops.paged_decode_attention(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
                                               ctx.seq_of_token, ctx.positions, self.scale, self.window, H, Hk, D,
                                               ctx.n_seqs, ctx.max_kv)
-        if ctx.max_new >= TC_PREFILL_MIN_TOKENS and ops.prefill_attention_tc_supported(
-                qkv.dtype, D, cache.k_pool.shape[2], H // Hk):
-            # prompt portions on the tcgen05 tensor cores
-            return ops.paged_prefill_attention_tc(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
-                                                  ctx.cu_seqlens, ctx.kv_offsets, self.scale, self.window, H, Hk, D,
-                                                  ctx.n_seqs, ctx.max_new, qkv.shape[0])
-        if ops.prefill_attention_supported(qkv.dtype, D, cache.k_pool.shape[2]):
-            return ops.paged_prefill_attention(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
-                                               ctx.cu_seqlens, ctx.kv_offsets, self.scale, self.window, H, Hk, D,
-                                               ctx.n_seqs, ctx.max_new, qkv.shape[0])
+        page = cache.k_pool.shape[2]
+        use_tc = ctx.max_new >= TC_PREFILL_MIN_TOKENS and ops.prefill_attention_tc_supported(qkv.dtype, D, page, H // Hk)
+        if use_tc or ops.prefill_attention_supported(qkv.dtype, D, page):
+            prefill = ops.paged_prefill_attention_tc if use_tc else ops.paged_prefill_attention  # tcgen05 | mma.sync
+            out, seqs, n = None, None, ctx.n_seqs
+            if ctx.n_single and ops.decode_attention_supported(qkv.dtype, D, page, H // Hk):
+                # A mixed step: the requests that bring one token go to the decode kernel (a
+                # warp per 256 keys, every key read once), not into a query tile of their own;
+                # the kernels write disjoint rows.  A decoded token's result is then the same
+                # bits whether or not prompt portions ride in its step.
+                out = torch.empty((qkv.shape[0], H * D), dtype=qkv.dtype, device=qkv.device)
+                ops.paged_decode_attention(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
+                                           ctx.seq_of_token, ctx.positions, self.scale, self.window, H, Hk, D,
+                                           ctx.n_single, ctx.max_kv_single, token_rows=ctx.single_rows, out=out)
+                seqs, n = ctx.portion_seqs, ctx.n_portions
+            return prefill(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table, ctx.cu_seqlens,
+                           ctx.kv_offsets, self.scale, self.window, H, Hk, D, n, ctx.max_new, qkv.shape[0],
+                           seq_list=seqs, out=out)
         return ops.paged_attention_generic(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
                                            ctx.seq_of_token, ctx.positions, self.scale, self.window, H, Hk, D,
                                            qkv.shape[0])

@@ -8,15 +8,17 @@ part knows which model it is in.
                   bind(tensors, runtime) -> takes them (already on the device)
     Norm          forward(x) ; add_norm(residual, delta) -> normed
     Position      an encoding of positions that a mixer applies to q and k
-    Mixer         cache_spec() -> PagedKV | FixedState | None
+    Mixer         cache_spec() -> PagedKV | FixedState | a spec of a registered cache kind | None
                   forward(h, ctx, cache) -> y          h, y: [tokens, hidden]
     FeedForward   forward(h, ctx) -> y
     Block         forward(residual, delta, ctx, cache) -> (residual, delta)
+                  built from a mixer, a feed-forward (or None) and norms by name
+    Embedding     forward(ctx) -> float32 residual [tokens, hidden]
 
 `h` and `y` have the engine's element type; the residual stream is float32.
 `ctx` is the step's `StepContext` (engine/batch.py): positions, which request
 each token belongs to, block tables and slot mappings per cache group, state
-slots.  `cache` is the layer's `LayerCache` (cache/manager.py).
+slots.  `cache` is the layer's `LayerCache` (cache/kinds.py).
 """
 from __future__ import annotations
 
@@ -120,13 +122,37 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class Embedding(Part):
+    """What opens a step: the float32 residual stream [tokens, hidden] from the
+    step's context (its token ids, and whatever else of the step an input
+    encoding needs: positions, the request of each token)."""
+
+    def forward(self, ctx) -> torch.Tensor:
+        raise NotImplementedError
+
+
 class Block:
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm):
-        self.mixer, self.feed_forward = mixer, feed_forward
-        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+    """An arrangement of a layer's parts.  A subclass names the norms it wants in
+    `norm_names` and says whether it can do without a mixer or a feed-forward;
+    the layer's plan gives the norms by those names."""
+    norm_names: Tuple[str, ...] = ()
+    needs_mixer = True
+    needs_feed_forward = True
+
+    def __init__(self, mixer: Optional[Mixer], feed_forward: Optional[FeedForward], norms: Dict[str, Norm]):
+        kind = type(self).__name__
+        if sorted(norms) != sorted(self.norm_names):
+            raise ValueError("%s takes the norms %s; the layer's plan gives %s"
+                             % (kind, sorted(self.norm_names), sorted(norms)))
+        if mixer is None and self.needs_mixer:
+            raise ValueError("%s needs a mixer; the layer's plan gives none" % kind)
+        if feed_forward is None and self.needs_feed_forward:
+            raise ValueError("%s needs a feed-forward; the layer's plan gives none" % kind)
+        self.mixer, self.feed_forward, self.norms = mixer, feed_forward, dict(norms)
 
     def parts(self) -> List[Part]:
-        return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+        out: List[Part] = [self.norms[n] for n in self.norm_names]
+        return out + [p for p in (self.mixer, self.feed_forward) if p is not None]
 
     def forward(self, residual, delta, ctx, cache):
         raise NotImplementedError

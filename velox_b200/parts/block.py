@@ -14,9 +14,11 @@ from .base import Block
 
 
 class PreNormBlock(Block):
+    norm_names = ("mixer", "feed_forward")
+
     def forward(self, residual, delta, ctx, cache):
-        h = self.mixer_norm.add_norm(residual, delta)
+        h = self.norms["mixer"].add_norm(residual, delta)
         a = self.mixer.forward(h, ctx, cache)
-        h = self.feed_forward_norm.add_norm(residual, a)
+        h = self.norms["feed_forward"].add_norm(residual, a)
         f = self.feed_forward.forward(h, ctx)
         return residual, f

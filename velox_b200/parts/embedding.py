@@ -13,11 +13,11 @@ from typing import Dict, List, Optional
 import torch
 
 from ..csrc import ops
-from .base import Part, Runtime, TensorSpec
+from .base import Embedding, Part, Runtime, TensorSpec
 from .linear import matmul
 
 
-class TokenEmbedding(Part):
+class TokenEmbedding(Embedding):
     cuda_graph_safe = True  # reads nothing of a step but device tensors and sizes fixed per graph
 
     def __init__(self, prefix: str, vocab_size: int, hidden_size: int):
@@ -32,8 +32,8 @@ class TokenEmbedding(Part):
         super().bind(tensors, runtime)
         self.weight = tensors[self.prefix + "weight"]
 
-    def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
-        return ops.embedding(token_ids, self.weight)
+    def forward(self, ctx) -> torch.Tensor:
+        return ops.embedding(ctx.token_ids, self.weight)
 
 
 class OutputHead(Part):

@@ -27,10 +27,12 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    """A layer: a mixer, a feed-forward (or none), and its norms by the names that
+    its block arrangement gives them ("mixer" and "feed_forward" in the pre-norm
+    block; another arrangement may ask for one, four or none)."""
+    mixer: Optional[PartSpec]
+    feed_forward: Optional[PartSpec] = None
+    norms: Dict[str, PartSpec] = field(default_factory=dict)
     block: str = "pre_norm"
     cache_of: Optional[int] = None
 
