@@ -35,3 +35,11 @@ def model_folders(tmp_path_factory):
 
     root = tmp_path_factory.mktemp("models")
     return {name: write_tiny(name, str(root / name)) for name in TINY}
+
+
+def pytest_terminal_summary(terminalreporter):
+    import helpers
+    if helpers.WORST["rms"][0] > 0:
+        terminalreporter.write_line(
+            "bfloat16 against rounding alone: worst rms ratio %.3f (%s; bound %.2f), worst single value %.2f (%s; bound %.0f)"
+            % (helpers.WORST["rms"] + (helpers.RMS_SLACK,) + helpers.WORST["max"] + (helpers.MAX_SLACK,)))

@@ -51,9 +51,15 @@ TINY = {
 }
 
 FP32_ATOL = 1e-4
-# bfloat16: the bound the reference's kernel tests use, atol + rtol * |x|
-# (tests/metal_decode_parity.rs:131-136)
-BF16_ATOL, BF16_RTOL = 3e-2, 3e-2
+# bfloat16 logits are held to what rounding costs: the plain implementation with every
+# stored activation rounded to bfloat16 (`store=store_bfloat16`) lies at some root-mean-
+# square distance from the exact logits of a row; the engine's row may lie at most
+# RMS_SLACK times as far from them, and no single value further than MAX_SLACK times.
+# (An elementwise bound of 3e-2 + 3e-2 |x|, which the reference's kernel tests use,
+# tests/metal_decode_parity.rs:131-136, is a tenth of the spread of the tiny models'
+# logits and could hardly fail.)
+RMS_SLACK, MAX_SLACK = 1.25, 8.0
+WORST = {"rms": (0.0, ""), "max": (0.0, "")}   # the largest ratios seen in this session, for the summary
 
 
 def tiny_config(name):
@@ -70,30 +76,62 @@ def random_tokens(vocab, length, seed):
     return [int(t) for t in np.random.default_rng(seed).integers(0, vocab, size=length)]
 
 
-def assert_close(got, want, dtype, what=""):
+class Oracle:
+    """The plain implementation's logits of one whole sequence: `exact` [T, V] (float64)
+    and `cost` [T], the root-mean-square distance per row of the same computation with
+    every stored activation rounded to bfloat16.  `oracle[row]` is the exact row."""
+
+    def __init__(self, cfg, w, tokens, rows=None):
+        import plain_qwen3 as P
+        self.exact = P.forward_logits(cfg, w, tokens, rows=rows)
+        rounded = P.forward_logits(cfg, w, tokens, store=P.store_bfloat16, rows=rows)
+        self.cost = np.sqrt(np.mean(np.square(rounded - self.exact), axis=1))
+
+    def __getitem__(self, row):
+        return self.exact[row]
+
+
+def assert_close(got, want, dtype, what="", cost=None):
+    """float32: every value within FP32_ATOL.  bfloat16: `cost` [rows] is what rounding
+    costs at each row; see RMS_SLACK and MAX_SLACK."""
     got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
     assert got.shape == want.shape, "%s: shape %s vs %s" % (what, got.shape, want.shape)
     assert np.isfinite(got).all(), "%s: non-finite values in the engine's output" % what
     err = np.abs(got - want)
     if dtype == "float32":
-        bound = np.full_like(err, FP32_ATOL)
-    else:
-        bound = BF16_ATOL + BF16_RTOL * np.abs(want)
-    bad = err > bound
+        bad = err > FP32_ATOL
+        if bad.any():
+            idx = np.unravel_index(np.argmax(err), err.shape)
+            rows = np.unique(np.nonzero(bad)[0])
+            raise AssertionError("%s: %d values beyond %g (float32); worst at %s: got %.6g want %.6g; first wrong row %d, wrong rows %s"
+                                 % (what, int(bad.sum()), FP32_ATOL, idx, got[idx], want[idx], rows[0], rows[:20].tolist()))
+        return
+    assert cost is not None, "bfloat16 results are judged by what rounding costs: give `cost`"
+    cost = np.asarray(cost, np.float64)
+    rms = np.sqrt(np.mean(err * err, axis=1))
+    r_rms, r_max = rms / cost, err.max(axis=1) / cost
+    for key, r in (("rms", r_rms), ("max", r_max)):
+        if r.max() > WORST[key][0]:
+            WORST[key] = (float(r.max()), what)
+    bad = (r_rms > RMS_SLACK) | (r_max > MAX_SLACK)
     if bad.any():
-        idx = np.unravel_index(np.argmax(err - bound), err.shape)
-        rows = np.unique(np.nonzero(bad)[0])
-        raise AssertionError("%s: %d values beyond tolerance (%s); worst at %s: got %.6g want %.6g; first wrong row %d, wrong rows %s"
-                             % (what, int(bad.sum()), dtype, idx, got[idx], want[idx], rows[0], rows[:20].tolist()))
+        rows = np.nonzero(bad)[0]
+        k = rows[np.argmax(r_rms[rows])]
+        raise AssertionError("%s: %d rows beyond what rounding to bfloat16 costs; first wrong row %d, wrong rows %s; "
+                             "row %d: rms distance %.4g (rounding alone %.4g, ratio %.2f), largest single error %.4g (ratio %.1f)"
+                             % (what, len(rows), rows[0], rows[:20].tolist(), k, rms[k], cost[k], r_rms[k],
+                                err[k].max(), r_max[k]))
 
 
-def run_trace(model_dir, dtype, steps, max_tokens, out_dir, page_size=16, poison=True, timeout=600):
+def run_trace(model_dir, dtype, steps, max_tokens, out_dir, page_size=16, poison=True, timeout=600, max_requests=None):
     """Runs bin/trace_run as a user would: steps on stdin one at a time, waiting
     for `done <step>` after each.  Returns {step: float32 array [wanted, vocab]}."""
     cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype,
            "--out", out_dir, "--max-tokens", str(max_tokens), "--page-size", str(page_size)]
     if poison:
         cmd.append("--poison-cache")
+    if max_requests is not None:
+        cmd += ["--max-requests", str(max_requests)]
     proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, bufsize=1)
     try:
         for rec in steps:

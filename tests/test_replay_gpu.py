@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 
 import plain_qwen3 as P
-from helpers import TINY, assert_close, random_tokens, run_trace
+from helpers import TINY, Oracle, assert_close, random_tokens, run_trace
 
 pytestmark = pytest.mark.gpu
 
@@ -18,7 +18,7 @@ LENGTHS = {"tiny_a": [70, 45, 33, 90, 1, 2, 3, 64], "tiny_b": [81, 40, 57, 96, 1
 
 class Trace:
     def __init__(self):
-        self.steps, self.expect = [], {}
+        self.steps, self.expect, self.cost = [], {}, {}
 
     def add(self, entries, end=(), plain=None):
         """entries: [(request id, tokens, want, first position)]"""
@@ -28,6 +28,7 @@ class Trace:
         rows = [plain[i][pos + w_] for i, t, w, pos in entries for w_ in w]
         if rows:
             self.expect[n] = np.stack(rows)
+            self.cost[n] = np.array([plain[i].cost[pos + w_] for i, t, w, pos in entries for w_ in w])
 
 
 def cut(tokens, sizes):
@@ -99,7 +100,7 @@ def test_replay_every_way_of_cutting(model_folders, tmp_path, name, dtype):
     folder = model_folders[name]
     cfg, w = P.load_model_folder(folder)
     seqs = {"r%d" % n: random_tokens(cfg["vocab_size"], L, 100 + n) for n, L in enumerate(LENGTHS[name])}
-    plain = {i: P.forward_logits(cfg, w, t) for i, t in seqs.items()}
+    plain = {i: Oracle(cfg, w, t) for i, t in seqs.items()}
     tr = build_trace(seqs, plain)
     # the four longest live at once, each rounded up to 64: nothing to spare, so pages are used again
     pool = sum(-(-L // 64) * 64 for L in sorted(LENGTHS[name])[-4:])
@@ -107,7 +108,7 @@ def test_replay_every_way_of_cutting(model_folders, tmp_path, name, dtype):
     assert sorted(got) == sorted(tr.expect)
     for n in sorted(tr.expect):
         assert_close(got[n], tr.expect[n], dtype, "%s %s step %d %s" % (name, dtype, n, [
-            (e["id"], len(e["tokens"])) for e in tr.steps[n]["entries"]]))
+            (e["id"], len(e["tokens"])) for e in tr.steps[n]["entries"]]), cost=tr.cost[n])
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -116,7 +117,7 @@ def test_long_decoding(model_folders, tmp_path, dtype):
     folder = model_folders["tiny_c"]
     cfg, w = P.load_model_folder(folder)
     seqs = {"x": random_tokens(cfg["vocab_size"], 420, 7), "y": random_tokens(cfg["vocab_size"], 333, 8)}
-    plain = {i: P.forward_logits(cfg, w, t) for i, t in seqs.items()}
+    plain = {i: Oracle(cfg, w, t) for i, t in seqs.items()}
     tr = Trace()
     tr.add([("x", seqs["x"][:20], [19], 0), ("y", seqs["y"][:5], [4], 0)], plain=plain)
     at = {"x": 20, "y": 5}
@@ -131,7 +132,7 @@ def test_long_decoding(model_folders, tmp_path, dtype):
         tr.add(entries, end=end, plain=plain)
     got = run_trace(folder, dtype, tr.steps, 448 + 384, str(tmp_path / "out"), page_size=16)
     for n in sorted(tr.expect):
-        assert_close(got[n], tr.expect[n], dtype, "long decode step %d" % n)
+        assert_close(got[n], tr.expect[n], dtype, "long decode step %d" % n, cost=tr.cost[n])
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -141,7 +142,7 @@ def test_a_long_prompt_in_one_step_and_in_two(model_folders, tmp_path, dtype):
     folder = model_folders["tiny_d"]
     cfg, w = P.load_model_folder(folder)
     toks = random_tokens(cfg["vocab_size"], 1100, 9)
-    plain = {"whole": P.forward_logits(cfg, w, toks)}
+    plain = {"whole": Oracle(cfg, w, toks)}
     plain["cut"] = plain["whole"]
     want = list(range(0, 1100, 37)) + [1099]
     tr = Trace()
@@ -150,7 +151,7 @@ def test_a_long_prompt_in_one_step_and_in_two(model_folders, tmp_path, dtype):
     tr.add([("cut", toks[1030:], [w_ - 1030 for w_ in want if w_ >= 1030], 1030)], end=["cut"], plain=plain)
     got = run_trace(folder, dtype, tr.steps, 1152, str(tmp_path / "out"), page_size=16)
     for n in sorted(tr.expect):
-        assert_close(got[n], tr.expect[n], dtype, "long prompt step %d" % n)
+        assert_close(got[n], tr.expect[n], dtype, "long prompt step %d" % n, cost=tr.cost[n])
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -161,7 +162,7 @@ def test_a_context_of_4000_tokens(model_folders, tmp_path, dtype):
     folder = model_folders["tiny_d"]
     cfg, w = P.load_model_folder(folder)
     long_, short = random_tokens(cfg["vocab_size"], 4000, 41), random_tokens(cfg["vocab_size"], 60, 42)
-    plain = {"L": P.forward_logits(cfg, w, long_), "s": P.forward_logits(cfg, w, short)}
+    plain = {"L": Oracle(cfg, w, long_), "s": Oracle(cfg, w, short)}
     tr = Trace()
     tr.add([("L", long_[:2048], [0, 1000, 2047], 0)], plain=plain)
     tr.add([("L", long_[2048:3950], [0, 1, 951, 1901], 2048), ("s", short[:10], [9], 0)], plain=plain)
@@ -170,7 +171,7 @@ def test_a_context_of_4000_tokens(model_folders, tmp_path, dtype):
                end=["L", "s"] if k == 49 else [], plain=plain)
     got = run_trace(folder, dtype, tr.steps, 4032 + 64, str(tmp_path / "out"), page_size=16)
     for n in sorted(tr.expect):
-        assert_close(got[n], tr.expect[n], dtype, "context of 4000, step %d" % n)
+        assert_close(got[n], tr.expect[n], dtype, "context of 4000, step %d" % n, cost=tr.cost[n])
 
 
 ODD = {
@@ -204,13 +205,13 @@ def test_sizes_that_no_fast_kernel_takes(tmp_path, name, dtype):
                                 dtype="bfloat16")
     cfg, w = P.load_model_folder(folder)
     seqs = {"r%d" % n: random_tokens(cfg["vocab_size"], L, 300 + n) for n, L in enumerate(spec["lens"])}
-    plain = {i: P.forward_logits(cfg, w, t) for i, t in seqs.items()}
+    plain = {i: Oracle(cfg, w, t) for i, t in seqs.items()}
     tr = build_trace(seqs, plain)
     pool = sum(-(-L // 64) * 64 for L in sorted(spec["lens"])[-4:])
     got = run_trace(folder, dtype, tr.steps, pool, str(tmp_path / "out"), page_size=spec["page_size"])
     assert sorted(got) == sorted(tr.expect)
     for n in sorted(tr.expect):
-        assert_close(got[n], tr.expect[n], dtype, "%s %s step %d" % (name, dtype, n))
+        assert_close(got[n], tr.expect[n], dtype, "%s %s step %d" % (name, dtype, n), cost=tr.cost[n])
 
 
 @pytest.mark.parametrize("seed", [3, 11, 26])
@@ -225,12 +226,12 @@ def test_random_traces(model_folders, tmp_path, seed):
     cfg, w = P.load_model_folder(model_folders[name])
     lens = [rng.choice([1, 2, 3, 17, 40, 64, 65, 100, 130, 257, 300]) for _ in range(rng.randint(3, 8))]
     seqs = {"q%d" % i: random_tokens(cfg["vocab_size"], L, 7000 * seed + i) for i, L in enumerate(lens)}
-    plain = {i: P.forward_logits(cfg, w, t) for i, t in seqs.items()}
-    waiting, live, steps, expect = list(seqs), {}, [], {}
+    plain = {i: Oracle(cfg, w, t) for i, t in seqs.items()}
+    waiting, live, steps, expect, costs = list(seqs), {}, [], {}, {}
     while waiting or live:
         while waiting and len(live) < 4 and (not live or rng.random() < 0.7):
             live[waiting.pop(0)] = 0
-        entries, end, rows = [], [], []
+        entries, end, rows, row_costs = [], [], [], []
         order = list(live)
         rng.shuffle(order)
         for i in order:
@@ -240,6 +241,7 @@ def test_random_traces(model_folders, tmp_path, seed):
             want = sorted(rng.sample(range(k), rng.choice([0, 1, min(k, 3), k])))
             entries.append({"id": i, "tokens": seqs[i][live[i]:live[i] + k], "want": want})
             rows += [plain[i][live[i] + w_] for w_ in want]
+            row_costs += [plain[i].cost[live[i] + w_] for w_ in want]
             live[i] += k
             if live[i] == len(seqs[i]):
                 end.append(i)
@@ -247,9 +249,49 @@ def test_random_traces(model_folders, tmp_path, seed):
         steps.append({"step": len(steps), "entries": entries, "end": end})
         if rows:
             expect[len(steps) - 1] = np.stack(rows)
+            costs[len(steps) - 1] = np.array(row_costs)
     pool = sum(sorted(-(-L // 64) * 64 for L in lens)[-4:])
     for dtype in ("float32", "bfloat16"):
         got = run_trace(model_folders[name], dtype, steps, pool, str(tmp_path / dtype), page_size=TINY[name]["page_size"])
         assert sorted(got) == sorted(expect)
         for n in sorted(expect):
-            assert_close(got[n], expect[n], dtype, "%s %s seed %d step %d" % (name, dtype, seed, n))
+            assert_close(got[n], expect[n], dtype, "%s %s seed %d step %d" % (name, dtype, seed, n), cost=costs[n])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_steps_of_twelve_requests_in_a_padded_captured_step(model_folders, tmp_path, dtype):
+    """More than eight requests decode together: the step is padded to a bucket of 16 rows
+    (rows that read page 0 and write nothing) and runs as a captured graph.  The logits
+    of every real row are compared; requests end one after the other, so the batch
+    shrinks through 12, 11, 10 and 9 rows of the same bucket and then below it.  (The
+    reference's mixed-batch test holds 13 sequences in one batch:
+    tests/metal_batched_kernels_parity.rs:297-359.)"""
+    folder = model_folders["tiny_d"]
+    cfg, w = P.load_model_folder(folder)
+    lens = [300, 20, 530, 41, 17, 260, 33, 90, 700, 64, 129, 48]   # some need two and three pieces of 256 keys
+    new = [14, 9, 12, 10, 16, 8, 11, 13, 15, 7, 12, 9]
+    seqs = {"s%d" % i: random_tokens(cfg["vocab_size"], L + n, 500 + i) for i, (L, n) in enumerate(zip(lens, new))}
+    plain = {i: Oracle(cfg, w, t) for i, t in seqs.items()}
+    tr = Trace()
+    ids = list(seqs)
+    for at in range(0, 12, 3):   # the prompts, three requests a step
+        tr.add([(i, seqs[i][:lens[k]], [lens[k] - 1], 0) for k, i in enumerate(ids) if at <= k < at + 3], plain=plain)
+    pos = {i: lens[k] for k, i in enumerate(ids)}
+    sizes = []
+    while pos:
+        entries, end = [], []
+        for i in list(pos):
+            entries.append((i, [seqs[i][pos[i]]], [0], pos[i]))
+            pos[i] += 1
+            if pos[i] == len(seqs[i]):
+                end.append(i)
+                del pos[i]
+        sizes.append(len(entries))
+        tr.add(entries, end=end, plain=plain)
+    assert sizes[0] == 12 and {9, 10, 11, 12} <= set(sizes) and min(sizes) == 1
+    pool = sum(-(-len(t) // 64) * 64 for t in seqs.values())
+    got = run_trace(folder, dtype, tr.steps, pool, str(tmp_path / "out"), page_size=16, max_requests=16)
+    assert sorted(got) == sorted(tr.expect)
+    for n in sorted(tr.expect):
+        assert_close(got[n], tr.expect[n], dtype, "twelve live, step %d (%d rows)" % (n, len(tr.steps[n]["entries"])),
+                     cost=tr.cost[n])
