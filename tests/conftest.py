@@ -39,7 +39,9 @@ def model_folders(tmp_path_factory):
 
 def pytest_terminal_summary(terminalreporter):
     import helpers
-    if helpers.WORST["rms"][0] > 0:
-        terminalreporter.write_line(
-            "bfloat16 against rounding alone: worst rms ratio %.3f (%s; bound %.2f), worst single value %.2f (%s; bound %.0f)"
-            % (helpers.WORST["rms"] + (helpers.RMS_SLACK,) + helpers.WORST["max"] + (helpers.MAX_SLACK,)))
+    if helpers.REPORT:
+        terminalreporter.write_line("bfloat16 against what rounding alone costs (pooled rms ratio, bound %.2f; worst row, "
+                                    "bound %.1f; worst single value, bound %.0f):"
+                                    % (helpers.RMS_SLACK, helpers.ROW_SLACK, helpers.MAX_SLACK))
+        for what, rows, ratio, row, value in helpers.REPORT:
+            terminalreporter.write_line("  %-60s %6d rows  %.3f  %.2f  %.2f" % (what, rows, ratio, row, value))

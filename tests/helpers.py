@@ -51,15 +51,25 @@ TINY = {
 }
 
 FP32_ATOL = 1e-4
-# bfloat16 logits are held to what rounding costs: the plain implementation with every
+# bfloat16 logits are held to what rounding costs.  The plain implementation with every
 # stored activation rounded to bfloat16 (`store=store_bfloat16`) lies at some root-mean-
-# square distance from the exact logits of a row; the engine's row may lie at most
-# RMS_SLACK times as far from them, and no single value further than MAX_SLACK times.
-# (An elementwise bound of 3e-2 + 3e-2 |x|, which the reference's kernel tests use,
-# tests/metal_decode_parity.rs:131-136, is a tenth of the spread of the tiny models'
-# logits and could hardly fail.)
-RMS_SLACK, MAX_SLACK = 1.25, 8.0
-WORST = {"rms": (0.0, ""), "max": (0.0, "")}   # the largest ratios seen in this session, for the summary
+# square distance from the exact logits of a row: the row's `cost`.  The engine rounds at
+# the same places but not to the same bits, so its distance from the exact logits is
+# another draw of the same random quantity.  At a width of 4,096 that quantity hardly
+# varies from draw to draw (tests/test_real_sizes_gpu.py holds every row to 1.25 times its
+# cost); at the tiny models' widths of 50 to 256 a single row's distance scatters by tens of
+# per cent around its mean.  So three things are asked (`RoundingJudge`):
+#   pooled over all rows of a test, the engine's rms distance is at most RMS_SLACK times
+#     the pooled cost (the scatter averages out over hundreds of rows; a part that rounds
+#     once more than it has to shows here: 1.4 to 1.7 times);
+#   no row's rms distance exceeds ROW_SLACK times its cost (or the pooled cost, if larger);
+#   no single value is further off than MAX_SLACK times that.
+# A wrong or missing key, a stale page or a wrong position moves logits by many times what
+# rounding does.  (An elementwise bound of 3e-2 + 3e-2 |x|, which the reference's kernel
+# tests use, tests/metal_decode_parity.rs:131-136, is a tenth of the spread of the tiny
+# models' logits and could hardly fail.)
+RMS_SLACK, ROW_SLACK, MAX_SLACK = 1.25, 3.0, 8.0
+REPORT = []   # (what, rows, pooled ratio, largest row ratio, largest single-value ratio) per judged test
 
 
 def tiny_config(name):
@@ -91,36 +101,70 @@ class Oracle:
         return self.exact[row]
 
 
-def assert_close(got, want, dtype, what="", cost=None):
-    """float32: every value within FP32_ATOL.  bfloat16: `cost` [rows] is what rounding
-    costs at each row; see RMS_SLACK and MAX_SLACK."""
+class RoundingJudge:
+    """Judges the bfloat16 results of one test against what rounding costs (see above).
+    `typical`: the pooled cost of the test's oracles, known before anything runs."""
+
+    def __init__(self, what, typical=0.0):
+        self.what, self.typical = what, float(typical)
+        self.err2 = self.cost2 = 0.0
+        self.rows, self.worst_row, self.worst_value = 0, 0.0, 0.0
+
+    @staticmethod
+    def of(oracles, what):
+        costs = np.concatenate([np.ravel(o.cost) for o in oracles])
+        return RoundingJudge(what, np.sqrt(np.mean(costs * costs)))
+
+    def check(self, got, want, cost, what=""):
+        got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+        cost = np.asarray(cost, np.float64)
+        assert got.shape == want.shape, "%s: shape %s vs %s" % (what, got.shape, want.shape)
+        assert np.isfinite(got).all(), "%s: non-finite values in the engine's output" % what
+        err = np.abs(got - want)
+        rms = np.sqrt(np.mean(err * err, axis=1))
+        scale = np.maximum(cost, self.typical)
+        r_row, r_val = rms / scale, err.max(axis=1) / scale
+        self.err2 += float(np.sum(rms * rms))
+        self.cost2 += float(np.sum(cost * cost))
+        self.rows += len(rms)
+        self.worst_row, self.worst_value = max(self.worst_row, r_row.max()), max(self.worst_value, r_val.max())
+        bad = (r_row > ROW_SLACK) | (r_val > MAX_SLACK)
+        if bad.any():
+            rows = np.nonzero(bad)[0]
+            k = rows[np.argmax(r_row[rows])]
+            raise AssertionError(
+                "%s: %d rows beyond what rounding to bfloat16 costs; first wrong row %d, wrong rows %s; row %d: rms "
+                "distance %.4g (rounding alone %.4g, pooled %.4g: ratio %.2f), largest single error %.4g (ratio %.1f)"
+                % (what, len(rows), rows[0], rows[:20].tolist(), k, rms[k], cost[k], self.typical, r_row[k],
+                   err[k].max(), r_val[k]))
+
+    def finish(self):
+        """The pooled measure, once every step of the test has been checked."""
+        assert self.rows > 0, "%s: nothing was judged" % self.what
+        ratio = (self.err2 / self.cost2) ** 0.5
+        REPORT.append((self.what, self.rows, ratio, self.worst_row, self.worst_value))
+        assert ratio <= RMS_SLACK, (
+            "%s: over %d rows the engine lies %.3f times as far from the exact logits as rounding to bfloat16 "
+            "alone does (at most %.2f)" % (self.what, self.rows, ratio, RMS_SLACK))
+
+
+def assert_close(got, want, dtype, what="", cost=None, judge=None):
+    """float32: every value within FP32_ATOL.  bfloat16: by `judge` (a RoundingJudge,
+    whose `finish()` the test calls at its end) with `cost` [rows]."""
+    if dtype != "float32":
+        assert cost is not None and judge is not None, "bfloat16 results are judged by what rounding costs"
+        judge.check(got, want, cost, what)
+        return
     got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
     assert got.shape == want.shape, "%s: shape %s vs %s" % (what, got.shape, want.shape)
     assert np.isfinite(got).all(), "%s: non-finite values in the engine's output" % what
     err = np.abs(got - want)
-    if dtype == "float32":
-        bad = err > FP32_ATOL
-        if bad.any():
-            idx = np.unravel_index(np.argmax(err), err.shape)
-            rows = np.unique(np.nonzero(bad)[0])
-            raise AssertionError("%s: %d values beyond %g (float32); worst at %s: got %.6g want %.6g; first wrong row %d, wrong rows %s"
-                                 % (what, int(bad.sum()), FP32_ATOL, idx, got[idx], want[idx], rows[0], rows[:20].tolist()))
-        return
-    assert cost is not None, "bfloat16 results are judged by what rounding costs: give `cost`"
-    cost = np.asarray(cost, np.float64)
-    rms = np.sqrt(np.mean(err * err, axis=1))
-    r_rms, r_max = rms / cost, err.max(axis=1) / cost
-    for key, r in (("rms", r_rms), ("max", r_max)):
-        if r.max() > WORST[key][0]:
-            WORST[key] = (float(r.max()), what)
-    bad = (r_rms > RMS_SLACK) | (r_max > MAX_SLACK)
+    bad = err > FP32_ATOL
     if bad.any():
-        rows = np.nonzero(bad)[0]
-        k = rows[np.argmax(r_rms[rows])]
-        raise AssertionError("%s: %d rows beyond what rounding to bfloat16 costs; first wrong row %d, wrong rows %s; "
-                             "row %d: rms distance %.4g (rounding alone %.4g, ratio %.2f), largest single error %.4g (ratio %.1f)"
-                             % (what, len(rows), rows[0], rows[:20].tolist(), k, rms[k], cost[k], r_rms[k],
-                                err[k].max(), r_max[k]))
+        idx = np.unravel_index(np.argmax(err), err.shape)
+        rows = np.unique(np.nonzero(bad)[0])
+        raise AssertionError("%s: %d values beyond %g (float32); worst at %s: got %.6g want %.6g; first wrong row %d, wrong rows %s"
+                             % (what, int(bad.sum()), FP32_ATOL, idx, got[idx], want[idx], rows[0], rows[:20].tolist()))
 
 
 def run_trace(model_dir, dtype, steps, max_tokens, out_dir, page_size=16, poison=True, timeout=600, max_requests=None):

@@ -258,7 +258,6 @@ def test_decode_steps_of_more_than_eight_requests(model_folders, dtype, count):
     padded = -(-count // 8) * 8
     assert padded in buckets and all(b <= 8 or b % 8 == 0 for b in buckets), buckets
     assert len([b for b in buckets if b > 8]) >= max(1, (padded // 8 - 1) // 2), buckets   # and buckets on the way down
-    assert len({kv for _, kv in e.runner.graphs.graphs}) >= 2              # and more than one range of keys
     e.cache.check()
     assert e.cache.free_pages() == [pages, pages] and e.stats()["preemptions"] == 0
 

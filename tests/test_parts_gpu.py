@@ -7,7 +7,7 @@ import pytest
 import torch
 
 import plain_qwen3 as P
-from helpers import assert_close
+from helpers import RoundingJudge
 
 pytestmark = pytest.mark.gpu
 DEV = torch.device("cuda:0")
@@ -40,7 +40,9 @@ def close(got, want, dtype, what="", rounded=None):
             "%s: max err %.3g" % (what, err.max())
         return
     cost = np.sqrt(np.mean(np.square(rounded - want), axis=1))
-    assert_close(got, want, "bfloat16", what, cost=cost)
+    judge = RoundingJudge("part: " + what, np.sqrt(np.mean(cost * cost)))
+    judge.check(got, want, cost, what)
+    judge.finish()
 
 
 def act(shape, dtype, seed):

@@ -84,3 +84,75 @@ def test_whole_and_cut_beside_another_request(folder_and_plain, tmp_path, dtype)
             assert_close(got[n], expect[n], dtype, what)
         else:
             assert_within_rounding(got[n], expect[n], costs[n], what)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_portions_down_to_two_tokens_and_four_live_requests_in_reused_pages(folder_and_plain, tmp_path, dtype):
+    """At the real widths: one request in portions of changing size down to two tokens (and
+    one), then four requests live at once, portions of some beside decoded tokens of others, in
+    a pool that holds exactly the four: the fifth request starts in the pages the third gave
+    back.  The longest request decodes past 600 keys, so its decode attention joins three
+    pieces of 256 keys at 32 query and 8 key/value heads."""
+    folder = folder_and_plain[0]
+    cfg, w = P.load_model_folder(folder, dtype="float32")
+    vocab = cfg["vocab_size"]
+    seqs = {"a": random_tokens(vocab, 640, 31), "b": random_tokens(vocab, 150, 32), "c": random_tokens(vocab, 90, 33),
+            "d": random_tokens(vocab, 200, 34), "e": random_tokens(vocab, 70, 35)}
+    steps, wanted = [], []      # wanted: per step [(sequence, position)] in the order of the logits' rows
+
+    def add(entries, end=()):
+        """entries: [(id, sequence, first position, count, wanted places)]"""
+        steps.append({"step": len(steps), "end": list(end), "entries": [
+            {"id": i, "tokens": seqs[s][at:at + k], "want": list(wp)} for i, s, at, k, wp in entries]})
+        wanted.append([(s, at + p) for i, s, at, k, wp in entries for p in wp])
+
+    # portions of changing size, down to two tokens (and one)
+    at = 0
+    sizes = [7, 5, 3, 2, 2, 11, 2, 1, 16]
+    n = 0
+    while at < 150:
+        k = min(sizes[n % len(sizes)], 150 - at)
+        add([("b1", "b", at, k, [k - 1])], end=["b1"] if at + k == 150 else [])
+        at, n = at + k, n + 1
+    # four live: a's prompt in three portions beside the others, then everybody token by token
+    add([("a", "a", 0, 256, [255]), ("b", "b", 0, 100, []), ("c", "c", 0, 60, [59])])
+    add([("a", "a", 256, 300, [0, 299]), ("b", "b", 100, 2, [1]), ("c", "c", 60, 1, [0]), ("d", "d", 0, 180, [179])])
+    add([("a", "a", 556, 60, [59]), ("b", "b", 102, 1, [0]), ("c", "c", 61, 1, [0]), ("d", "d", 180, 2, [0, 1])])
+    pos = {"a": 616, "b": 103, "c": 62, "d": 182}
+    live = {"a": "a", "b": "b", "c": "c", "d": "d"}
+    while live:
+        entries, end = [], []
+        for i in list(live):
+            if i == "e" and pos[i] == 0:
+                entries.append((i, "e", 0, 40, [39]))      # the newcomer's prompt beside the others' decoded tokens
+                pos[i] = 40
+                continue
+            entries.append((i, live[i], pos[i], 1, [0]))
+            pos[i] += 1
+            if pos[i] == min(len(seqs[live[i]]), {"a": 640, "b": 130, "c": 80, "d": 206, "e": 56}[i]):
+                end.append(i)
+        add(entries, end=end)
+        for i in end:
+            del live[i]
+            if i == "c":
+                live["e"], pos["e"] = "e", 0
+    rows = {s: sorted({p for step in wanted for s_, p in step if s_ == s}) for s in seqs}
+    exact = {s: P.forward_logits(cfg, w, seqs[s][:rows[s][-1] + 1], dtype=np.float32, rows=rows[s]) for s in seqs}
+    if dtype == "bfloat16":
+        rounded = {s: P.forward_logits(cfg, w, seqs[s][:rows[s][-1] + 1], dtype=np.float32, store=P.store_bfloat16,
+                                       rows=rows[s]) for s in seqs}
+        cost = {s: np.sqrt(np.mean(np.square(rounded[s] - exact[s], dtype=np.float64), axis=1)) for s in seqs}
+        del rounded
+    del w
+    # the pool holds a (640), b (192), d (256) and c or e (128): nothing to spare
+    got = run_trace(folder, dtype, steps, 640 + 192 + 256 + 128, str(tmp_path / "out"), page_size=16, timeout=1200)
+    assert sorted(got) == [n for n, ws in enumerate(wanted) if ws]
+    for n, ws in enumerate(wanted):
+        if not ws:
+            continue
+        what = "step %d %s" % (n, [(e["id"], len(e["tokens"])) for e in steps[n]["entries"]])
+        want = np.stack([exact[s][rows[s].index(p)] for s, p in ws])
+        if dtype == "float32":
+            assert_close(got[n], want, dtype, what)
+        else:
+            assert_within_rounding(got[n], want, np.array([cost[s][rows[s].index(p)] for s, p in ws]), what)

@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 
 import plain_qwen3 as P
-from helpers import TINY, Oracle, assert_close, random_tokens, run_trace
+from helpers import TINY, Oracle, RoundingJudge, assert_close, random_tokens, run_trace
 
 pytestmark = pytest.mark.gpu
 
@@ -106,9 +106,12 @@ def test_replay_every_way_of_cutting(model_folders, tmp_path, name, dtype):
     pool = sum(-(-L // 64) * 64 for L in sorted(LENGTHS[name])[-4:])
     got = run_trace(folder, dtype, tr.steps, pool, str(tmp_path / "out"), page_size=TINY[name]["page_size"])
     assert sorted(got) == sorted(tr.expect)
+    judge = RoundingJudge.of(plain.values(), "replay %s" % name)
     for n in sorted(tr.expect):
         assert_close(got[n], tr.expect[n], dtype, "%s %s step %d %s" % (name, dtype, n, [
-            (e["id"], len(e["tokens"])) for e in tr.steps[n]["entries"]]), cost=tr.cost[n])
+            (e["id"], len(e["tokens"])) for e in tr.steps[n]["entries"]]), cost=tr.cost[n], judge=judge)
+    if dtype == "bfloat16":
+        judge.finish()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -131,8 +134,11 @@ def test_long_decoding(model_folders, tmp_path, dtype):
                 del at[i]
         tr.add(entries, end=end, plain=plain)
     got = run_trace(folder, dtype, tr.steps, 448 + 384, str(tmp_path / "out"), page_size=16)
+    judge = RoundingJudge.of(plain.values(), "long decoding")
     for n in sorted(tr.expect):
-        assert_close(got[n], tr.expect[n], dtype, "long decode step %d" % n, cost=tr.cost[n])
+        assert_close(got[n], tr.expect[n], dtype, "long decode step %d" % n, cost=tr.cost[n], judge=judge)
+    if dtype == "bfloat16":
+        judge.finish()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -150,8 +156,11 @@ def test_a_long_prompt_in_one_step_and_in_two(model_folders, tmp_path, dtype):
     tr.add([("cut", toks[:1030], [w_ for w_ in want if w_ < 1030], 0)], plain=plain)
     tr.add([("cut", toks[1030:], [w_ - 1030 for w_ in want if w_ >= 1030], 1030)], end=["cut"], plain=plain)
     got = run_trace(folder, dtype, tr.steps, 1152, str(tmp_path / "out"), page_size=16)
+    judge = RoundingJudge.of(plain.values(), "a long prompt")
     for n in sorted(tr.expect):
-        assert_close(got[n], tr.expect[n], dtype, "long prompt step %d" % n, cost=tr.cost[n])
+        assert_close(got[n], tr.expect[n], dtype, "long prompt step %d" % n, cost=tr.cost[n], judge=judge)
+    if dtype == "bfloat16":
+        judge.finish()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -170,8 +179,11 @@ def test_a_context_of_4000_tokens(model_folders, tmp_path, dtype):
         tr.add([("L", [long_[3950 + k]], [0], 3950 + k), ("s", [short[10 + k]], [0], 10 + k)],
                end=["L", "s"] if k == 49 else [], plain=plain)
     got = run_trace(folder, dtype, tr.steps, 4032 + 64, str(tmp_path / "out"), page_size=16)
+    judge = RoundingJudge.of(plain.values(), "a context of 4000")
     for n in sorted(tr.expect):
-        assert_close(got[n], tr.expect[n], dtype, "context of 4000, step %d" % n, cost=tr.cost[n])
+        assert_close(got[n], tr.expect[n], dtype, "context of 4000, step %d" % n, cost=tr.cost[n], judge=judge)
+    if dtype == "bfloat16":
+        judge.finish()
 
 
 ODD = {
@@ -210,8 +222,11 @@ def test_sizes_that_no_fast_kernel_takes(tmp_path, name, dtype):
     pool = sum(-(-L // 64) * 64 for L in sorted(spec["lens"])[-4:])
     got = run_trace(folder, dtype, tr.steps, pool, str(tmp_path / "out"), page_size=spec["page_size"])
     assert sorted(got) == sorted(tr.expect)
+    judge = RoundingJudge.of(plain.values(), "sizes no fast kernel takes, %s" % name)
     for n in sorted(tr.expect):
-        assert_close(got[n], tr.expect[n], dtype, "%s %s step %d" % (name, dtype, n), cost=tr.cost[n])
+        assert_close(got[n], tr.expect[n], dtype, "%s %s step %d" % (name, dtype, n), cost=tr.cost[n], judge=judge)
+    if dtype == "bfloat16":
+        judge.finish()
 
 
 @pytest.mark.parametrize("seed", [3, 11, 26])
@@ -254,8 +269,12 @@ def test_random_traces(model_folders, tmp_path, seed):
     for dtype in ("float32", "bfloat16"):
         got = run_trace(model_folders[name], dtype, steps, pool, str(tmp_path / dtype), page_size=TINY[name]["page_size"])
         assert sorted(got) == sorted(expect)
+        judge = RoundingJudge.of(plain.values(), "random trace %d (%s)" % (seed, name))
         for n in sorted(expect):
-            assert_close(got[n], expect[n], dtype, "%s %s seed %d step %d" % (name, dtype, seed, n), cost=costs[n])
+            assert_close(got[n], expect[n], dtype, "%s %s seed %d step %d" % (name, dtype, seed, n), cost=costs[n],
+                         judge=judge)
+        if dtype == "bfloat16":
+            judge.finish()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -292,6 +311,9 @@ def test_decode_steps_of_twelve_requests_in_a_padded_captured_step(model_folders
     pool = sum(-(-len(t) // 64) * 64 for t in seqs.values())
     got = run_trace(folder, dtype, tr.steps, pool, str(tmp_path / "out"), page_size=16, max_requests=16)
     assert sorted(got) == sorted(tr.expect)
+    judge = RoundingJudge.of(plain.values(), "twelve live requests")
     for n in sorted(tr.expect):
         assert_close(got[n], tr.expect[n], dtype, "twelve live, step %d (%d rows)" % (n, len(tr.steps[n]["entries"])),
-                     cost=tr.cost[n])
+                     cost=tr.cost[n], judge=judge)
+    if dtype == "bfloat16":
+        judge.finish()

@@ -254,8 +254,8 @@ extern "C" int vx_rmsnorm(const void* x, const float* weight, void* out, int row
 // and up i sit in a row of 2 * inner values: with block == 0 the gate half is
 // followed by the up half; with block > 0 the row is made of tiles of 2 * block
 // values, `block` gates followed by their `block` ups.
-template <typename T>
-__global__ void gated_act_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long total,
+template <typename T, typename TO>
+__global__ void gated_act_kernel(const T* __restrict__ gate_up, TO* __restrict__ out, long long total,
                                  int inner, int act, int block) {
     pdl_wait();
     pdl_trigger();
@@ -266,15 +266,15 @@ __global__ void gated_act_kernel(const T* __restrict__ gate_up, T* __restrict__ 
         const T* row = gate_up + t * 2 * inner;
         const int gi = block > 0 ? (i / block) * 2 * block + i % block : i;
         const int ui = block > 0 ? gi + block : inner + i;
-        out[idx] = from_f32<T>(activation(to_f32(row[gi]), act) * to_f32(row[ui]));
+        out[idx] = from_f32<TO>(activation(to_f32(row[gi]), act) * to_f32(row[ui]));
     }
 }
 
 // Eight features per thread: with tiles of 8 (block == 8) the gates of a tile are
 // 16 contiguous bytes (bf16) followed by its ups; with halves (block == 0) eight
 // gates and eight ups are contiguous each.  inner a multiple of 8, 16-byte aligned.
-template <typename T>
-__global__ void gated_act_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long chunks,
+template <typename T, typename TO>
+__global__ void gated_act_vec_kernel(const T* __restrict__ gate_up, TO* __restrict__ out, long long chunks,
                                      int inner, int act, int block) {
     pdl_wait();
     pdl_trigger();
@@ -298,8 +298,24 @@ __global__ void gated_act_vec_kernel(const T* __restrict__ gate_up, T* __restric
     }
 }
 
+template <typename T, typename TO>
+static int launch_gated_act(const void* gate_up, void* out, bool vec, long long blocks, int threads, long long items,
+                            long long total, int inner, int act, int block, cudaStream_t stream) {
+    if (vec)
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (gated_act_vec_kernel<T, TO>), (int)blocks, threads, 0, stream, (const T*)gate_up,
+                    (TO*)out, items, inner, act, block);
+    else
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (gated_act_kernel<T, TO>), (int)blocks, threads, 0, stream, (const T*)gate_up,
+                    (TO*)out, total, inner, act, block);
+    VX_LAUNCH_CHECK();
+    return VX_OK;
+}
+
+// act(gate) * up of rows [gates | ups] (block == 0) or tiles of `block` gates and their
+// ups.  The input may be float32 with a bfloat16 result: a library product then hands
+// over its float32 sums and nothing is rounded before the activation.
 extern "C" int vx_gated_act(const void* gate_up, void* out, int rows, int inner, int act, int block, int dtype,
-                            cudaStream_t stream) {
+                            int out_dtype, cudaStream_t stream) {
     if (rows <= 0) return VX_OK;
     if (inner <= 0 || act < 0 || act > 3 || block < 0 || (block > 0 && inner % block)) return VX_ERR_SHAPE;
     const long long total = (long long)rows * inner;
@@ -309,21 +325,37 @@ extern "C" int vx_gated_act(const void* gate_up, void* out, int rows, int inner,
     const long long items = vec ? total / 8 : total;
     long long blocks = (items + threads - 1) / threads;
     if (blocks > 148 * 32) blocks = 148 * 32;
-    if (dtype == VX_F32) {
-        if (vec)
-            VX_LAUNCH_K(VX_K_ELEMENTWISE, (gated_act_vec_kernel<float>), (int)blocks, threads, 0, stream,
-                        (const float*)gate_up, (float*)out, items, inner, act, block);
-        else
-            VX_LAUNCH_K(VX_K_ELEMENTWISE, (gated_act_kernel<float>), (int)blocks, threads, 0, stream,
-                        (const float*)gate_up, (float*)out, total, inner, act, block);
-    } else if (dtype == VX_BF16) {
-        if (vec)
-            VX_LAUNCH_K(VX_K_ELEMENTWISE, (gated_act_vec_kernel<bf16>), (int)blocks, threads, 0, stream,
-                        (const bf16*)gate_up, (bf16*)out, items, inner, act, block);
-        else
-            VX_LAUNCH_K(VX_K_ELEMENTWISE, (gated_act_kernel<bf16>), (int)blocks, threads, 0, stream,
-                        (const bf16*)gate_up, (bf16*)out, total, inner, act, block);
-    }
+    if (dtype == VX_F32 && out_dtype == VX_F32)
+        return launch_gated_act<float, float>(gate_up, out, vec, blocks, threads, items, total, inner, act, block, stream);
+    if (dtype == VX_BF16 && out_dtype == VX_BF16)
+        return launch_gated_act<bf16, bf16>(gate_up, out, vec, blocks, threads, items, total, inner, act, block, stream);
+    if (dtype == VX_F32 && out_dtype == VX_BF16)
+        return launch_gated_act<float, bf16>(gate_up, out, vec, blocks, threads, items, total, inner, act, block, stream);
+    return VX_ERR_DTYPE;
+}
+
+// out[m, n] = in[m, n] + bias[n], float32 in, float32 or bfloat16 out: the bias of a
+// library product is added to its float32 sums, and the result rounded once.
+template <typename TO>
+__global__ void add_bias_kernel(const float* __restrict__ in, const float* __restrict__ bias, TO* __restrict__ out,
+                                long long total, int n) {
+    pdl_wait();
+    pdl_trigger();
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x)
+        out[idx] = from_f32<TO>(in[idx] + bias[idx % n]);
+}
+
+extern "C" int vx_add_bias(const float* in, const float* bias, void* out, int rows, int n, int out_dtype,
+                           cudaStream_t stream) {
+    if (rows <= 0 || n <= 0) return VX_OK;
+    const long long total = (long long)rows * n;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (out_dtype == VX_F32)
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (add_bias_kernel<float>), (int)blocks, 256, 0, stream, in, bias, (float*)out, total, n);
+    else if (out_dtype == VX_BF16)
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (add_bias_kernel<bf16>), (int)blocks, 256, 0, stream, in, bias, (bf16*)out, total, n);
     else
         return VX_ERR_DTYPE;
     VX_LAUNCH_CHECK();

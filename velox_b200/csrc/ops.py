@@ -67,7 +67,8 @@ def _declare(lib) -> None:
         "vx_embedding": [P, P, P, I, I, I, I, P],
         "vx_add_rmsnorm": [P, P, P, P, P, P, I, I, F, I, P],
         "vx_rmsnorm": [P, P, P, I, I, F, I, P],
-        "vx_gated_act": [P, P, I, I, I, I, I, P],
+        "vx_gated_act": [P, P, I, I, I, I, I, I, P],
+        "vx_add_bias": [P, P, P, I, I, I, P],
         "vx_qk_norm_rope_kv": [P, I, P, P, F, P, I, P, P, P, P, I, I, I, I, I, I, P],
         "vx_paged_attention_generic": [P, I, P, P, P, I, P, P, P, I, F, I, I, I, I, I, I, I, P],
         "vx_gemm_nt_simt": [P, P, P, P, I, I, I, I, I, I, I, I, P],
@@ -205,16 +206,18 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     return out
 
 
-def gated_act(gate_up: torch.Tensor, activation: str, block: int = 0) -> torch.Tensor:
+def gated_act(gate_up: torch.Tensor, activation: str, block: int = 0,
+              out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """act(gate) * up.  block == 0: rows are [all gates | all ups]; block > 0: rows
-    are tiles of `block` gates followed by their `block` ups."""
+    are tiles of `block` gates followed by their `block` ups.  float32 input may give a
+    bfloat16 result (`out_dtype`)."""
     _dev(gate_up)
     _need(gate_up.is_contiguous() and gate_up.shape[-1] % 2 == 0, "gated_act: contiguous rows of even width")
     _need(activation in ACTIVATIONS, "gated_act: activation %r is not one of %s" % (activation, sorted(ACTIVATIONS)))
     rows, inner = gate_up.shape[0], gate_up.shape[-1] // 2
-    out = torch.empty((rows, inner), dtype=gate_up.dtype, device=gate_up.device)
+    out = torch.empty((rows, inner), dtype=out_dtype or gate_up.dtype, device=gate_up.device)
     _check(library().vx_gated_act(_ptr(gate_up), _ptr(out), rows, inner, ACTIVATIONS[activation], int(block),
-                                  dtype_code(gate_up.dtype), _stream()), "gated_act")
+                                  dtype_code(gate_up.dtype), dtype_code(out.dtype), _stream()), "gated_act")
     return out
 
 
@@ -513,12 +516,17 @@ def gemm_bf16(a: torch.Tensor, w: torch.Tensor, bias=None, out_dtype: Optional[t
     if not _MATMUL_SET:
         torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
         _MATMUL_SET = True
-    if out_dtype == torch.float32:
+    if out_dtype == torch.float32 or bias is not None:
         out = torch.mm(a, w.t(), out_dtype=torch.float32)
     else:
         out = torch.mm(a, w.t())
     if bias is not None:
-        out = (out.float() + bias).to(out_dtype)
+        # added to the float32 sums; the result is rounded once
+        _need(bias.dtype == torch.float32 and bias.numel() == w.shape[0], "gemm_bf16: float32 bias of N elements")
+        summed = out
+        out = torch.empty(summed.shape, dtype=out_dtype, device=a.device)
+        _check(library().vx_add_bias(_ptr(summed), _ptr(bias), _ptr(out), summed.shape[0], summed.shape[1],
+                                     dtype_code(out_dtype), _stream()), "add_bias")
     return out
 
 

@@ -64,6 +64,10 @@ class GatedMLP(FeedForward):
             # a prompt portion: tcgen05 product with the same epilogue (measured faster than
             # the library product followed by the activation kernel from about a thousand rows)
             a = ops.gemm_tcgen05(h, w, None, gated_activation=self.activation)
+        elif h.dtype == torch.bfloat16:
+            # the library product hands over its float32 sums: gate and up are not rounded
+            # before the activation, as in the fused kernels
+            a = ops.gated_act(self.gate_up(h, torch.float32), self.activation, self.tile, out_dtype=h.dtype)
         else:
             a = ops.gated_act(self.gate_up(h), self.activation, self.tile)
         return self.down(a)
