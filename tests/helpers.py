@@ -62,13 +62,14 @@ FP32_ATOL = 1e-4
 #   pooled over all rows of a test, the engine's rms distance is at most RMS_SLACK times
 #     the pooled cost (the scatter averages out over hundreds of rows; a part that rounds
 #     once more than it has to shows here: 1.4 to 1.7 times);
-#   no row's rms distance exceeds ROW_SLACK times its cost (or the pooled cost, if larger);
+#   no row's rms distance exceeds ROW_SLACK times its cost (or the pooled cost, if larger:
+#     the largest seen over some 15,000 rows of the tiny models is 1.3);
 #   no single value is further off than MAX_SLACK times that.
 # A wrong or missing key, a stale page or a wrong position moves logits by many times what
 # rounding does.  (An elementwise bound of 3e-2 + 3e-2 |x|, which the reference's kernel
 # tests use, tests/metal_decode_parity.rs:131-136, is a tenth of the spread of the tiny
 # models' logits and could hardly fail.)
-RMS_SLACK, ROW_SLACK, MAX_SLACK = 1.25, 3.0, 8.0
+RMS_SLACK, ROW_SLACK, MAX_SLACK = 1.25, 2.0, 8.0
 REPORT = []   # (what, rows, pooled ratio, largest row ratio, largest single-value ratio) per judged test
 
 

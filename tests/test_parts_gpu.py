@@ -174,8 +174,8 @@ def test_pre_norm_block(dtype):
                rope_theta=1e6)
     res = torch.randn(T, E, generator=torch.Generator().manual_seed(7)).to(DEV)
     want = P.decoder_layer(res.double().cpu().numpy(), np.arange(T), w, 0, cfg)
+    rounded = P.decoder_layer(res.double().cpu().numpy(), np.arange(T), w, 0, cfg, P.store_bfloat16)
     cache = CacheManager([att.cache_spec()], [None], 16, 4, 1, 4, dtype, DEV, poison=True)
     entries, ctx = step_context(cache, [("r", list(range(T)))], DEV)
     residual, delta = block.forward(res, None, ctx, cache.layer(0))
-    rounded = P.decoder_layer(res.double().cpu().numpy(), np.arange(T), w, 0, cfg, P.store_bfloat16)
-    close(residual.double() + delta.double(), want, dtype, "block", rounded)
+    close(residual.double() + delta.double(), want, dtype, "block", rounded)   # (the block updated `res` in place)

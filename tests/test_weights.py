@@ -17,7 +17,7 @@ class Recorder(DecoderModel):
     """A model that keeps what the loader binds, without touching kernels."""
 
     def bind(self, tensors, runtime):
-        self.bound = tensors
+        self.bound = dict(tensors)   # (tensors are made when looked up, and only while the files are open)
 
 
 def test_own_reader_agrees_with_the_safetensors_package(tmp_path):

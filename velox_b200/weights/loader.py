@@ -16,7 +16,7 @@ Element types on the device:
 """
 from __future__ import annotations
 
-from typing import Dict, List
+from typing import Callable, Dict, List, Mapping
 
 import torch
 
@@ -55,6 +55,24 @@ def held_dtype(role: str, stored: torch.dtype, runtime: Runtime) -> torch.dtype:
     return runtime.dtype
 
 
+class OnDemand(Mapping):
+    """name -> tensor on the device, made by `fetch` at every lookup and not kept."""
+
+    def __init__(self, fetch: Callable[[str], torch.Tensor], names):
+        self._fetch, self._names = fetch, names
+
+    def __getitem__(self, name: str) -> torch.Tensor:
+        if name not in self._names:
+            raise KeyError(name)
+        return self._fetch(name)
+
+    def __iter__(self):
+        return iter(self._names)
+
+    def __len__(self) -> int:
+        return len(self._names)
+
+
 def load_weights(model, folder: str, runtime: Runtime) -> None:
     """Reads the folder's safetensors and binds them to `model` on the device."""
     files = [SafetensorsFile(p) for p in model_files(folder)]
@@ -81,10 +99,15 @@ def load_weights(model, folder: str, runtime: Runtime) -> None:
         for f in files:
             f.close()
         raise WeightError(folder, missing, unexpected, wrong_shape, wrong_dtype)
-    tensors: Dict[str, torch.Tensor] = {}
-    for s in specs:
-        src = where[s.name].tensor(s.name)
-        tensors[s.name] = src.to(device=runtime.device, dtype=held_dtype(s.role, src.dtype, runtime)).contiguous()
-    model.bind(tensors, runtime)
+    by_name = {s.name: s for s in specs}
+
+    def fetch(name: str) -> torch.Tensor:
+        s = by_name[name]
+        src = where[name].tensor(name)
+        return src.to(device=runtime.device, dtype=held_dtype(s.role, src.dtype, runtime)).contiguous()
+    # A tensor goes to the device when its part binds it and is kept by nobody else: a part
+    # that fuses matrices (q, k, v; gate and up) holds the originals only while it does so,
+    # and the peak stays near the size of the model, not near twice that.
+    model.bind(OnDemand(fetch, by_name), runtime)
     for f in files:
         f.close()

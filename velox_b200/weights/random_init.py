@@ -74,10 +74,12 @@ def bind_random_weights(model, runtime, seed: int) -> None:
     """Random weights made on the device, without a file: for measurements on
     large shapes.  (The values differ from `write_random_model`'s, whose
     generator runs on the host.)"""
-    from .loader import held_dtype
+    from .loader import OnDemand, held_dtype
 
-    tensors = {}
-    for s in model.tensor_specs():
+    specs = {s.name: s for s in model.tensor_specs()}
+
+    def make(name: str) -> torch.Tensor:
+        s = specs[name]
         t = random_tensor(s, seed, torch.float32 if s.role in ("norm", "bias") else runtime.dtype, runtime.device)
-        tensors[s.name] = t.to(held_dtype(s.role, t.dtype, runtime)).contiguous()
-    model.bind(tensors, runtime)
+        return t.to(held_dtype(s.role, t.dtype, runtime)).contiguous()
+    model.bind(OnDemand(make, specs), runtime)   # (made when a part binds them: see `load_weights`)
