@@ -141,7 +141,7 @@ def stream_workload(args, cfg, layers):
     pool = args.pool_tokens or n_req * (longest + new_tokens + PAGE)
     engine = Engine(model_config=cfg, random_seed=SEED, config=EngineConfig(
         dtype="bfloat16", page_size=PAGE, num_pages=-(-pool // PAGE), max_running_requests=n_req,
-        max_batch_tokens=2048, max_model_len=longest + new_tokens + PAGE))
+        max_batch_tokens=args.max_batch_tokens, max_model_len=longest + new_tokens + PAGE))
     gen = torch.Generator().manual_seed(SEED + 2)
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist() for n in lens]
     # warm-up: kernels, graphs of a few batch sizes, the library's handles
@@ -181,10 +181,11 @@ def stream_workload(args, cfg, layers):
     return {"metric": "generated tok/s, continuous batching, Qwen3-%s bf16" % args.shape.upper(), "unit": "tokens/s",
             "value": round(n_req * new_tokens / wall, 1), "wall_s": round(wall, 3), "n_gpus": 1,
             "requests": n_req, "prompt_tokens": sum(lens), "new_tokens": n_req * new_tokens,
-            "arrival_rate": args.arrival_rate, "pool_tokens": pool,
+            "arrival_rate": args.arrival_rate, "pool_tokens": pool, "max_batch_tokens": args.max_batch_tokens,
             "ttft_ms": {"p50": pct(first.values(), 0.5), "p90": pct(first.values(), 0.9), "p99": pct(first.values(), 0.99)},
             "itl_ms": {"p50": pct(gaps, 0.5), "p90": pct(gaps, 0.9), "p99": pct(gaps, 0.99)},
             "steps": st["steps"], "preemptions": st["preemptions"], "layers": layers,
+            "mean_step_ms": round(st["total_step_us"] / max(st["steps"], 1) / 1000.0, 3),   # (the scheduler's own clock)
             "graphs_captured_before": captured, "capture_s": round(t_cap, 2),
             "data": "synthetic: random weights, uniform random token ids, seeded arrivals"}
 
@@ -205,6 +206,8 @@ def main() -> int:
     ap.add_argument("--lazy-graphs", action="store_true",
                     help="stream: capture each decode graph when a step first needs it, inside the run")
     ap.add_argument("--pool-tokens", type=int, default=0, help="stream: cache pool in tokens (0: room for all)")
+    ap.add_argument("--max-batch-tokens", type=int, default=2048,
+                    help="stream: new tokens of one step (a decoded token that rides with a prompt portion waits for it)")
     ap.add_argument("--shape", default="8b", choices=sorted(SHAPES),
                     help="layer sizes: 8b is the benchmark's; 14b and 32b are Qwen3-14B / 32B")
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64 and prefill")
@@ -231,7 +234,10 @@ def main() -> int:
     cfg = Qwen3Config.from_dict(raw)
     pk = peaks()
     if args.workload == "stream":
-        print(json.dumps(stream_workload(args, cfg, layers)))
+        with ClockSampler() as clocks:
+            res = stream_workload(args, cfg, layers)
+        res["clocks"] = clocks.summary()
+        print(json.dumps(res))
         return 0
     max_batch = 64 if not args.skip_points else args.batch
     engine = Engine(model_config=cfg, random_seed=SEED, config=EngineConfig(

@@ -7,8 +7,8 @@
 // query heads of one kv head (G in {1, 2, 4, 8}), so the heads of a group share
 // every key/value tile.  It walks over the request's keys in tiles of 128.
 //
-//   warps 0, 10-12  producers: warp 0 loads the query tile once; then, tile by tile,
-//               warps 0 and 10 load the keys and warps 11 and 12 the values, page by
+//   warps 0, 18-20  producers: warp 0 loads the query tile once; then, tile by tile,
+//               warps 0 and 18 load the keys and warps 19 and 20 the values, page by
 //               page with tiled TMA loads (128-byte swizzle), one 16-key x 64-column
 //               box per lane (eight lanes a warp), into two shared-memory buffers each;
 //   warp 1      tensor core: one thread issues S = Q K^T (128 x 128, 8 instructions
@@ -17,20 +17,22 @@
 //               O += P V (A operand straight from tensor memory, V as the
 //               MN-major B operand).  S of tile i + 1 is issued before P V of tile i,
 //               so the tensor core works while the softmax of tile i runs;
-//   warps 2-9   softmax: two threads own one query row (one lane of tensor memory),
-//               warps 2-5 its keys 0-63 of the tile, warps 6-9 its keys 64-127.  A
-//               thread reads its 64 scores, masks by select (causal: key <= the
-//               row's position; window: key >= position + 1 - W), exchanges the
-//               maximum with its partner through shared memory (one named barrier a
-//               tile), keeps the running maximum and its half of the sum in float32
-//               (base 2), writes the probabilities back over the scores as packed
-//               bfloat16, and rescales its half of the row of O only when the
-//               maximum has grown by more than 2^8 (the probabilities are then
+//   warps 2-17  softmax: four threads own one query row (one lane of tensor memory),
+//               warps 2-5 its keys 0-31 of the tile, warps 6-9 its keys 32-63, and so
+//               on.  A thread reads its 32 scores, masks by select (causal: key <=
+//               the row's position; window: key >= position + 1 - W), exchanges the
+//               maximum with its partners through shared memory (one named barrier a
+//               tile), keeps the running maximum and its quarter of the sum in
+//               float32 (base 2), writes the probabilities back over the scores as
+//               packed bfloat16, and rescales its quarter of the row of O only when
+//               the maximum has grown by more than 2^8 (the probabilities are then
 //               bounded by 256 instead of 1, which float32 and bfloat16 hold
-//               without loss of accuracy).  At the end the same warps add the two
-//               half sums, divide O by the sum and store it.  The softmax, not the
-//               tensor core, sets the pace of this kernel: with one thread per row
-//               a tile took about 4,300 cycles against 1,024 of tensor-core work.
+//               without loss of accuracy).  At the end the same warps add the four
+//               partial sums, divide O by the sum and store it.  The softmax, not the
+//               tensor core, sets the pace of this kernel, and what sets the pace of
+//               the softmax is the latency of each thread's chain of instructions,
+//               not the exponentials' throughput: with one thread per row a tile took
+//               about 4,300 cycles against 1,024 of tensor-core work, with two 2,050.
 //
 // Keys past the request's last key and below its window are masked; the values of a
 // tile that reaches past the last key are cleared in shared memory first, because a
@@ -46,8 +48,10 @@
 #define PT_ROWS 128
 #define PT_KEYS 128
 #define PT_D 128
-#define PT_THREADS 416
-#define PT_SOFTMAX_THREADS 256
+#define PT_THREADS 672
+#define PT_SOFTMAX_THREADS 512
+#define PT_SPLIT 4                   // threads that share a row
+#define PT_PART (PT_KEYS / PT_SPLIT)  // keys of a tile, and columns of O, per thread
 #define PT_SPIN_LIMIT (1 << 24)
 #define PT_LOG2E 1.4426950408889634f
 #define PT_HALF_BYTES (128 * 128)   // 128 rows x 64 columns of bf16: one swizzled half of a tile
@@ -113,9 +117,13 @@ __device__ __forceinline__ float pt_ex2(float x) {
 // 2^f by a cubic on [-0.5, 0.5] (relative error 1.4e-4, thirty times below the
 // rounding of a probability to bfloat16), 2^n by an add to the exponent bits.  The
 // special-function unit makes 16 exponentials a cycle per SM, which is as long as
-// the tile's tensor-core work; every PT_POLY_EVERY-th one goes this way instead.
+// the tile's tensor-core work; every PT_POLY_EVERY-th exponential can go this way
+// instead.  With eight softmax warps every fourth one did (8,192 tokens: 644 -> 613
+// us); with sixteen the unit's latency hides behind the other warps and the cubic's
+// nine instructions cost more than they save (8,192 tokens: 653 us with every
+// fourth, 626 with every eighth, 600 with none), so none does by default.
 #ifndef PT_POLY_EVERY
-#define PT_POLY_EVERY 4
+#define PT_POLY_EVERY 1024
 #endif
 __device__ __forceinline__ float pt_ex2_poly(float x) {
     x = fmaxf(x, -126.f);
@@ -193,8 +201,8 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
     __shared__ __align__(8) PtBarriers bars;
     __shared__ unsigned tmem_base_s;
     __shared__ int failed;
-    __shared__ float row_max[2][2][PT_ROWS];   // [tile parity][half of the keys][row]: the halves' maxima
-    __shared__ float row_sum[2][PT_ROWS];      // [half of the keys][row]: the halves' sums, at the end
+    __shared__ float row_max[2][PT_SPLIT][PT_ROWS];   // [tile parity][part of the keys][row]: the parts' maxima
+    __shared__ float row_sum[PT_SPLIT][PT_ROWS];      // [part of the keys][row]: the parts' sums, at the end
     unsigned char* smem = (unsigned char*)(((uintptr_t)pt_smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* q_s = smem;                                   // 32 KB
     unsigned char* k_s = smem + PT_TILE_BYTES;                   // 2 x 32 KB
@@ -227,7 +235,7 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
             pt_mbar_init(pt_smem_u32(&bars.v_full[i]), 1);
             pt_mbar_init(pt_smem_u32(&bars.v_empty[i]), 1);
             pt_mbar_init(pt_smem_u32(&bars.s_full[i]), 1);
-            pt_mbar_init(pt_smem_u32(&bars.p_ready[i]), 8);   // one arrival per softmax warp
+            pt_mbar_init(pt_smem_u32(&bars.p_ready[i]), PT_SOFTMAX_THREADS / 32);   // one arrival per softmax warp
             pt_mbar_init(pt_smem_u32(&bars.pv_done[i]), 1);
         }
         failed = 0;
@@ -244,13 +252,13 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
     const unsigned tmem_base = tmem_base_s;
     const unsigned tmem_o = tmem_base + 256;
 
-    if (warp == 0 || warp >= 10) {
-        // ---------------- producers: warps 0 and 10 the keys, 11 and 12 the values ----------------
+    if (warp == 0 || warp >= 18) {
+        // ---------------- producers: warps 0 and 18 the keys, 19 and 20 the values ----------------
         // A tiled TMA load takes some 70 cycles to issue, and a tile of keys and values is 32
         // boxes of 16 keys x 64 columns (a page holds 16 keys), so the boxes are spread over four
         // warps of eight lanes; keys and values wait for their own buffers (a key buffer is free
         // as soon as its scores are formed, long before the value buffer of the same tile).
-        const int pw = warp == 0 ? 0 : warp - 9;            // 0..3
+        const int pw = warp == 0 ? 0 : warp - 17;           // 0..3
         const int which = pw >> 1, part = pw & 1;           // keys / values; groups 0-3 / 4-7 of the tile
         if (pw == 0) {
             // queries: for each shared head, its tokens' two 64-column halves
@@ -346,10 +354,10 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
             if (!ok) { failed = 1; atomicExch(error, 12); }
         }
     } else {
-        // ---------------- softmax and epilogue: two threads own one row ----------------
-        const int sw = warp - 2;                                 // 0..7
+        // ---------------- softmax and epilogue: four threads own one row ----------------
+        const int sw = warp - 2;                                 // 0..15
         const int quarter = warp & 3;                            // the warp's quarter of tensor memory's lanes
-        const int hc = sw >> 2;                                  // which 64 keys of a tile, which 64 columns of O
+        const int hc = sw >> 2;                                  // which 32 keys of a tile, which 32 columns of O
         const int r = quarter * 32 + lane;                       // row of the tile = lane of tensor memory
         const int tok = r & (toks_per_tile - 1), hi = r >> (7 - share_log2);
         const int pos = off + t0 + tok;
@@ -357,50 +365,47 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
         const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
         float m_used = -INFINITY, l = 0.f;
         const int warp_min_pos = __reduce_min_sync(0xffffffffu, pos), warp_max_lo = __reduce_max_sync(0xffffffffu, lo);
-        // All 256 threads pass the same named barriers in the same order whatever
+        // All softmax threads pass the same named barriers in the same order whatever
         // happens: a thread whose bounded wait ran out skips its work, and the
         // barrier's AND tells everybody to stop at the same place.
         bool ok = true;
         int i = 0;
         for (; i < ntiles; ++i) {
             const int b = i & 1;
-            const int key_base = (tile_lo + i) * PT_KEYS + hc * 64;   // of this thread's 64 keys
+            const int key_base = (tile_lo + i) * PT_KEYS + hc * PT_PART;   // of this thread's 32 keys
             if (ok) ok = pt_mbar_wait(pt_smem_u32(&bars.s_full[b]), (unsigned)((i >> 1) & 1));
             ok = __all_sync(0xffffffffu, ok);
             const unsigned s_addr = tmem_base + (unsigned)(b * 128) + lane_addr;
             // A stretch of keys that every row of the warp sees whole needs no masking at all.
-            const bool whole = key_base + 63 <= warp_min_pos && key_base >= warp_max_lo;
-            unsigned v[2][32];
+            const bool whole = key_base + PT_PART - 1 <= warp_min_pos && key_base >= warp_max_lo;
+            unsigned v[32];
             float mx = -INFINITY;
             if (ok) {
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                // the 64 scores are read once and stay in registers for both passes
-                pt_ld32_issue(s_addr + (unsigned)(hc * 64), v[0]);
-                pt_ld32_issue(s_addr + (unsigned)(hc * 64 + 32), v[1]);
-                pt_wait_ld();
-                // pass 1: the maximum over the visible keys
+                // the 32 scores are read once and stay in registers for both passes
+                pt_ld32(s_addr + (unsigned)(hc * PT_PART), v);
+                // pass 1: the maximum over the visible keys, in four chains so that no
+                // instruction waits for the one before it
+                float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
                 if (whole) {
 #pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(v[c][j]));
-                    }
+                    for (int j = 0; j < 32; j += 2)   // (the three-input maximum: one instruction for two scores)
+                        asm("max.f32 %0, %0, %1, %2;\n" : "+f"(m4[(j >> 1) & 3]) : "f"(__uint_as_float(v[j])), "f"(__uint_as_float(v[j + 1])));
                 } else {
 #pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const int key = key_base + c * 32 + j;
-                            if (key <= pos && key >= lo) mx = fmaxf(mx, __uint_as_float(v[c][j]));
-                        }
+                    for (int j = 0; j < 32; ++j) {
+                        const int key = key_base + j;
+                        if (key <= pos && key >= lo) m4[j & 3] = fmaxf(m4[j & 3], __uint_as_float(v[j]));
                     }
                 }
+                mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
             }
             row_max[b][hc][r] = mx;
             // (also orders every thread's reads of the scores before anybody's writes of probabilities)
             if (!pt_softmax_barrier_and(ok)) { ok = false; break; }
-            mx = fmaxf(mx, row_max[b][hc ^ 1][r]) * scale_log2;   // (the scale is positive)
-            // The reference maximum moves only when it has grown by more than the threshold.
+            mx = fmaxf(fmaxf(row_max[b][0][r], row_max[b][1][r]), fmaxf(row_max[b][2][r], row_max[b][3][r])) * scale_log2;
+            // (the scale is positive)  The reference maximum moves only when it has grown by more than the
+            // threshold; the four threads of a row see the same maxima and decide alike.
             float alpha = 1.f;
             bool move = mx > m_used + PT_RESCALE_THRESHOLD;
             if (move) {
@@ -409,54 +414,50 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
                 l *= alpha;
             }
             if (i > 0 && __any_sync(0xffffffffu, move)) {
-                // this half of O is rescaled in the rows that moved; P V of the previous tile must be complete
+                // this part of O is rescaled in the rows that moved; P V of the previous tile must be complete
                 ok = pt_mbar_wait(pt_smem_u32(&bars.pv_done[b ^ 1]), (unsigned)(((i - 1) >> 1) & 1));
                 ok = __all_sync(0xffffffffu, ok);
                 if (ok) {
                     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-#pragma unroll 1
-                    for (int c = 0; c < 2; ++c) {
-                        unsigned acc[32];
-                        pt_ld32(tmem_o + lane_addr + (unsigned)(hc * 64 + c * 32), acc);
+                    unsigned acc[32];
+                    pt_ld32(tmem_o + lane_addr + (unsigned)(hc * PT_PART), acc);
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) acc[j] = __float_as_uint(__uint_as_float(acc[j]) * alpha);
-                        pt_st32(tmem_o + lane_addr + (unsigned)(hc * 64 + c * 32), acc);
-                    }
+                    for (int j = 0; j < 32; ++j) acc[j] = __float_as_uint(__uint_as_float(acc[j]) * alpha);
+                    pt_st32(tmem_o + lane_addr + (unsigned)(hc * PT_PART), acc);
                 }
             }
             if (ok) {
                 // pass 2: probabilities, written back over the scores as packed bfloat16
-                float ps = 0.f;
+                float ps0 = 0.f, ps1 = 0.f;
                 const float neg_m = -m_used;   // (-inf only if the row has seen no key yet; then nothing is visible)
+                unsigned pk[16];
+                if (whole) {
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    unsigned pk[16];
-                    if (whole) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 2) {
-                            const float x0 = fmaf(__uint_as_float(v[c][j]), scale_log2, neg_m);
-                            const float x1 = fmaf(__uint_as_float(v[c][j + 1]), scale_log2, neg_m);
-                            const float p0 = (j % PT_POLY_EVERY == PT_POLY_EVERY - 1) ? pt_ex2_poly(x0) : pt_ex2(x0);
-                            const float p1 = ((j + 1) % PT_POLY_EVERY == PT_POLY_EVERY - 1) ? pt_ex2_poly(x1) : pt_ex2(x1);
-                            ps += p0 + p1;
-                            const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                            pk[j >> 1] = *reinterpret_cast<const unsigned*>(&h);
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 2) {
-                            const int key = key_base + c * 32 + j;
-                            float p0 = 0.f, p1 = 0.f;
-                            if (key <= pos && key >= lo) p0 = pt_ex2(fmaf(__uint_as_float(v[c][j]), scale_log2, neg_m));
-                            if (key + 1 <= pos && key + 1 >= lo) p1 = pt_ex2(fmaf(__uint_as_float(v[c][j + 1]), scale_log2, neg_m));
-                            ps += p0 + p1;
-                            const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                            pk[j >> 1] = *reinterpret_cast<const unsigned*>(&h);
-                        }
+                    for (int j = 0; j < 32; j += 2) {
+                        const float x0 = fmaf(__uint_as_float(v[j]), scale_log2, neg_m);
+                        const float x1 = fmaf(__uint_as_float(v[j + 1]), scale_log2, neg_m);
+                        const float p0 = (j % PT_POLY_EVERY == PT_POLY_EVERY - 1) ? pt_ex2_poly(x0) : pt_ex2(x0);
+                        const float p1 = ((j + 1) % PT_POLY_EVERY == PT_POLY_EVERY - 1) ? pt_ex2_poly(x1) : pt_ex2(x1);
+                        ps0 += p0;
+                        ps1 += p1;
+                        const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                        pk[j >> 1] = *reinterpret_cast<const unsigned*>(&h);
                     }
-                    pt_st16(s_addr + (unsigned)(hc * 32 + c * 16), pk);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        const int key = key_base + j;
+                        float p0 = 0.f, p1 = 0.f;
+                        if (key <= pos && key >= lo) p0 = pt_ex2(fmaf(__uint_as_float(v[j]), scale_log2, neg_m));
+                        if (key + 1 <= pos && key + 1 >= lo) p1 = pt_ex2(fmaf(__uint_as_float(v[j + 1]), scale_log2, neg_m));
+                        ps0 += p0;
+                        ps1 += p1;
+                        const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                        pk[j >> 1] = *reinterpret_cast<const unsigned*>(&h);
+                    }
                 }
-                l += ps;
+                pt_st16(s_addr + (unsigned)(hc * (PT_PART / 2)), pk);
+                l += ps0 + ps1;
             }
             if (ok && (tile_lo + i + 1) * PT_KEYS > kv_hi) {
                 // the tile reaches past the last key: clear those value rows (both halves)
@@ -485,21 +486,19 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
             ok = pt_mbar_wait(pt_smem_u32(&bars.pv_done[last & 1]), (unsigned)((last >> 1) & 1));
             ok = __all_sync(0xffffffffu, ok);
         }
-        // the two halves of a row's sum meet here (every thread arrives, failed or not)
+        // the parts of a row's sum meet here (every thread arrives, failed or not)
         row_sum[hc][r] = l;
         const bool all_ok = pt_softmax_barrier_and(ok);
         if (!all_ok) {
             if (!ok && lane == 0) { failed = 1; atomicExch(error, 13); }
         } else {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            const float inv = 1.f / (row_sum[0][r] + row_sum[1][r]);
+            const float inv = 1.f / ((row_sum[0][r] + row_sum[1][r]) + (row_sum[2][r] + row_sum[3][r]));
             const bool live = tok < toks_live;
-            bf16* dst = out + (size_t)(row_base + t0 + tok) * out_row_stride + (size_t)(hk * share + hi) * PT_D + hc * 64;
-#pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-                unsigned acc[32];
-                pt_ld32(tmem_o + lane_addr + (unsigned)(hc * 64 + c * 32), acc);
-                if (!live) continue;
+            bf16* dst = out + (size_t)(row_base + t0 + tok) * out_row_stride + (size_t)(hk * share + hi) * PT_D + hc * PT_PART;
+            unsigned acc[32];
+            pt_ld32(tmem_o + lane_addr + (unsigned)(hc * PT_PART), acc);
+            if (live) {
 #pragma unroll
                 for (int j = 0; j < 32; j += 8) {
                     uint4 pk;
@@ -508,7 +507,7 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
                     for (int q2 = 0; q2 < 4; ++q2)
                         h[q2] = __floats2bfloat162_rn(__uint_as_float(acc[j + 2 * q2]) * inv,
                                                       __uint_as_float(acc[j + 2 * q2 + 1]) * inv);
-                    *reinterpret_cast<uint4*>(dst + c * 32 + j) = pk;
+                    *reinterpret_cast<uint4*>(dst + j) = pk;
                 }
             }
         }
