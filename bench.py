@@ -191,6 +191,7 @@ def stream_workload(args, cfg, layers):
 
 
 def main() -> int:
+    global CONTEXT, PROMPT
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
@@ -211,6 +212,9 @@ def main() -> int:
     ap.add_argument("--shape", default="8b", choices=sorted(SHAPES),
                     help="layer sizes: 8b is the benchmark's; 14b and 32b are Qwen3-14B / 32B")
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64 and prefill")
+    ap.add_argument("--context", type=int, default=CONTEXT,
+                    help="context length the decoding requests reach (the benchmark's is %d; others for measurements "
+                         "beside it; the prefill point is a prompt of half of it)" % CONTEXT)
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -222,6 +226,7 @@ def main() -> int:
         print("bench.py: this engine runs on one GPU; --gpus %d is not supported" % args.gpus)
         return 2
     K, W = max(1, args.steps), max(3, args.warmup)
+    CONTEXT, PROMPT = int(args.context), int(args.context) // 2
 
     import torch
     from velox_b200 import Engine, EngineConfig, Qwen3Config, SamplingParams
@@ -239,7 +244,13 @@ def main() -> int:
         res["clocks"] = clocks.summary()
         print(json.dumps(res))
         return 0
-    max_batch = 64 if not args.skip_points else args.batch
+    # the points' largest batch: 64, or what the cache of so many requests at this context leaves room for
+    per_token = 2 * layers * cfg.num_key_value_heads * cfg.head_dim * 2
+    free_bytes = torch.cuda.mem_get_info()[0] - weight_bytes(raw, layers)
+    big = 64
+    while big > args.batch and big * (CONTEXT + PAGE) * per_token > 0.8 * free_bytes:
+        big //= 2
+    max_batch = max(big, args.batch) if not args.skip_points else args.batch
     engine = Engine(model_config=cfg, random_seed=SEED, config=EngineConfig(
         dtype="bfloat16", page_size=PAGE, num_pages=max_batch * (CONTEXT // PAGE + 1) + 8,
         max_running_requests=max_batch, max_batch_tokens=2048, max_model_len=CONTEXT + PAGE))
@@ -258,7 +269,8 @@ def main() -> int:
         torch.cuda.synchronize()
         return a.elapsed_time(b) / steps
 
-    def decode_run(batch, steps, warmup, context=CONTEXT):
+    def decode_run(batch, steps, warmup, context=None):
+        context = context or CONTEXT
         """`batch` requests prefilled so that the timed steps end at the context
         length.  Times `steps` steps through the public entry point (host ids in,
         sampled ids out, every step), then `steps` steps of the step function and
@@ -336,10 +348,10 @@ def main() -> int:
                           "frac": round(fl / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
         pts = {}
         steps = min(K, 32)
-        for b in ((1, 32, 64) if args.shape == "32b" else (1, 64)):
+        for b in ((1, 32, big) if args.shape == "32b" and big > 32 else (1, big)):
             _, m, _, _ = decode_run(b, steps, 4)
             pts["decode_b%d" % b] = round(b * 1000.0 / m, 1)
-        for b in (1, args.batch, 64):  # the same with half the context behind each request
+        for b in (1, args.batch, big):  # the same with half the context behind each request
             _, m, _, _ = decode_run(b, steps, 4, context=CONTEXT // 2)
             pts["decode_b%d_ctx%d" % (b, CONTEXT // 2)] = round(b * 1000.0 / m, 1)
         out["points"] = pts
