@@ -116,6 +116,6 @@ def test_quantized_checkpoints_are_refused_and_the_registry_fills_itself(tmp_pat
 def test_a_head_size_no_kernel_takes_is_refused_when_the_model_is_built():
     from velox_b200.models import DecoderModel
     from velox_b200.models.qwen3 import qwen3_plan
-    cfg = Qwen3Config.from_dict(dict(TINY["tiny_a"]["config"], head_dim=24))
-    with pytest.raises(ValueError, match="head_dim 24.*multiples of 16 up to 256"):
+    cfg = Qwen3Config.from_dict(dict(TINY["tiny_a"]["config"], head_dim=258))
+    with pytest.raises(ValueError, match="head_dim 258.*even head sizes up to 256"):
         DecoderModel(qwen3_plan(cfg))

@@ -231,6 +231,7 @@ ATT_CASES = [
     ([(0, 50), (45, 5), (63, 1)], 4, 1, 80, 16, 13),         # a window that is no multiple of the page
     ([(300, 2)], 2, 1, 256, 16, 0),                          # the largest head size
     ([(31, 1), (32, 1), (33, 1)], 4, 2, 16, 16, 0),          # around a page's edge
+    ([(0, 21), (40, 3)], 6, 2, 40, 4, 0),                    # a head size that is even and no multiple of 16
 ]
 
 

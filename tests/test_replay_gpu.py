@@ -201,6 +201,13 @@ ODD = {
                               max_position_embeddings=1024, tie_word_embeddings=False, rope_theta=500000.0,
                               rms_norm_eps=1e-6, hidden_act="silu", use_sliding_window=True, sliding_window=33,
                               max_window_layers=0)),
+    # a head size that is even and no multiple of 16 (40), three query heads per kv head, a width of 72
+    "odd_c": dict(seed=13, page_size=4, lens=[90, 45, 33, 70, 1, 2, 3, 64],
+                  config=dict(vocab_size=211, hidden_size=72, intermediate_size=104, num_hidden_layers=2,
+                              num_attention_heads=6, head_dim=40, attention_bias=False, num_key_value_heads=2,
+                              max_position_embeddings=512, tie_word_embeddings=True, rope_theta=10000.0,
+                              rms_norm_eps=1e-6, hidden_act="silu", use_sliding_window=True, sliding_window=50,
+                              max_window_layers=1)),
 }
 
 

@@ -1,5 +1,5 @@
-// Paged causal attention, the general kernel: any head size that is a multiple
-// of 16 (up to 256), any number of heads and groups, any page size, an optional
+// Paged causal attention, the general kernel: any head size up to 256, any
+// number of heads and groups, any page size, an optional
 // window, element type float or bfloat16.  It serves prompt portions and decoded
 // tokens alike, and it is the whole of the 32-bit path.
 //
@@ -113,7 +113,7 @@ extern "C" int vx_paged_attention_generic(const void* q, int q_row_stride, const
                                           int out_row_stride, float scale, int window, int tokens,
                                           int H, int Hk, int D, int S, int dtype, cudaStream_t stream) {
     if (tokens <= 0) return VX_OK;
-    if (H <= 0 || Hk <= 0 || H % Hk || D <= 0 || D > ATT_MAX_D || D % 16 || S <= 0 || max_blocks <= 0)
+    if (H <= 0 || Hk <= 0 || H % Hk || D <= 0 || D > ATT_MAX_D || S <= 0 || max_blocks <= 0)
         return VX_ERR_SHAPE;
     if (window < 0) return VX_ERR_SHAPE;
     dim3 grid(tokens, H);

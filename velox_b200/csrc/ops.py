@@ -249,8 +249,9 @@ ATTENTION_MAX_HEAD_DIM = 256
 
 
 def attention_head_dim_supported(head_dim: int) -> bool:
-    """Head sizes some attention kernel of the library takes: multiples of 16 up to 256."""
-    return 0 < head_dim <= ATTENTION_MAX_HEAD_DIM and head_dim % 16 == 0
+    """Head sizes some attention kernel of the library takes: even ones up to 256 (the general
+    kernel; the tensor-core kernels take 64 and 128)."""
+    return 0 < head_dim <= ATTENTION_MAX_HEAD_DIM and head_dim % 2 == 0
 
 
 def paged_attention_generic(q: torch.Tensor, q_row_stride: int, k_pool, v_pool, block_table: torch.Tensor,
@@ -261,7 +262,7 @@ def paged_attention_generic(q: torch.Tensor, q_row_stride: int, k_pool, v_pool, 
           "paged_attention: int32 block table [requests, blocks]")
     _need(k_pool.dtype == q.dtype and v_pool.dtype == q.dtype, "paged_attention: pools of the queries' element type")
     _need(attention_head_dim_supported(head_dim),
-          "paged_attention: head size %d (the kernels take multiples of 16 up to %d)" % (head_dim, ATTENTION_MAX_HEAD_DIM))
+          "paged_attention: head size %d (the kernels take even sizes up to %d)" % (head_dim, ATTENTION_MAX_HEAD_DIM))
     out = torch.empty((tokens, num_heads * head_dim), dtype=q.dtype, device=q.device)
     _check(library().vx_paged_attention_generic(
         _ptr(q), q_row_stride, _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1],

@@ -19,7 +19,6 @@ import torch
 
 from .. import models as _models  # noqa: F401  (registers architectures)
 from ..cache.manager import CacheManager
-from ..csrc import ops
 from ..config.engine_config import EngineConfig
 from ..config.model_config import ModelConfig
 from ..config.registry import load_config, resolve_architecture

@@ -44,7 +44,7 @@ class PagedAttention(Mixer):
         if num_heads % num_kv_heads:
             raise ValueError("num_heads %d is not a multiple of num_kv_heads %d" % (num_heads, num_kv_heads))
         if not ops.attention_head_dim_supported(int(head_dim)):
-            raise ValueError("%shead_dim %d: the attention kernels take head sizes that are multiples of 16 up to %d"
+            raise ValueError("%shead_dim %d: the attention kernels take even head sizes up to %d"
                              % (prefix, head_dim, ops.ATTENTION_MAX_HEAD_DIM))
         self.hidden_size, self.num_heads, self.num_kv_heads = int(hidden_size), int(num_heads), int(num_kv_heads)
         self.head_dim, self.bias, self.qk_norm = int(head_dim), bool(bias), bool(qk_norm)
