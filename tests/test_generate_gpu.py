@@ -292,3 +292,51 @@ def test_cancelling_a_request_leaves_the_others_tokens_as_they_were(model_folder
     assert st["requests_aborted"] == 2 and st["requests_completed"] == 2 and st["last_step_us"] > 0
     assert e.cache.free_pages() == [48]
     e.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("portion", [40, 16])
+def test_small_mixed_steps_of_a_recurring_shape_run_from_a_graph(model_folders, dtype, portion):
+    """A long prompt fed in portions of a fixed size beside four decoding requests gives the same
+    shape of step again and again: from its third occurrence the step is captured in a CUDA graph
+    and replayed.  Logits before, at and after the capture against the plain implementation (a
+    portion of 40 goes to the tcgen05 prompt kernel, one of 16 token by token to the decode kernel)."""
+    from helpers import Oracle, RoundingJudge, assert_close
+    from velox_b200.engine import StepEntry
+    name = "tiny_d"
+    cfg, w = P.load_model_folder(model_folders[name])
+    from velox_b200 import Engine, EngineConfig
+    e = Engine(model_folders[name], EngineConfig(dtype=dtype, page_size=16, num_pages=96, max_model_len=512,
+                                                 max_running_requests=8), poison_cache=True)
+    steps = 9
+    long_ = random_tokens(cfg["vocab_size"], 30 + portion * steps, 77)
+    shorts = [random_tokens(cfg["vocab_size"], 20 + 13 * i + steps, 78 + i) for i in range(4)]
+    oracles = {"L": Oracle(cfg, w, long_)}
+    oracles.update({"s%d" % i: Oracle(cfg, w, t) for i, t in enumerate(shorts)})
+    judge = RoundingJudge.of(oracles.values(), "mixed steps from a graph (%d)" % portion)
+    e.cache.add_request("L")
+    e.run_step([StepEntry("L", long_[:30], [])])
+    at = {"L": 30}
+    for i, t in enumerate(shorts):
+        e.cache.add_request("s%d" % i)
+        at["s%d" % i] = len(t) - steps
+        e.run_step([StepEntry("s%d" % i, t[:at["s%d" % i]], [])])
+    for k in range(steps):
+        entries, rows, costs = [], [], []
+        for i, t in enumerate(shorts):
+            rid = "s%d" % i
+            entries.append(StepEntry(rid, [t[at[rid]]], [0]))
+            rows.append(oracles[rid][at[rid]])
+            costs.append(oracles[rid].cost[at[rid]])
+            at[rid] += 1
+        entries.insert(2, StepEntry("L", long_[at["L"]:at["L"] + portion], [0, portion - 1]))   # (in the middle of the step)
+        rows[2:2] = [oracles["L"][at["L"]], oracles["L"][at["L"] + portion - 1]]
+        costs[2:2] = [oracles["L"].cost[at["L"]], oracles["L"].cost[at["L"] + portion - 1]]
+        at["L"] += portion
+        got = e.run_step(entries).cpu().numpy()
+        assert_close(got, np.stack(rows), dtype, "step %d (%d graphs)" % (k, len(e.runner.graphs.mixed)),
+                     cost=np.array(costs), judge=judge)
+    if dtype == "bfloat16":
+        judge.finish()
+    g = e.runner.graphs
+    assert len(g.mixed) >= 1 and any(m.graph is not None for m in g.mixed.values()), "no mixed step was captured"

@@ -16,7 +16,7 @@ def manager(window=24):
     return CacheManager(specs, [None, None, None], 8, 64, 6, 32)
 
 
-def plain(entries, cache):
+def plain(entries, cache, short_max=1):
     """The description built row by row from the request's books."""
     S, MB = cache.page_size, cache.max_blocks
     out = dict(token_ids=[], positions=[], seq_of_token=[], cu_seqlens=[0], kv_offsets=[], state_slots=[], wanted_rows=[],
@@ -36,8 +36,8 @@ def plain(entries, cache):
         out["kv_offsets"].append(rc.length)
         out["state_slots"].append(rc.slot)
         out["wanted_rows"] += [row + w for w in e.want]
-        if len(e.tokens) == 1:
-            out["single_rows"].append(row)
+        if len(e.tokens) <= short_max:
+            out["single_rows"] += list(range(row, row + len(e.tokens)))
         else:
             out["portion_seqs"].append(i)
         for g, table in zip(groups, rc.tables):
@@ -72,7 +72,14 @@ def test_a_mixed_step_is_described_as_the_books_say():
         sm = buf[starts[10 + 2 * g]:starts[10 + 2 * g] + sizes[10 + 2 * g]]
         assert bt.tolist() == ref["bt"] and sm.tolist() == ref["sm"]
     assert -1 in groups[1]["bt"][1][:4]            # pages the window passed are gone from request 7's table
-    assert summary == [33, 4, 19, 71, 1, 71, 3, 0]   # one request brings a single token (and has 71 keys then)
+    assert summary == [33, 4, 19, 71, 1, 71, 3, 1]   # one request brings a single token (and has 71 keys then)
+    # requests of up to 11 tokens listed token by token: a's 11, 7's one and d's two rows; b's 19 stay a portion
+    buf, sizes, starts, summary = build_step_arrays(entries, m, vocab_size=100, short_max=11)
+    want, _ = plain(entries, m, short_max=11)
+    assert want["single_rows"] == list(range(0, 12)) + [31, 32] and want["portion_seqs"] == [2]
+    for k, name in enumerate(want):
+        assert buf[starts[k]:starts[k] + sizes[k]].tolist()[:len(want[name])] == want[name], name
+    assert summary == [33, 4, 19, 71, 14, 71, 1, 11]
     assert all(s % 4 == 0 for s in starts)         # every section on a 16-byte boundary
 
 

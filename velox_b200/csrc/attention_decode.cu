@@ -57,7 +57,7 @@ paged_decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, cons
                               const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                               float* __restrict__ part_o, float* __restrict__ part_ml, int max_pieces,
                               bf16* __restrict__ out, int out_row_stride, float scale_log2, int window,
-                              int H, int Hk, int S, int piece_tiles, int requests) {
+                              int H, int Hk, int S, int piece_tiles, int requests, int early_ok) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     constexpr int TILE_BYTES = 16 * D * 2;
     constexpr int CHUNKS_PER_ROW = D / 8;
@@ -89,7 +89,9 @@ paged_decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, cons
     // The tiles asked for first hold keys and values of earlier steps, unless they reach the
     // request's newest position (which the kernel before this one has just written, or is
     // still writing): only then do they have to wait for that kernel.
-    const bool early = ((tile_begin + DEC_STAGES - 1) << 4) <= kv_len - 1;
+    // (`early_ok` is 0 when a request brings several tokens in this step: then the kernel before this
+    // one has written more than the newest position, and nothing is asked for before the wait)
+    const bool early = early_ok && ((tile_begin + DEC_STAGES - 1) << 4) <= kv_len - 1;
 
     auto issue = [&](int j) {
         const int key0 = (tile_begin + j) << 4;
@@ -353,11 +355,11 @@ static int launch_decode_pieces(int blocks, const bf16* q, int q_row_stride, con
                                 const int* block_table, int max_blocks, const int* token_rows,
                                 const int* seq_of_token, const int* positions, float* part_o, float* part_ml,
                                 int max_pieces, bf16* out, int out_row_stride, float scale, int window, int requests,
-                                int H, int Hk, int S, int piece_tiles, cudaStream_t stream) {
+                                int H, int Hk, int S, int piece_tiles, int early_ok, cudaStream_t stream) {
     const size_t smem = (size_t)WARPS * STAGES * 2 * 16 * D * 2;
     VX_LAUNCH_K(VX_K_ATTENTION, (paged_decode_attention_kernel<D, STAGES, WARPS>), dim3(blocks), WARPS * 32, smem, stream,
                 q, q_row_stride, k_pool, v_pool, block_table, max_blocks, token_rows, seq_of_token, positions, part_o,
-                part_ml, max_pieces, out, out_row_stride, scale * LOG2E, window, H, Hk, S, piece_tiles, requests);
+                part_ml, max_pieces, out, out_row_stride, scale * LOG2E, window, H, Hk, S, piece_tiles, requests, early_ok);
     VX_LAUNCH_CHECK();
     return VX_OK;
 }
@@ -392,7 +394,7 @@ static int launch_decode(const bf16* q, int q_row_stride, const bf16* k_pool, co
                          const int* block_table, int max_blocks, const int* token_rows,
                          const int* seq_of_token, const int* positions, float* scratch, int max_pieces,
                          bf16* out, int out_row_stride, float scale, int window, int requests, int H, int Hk,
-                         int S, int piece_tiles, cudaStream_t stream) {
+                         int S, int piece_tiles, int early_ok, cudaStream_t stream) {
     const int ready = configure_decode<D>();
     if (ready != VX_OK) return ready;
     float* part_o = scratch;
@@ -406,7 +408,7 @@ static int launch_decode(const bf16* q, int q_row_stride, const bf16* k_pool, co
 #define DEC_LAUNCH(ST, W)                                                                                            \
     launch_decode_pieces<D, ST, W>(blocks, q, q_row_stride, k_pool, v_pool, block_table, max_blocks, token_rows,       \
                                    seq_of_token, positions, part_o, part_ml, max_pieces, out, out_row_stride, scale, \
-                                   window, requests, H, Hk, S, piece_tiles, stream)
+                                   window, requests, H, Hk, S, piece_tiles, early_ok, stream)
     int rc;
     if (warps == 5) rc = DEC_LAUNCH(5, 5);
     else if (warps == 6) rc = DEC_LAUNCH(4, 6);
@@ -422,8 +424,11 @@ static int launch_decode(const bf16* q, int q_row_stride, const bf16* k_pool, co
     return VX_OK;
 }
 
-// One query token per request.  `token_rows[i]` is the token row (in q, out,
-// seq_of_token, positions) of request i, or null when request i is row i.
+// One query token per entry.  `token_rows[i]` is the token row (in q, out,
+// seq_of_token, positions) of entry i, or null when entry i is row i; several
+// entries may be tokens of one request (a short prompt portion, token by token).
+// `early_ok`: every entry is its request's only new token of this step (then a warp
+// may ask for keys and values of earlier positions before the kernel before it ends).
 // `max_pieces` bounds the pieces of any request: ceil(ceil(max keys / 16) / piece_tiles)
 // (one more with a window that does not start on a tile's edge); `scratch` holds
 // vx_paged_decode_scratch_floats(...) floats (may be null when max_pieces is 1).
@@ -432,7 +437,7 @@ extern "C" int vx_paged_decode_attention(const void* q, int q_row_stride, const 
                                          const int* token_rows, const int* seq_of_token,
                                          const int* positions, float* scratch, int max_pieces, void* out,
                                          int out_row_stride, float scale, int window, int requests, int H,
-                                         int Hk, int D, int S, int piece_tiles, cudaStream_t stream) {
+                                         int Hk, int D, int S, int piece_tiles, int early_ok, cudaStream_t stream) {
     if (requests <= 0) return VX_OK;
     if (H <= 0 || Hk <= 0 || H % Hk || H / Hk > 16 || S <= 0 || S % 16 || window < 0) return VX_ERR_SHAPE;
     if (piece_tiles <= 0 || piece_tiles > 32 || max_pieces <= 0 || (max_pieces > 1 && !scratch)) return VX_ERR_SHAPE;
@@ -443,12 +448,12 @@ extern "C" int vx_paged_decode_attention(const void* q, int q_row_stride, const 
         return launch_decode<128>((const bf16*)q, q_row_stride, (const bf16*)k_pool, (const bf16*)v_pool,
                                   block_table, max_blocks, token_rows, seq_of_token, positions, scratch,
                                   max_pieces, (bf16*)out, out_row_stride, scale, window, requests, H, Hk, S,
-                                  piece_tiles, stream);
+                                  piece_tiles, early_ok, stream);
     if (D == 64)
         return launch_decode<64>((const bf16*)q, q_row_stride, (const bf16*)k_pool, (const bf16*)v_pool,
                                  block_table, max_blocks, token_rows, seq_of_token, positions, scratch,
                                  max_pieces, (bf16*)out, out_row_stride, scale, window, requests, H, Hk, S,
-                                 piece_tiles, stream);
+                                 piece_tiles, early_ok, stream);
     return VX_ERR_SHAPE;
 }
 
@@ -494,7 +499,7 @@ extern "C" int vx_paged_decode_attention_static(const void* q, int q_row_stride,
     vx_pdl_suppress(1);
     const int rc = vx_paged_decode_attention(q, q_row_stride, k_pool, v_pool, block_table, max_blocks, token_rows,
                                              seq_of_token, positions, g_decode_static_ptr[dev], max_splits, out,
-                                             out_row_stride, scale, window, requests, H, Hk, D, S, chunk_tiles, stream);
+                                             out_row_stride, scale, window, requests, H, Hk, D, S, chunk_tiles, 1, stream);
     vx_pdl_suppress(0);
     return rc;
 }

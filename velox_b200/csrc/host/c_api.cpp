@@ -108,8 +108,8 @@ int vxh_cache_commit_many(void* c, int n, const int64_t* rids, const int* counts
 
 // ---- step builders ----
 int vxh_build_step(void* c, int n, const int64_t* rids, const int* lens, const int* tokens, const int* want_counts,
-                   const int* wants, int vocab, int32_t* dst, const int64_t* starts, int64_t* summary) {
-    return build_step(*(CacheBook*)c, n, rids, lens, tokens, want_counts, wants, vocab, dst, starts, summary);
+                   const int* wants, int vocab, int short_max, int32_t* dst, const int64_t* starts, int64_t* summary) {
+    return build_step(*(CacheBook*)c, n, rids, lens, tokens, want_counts, wants, vocab, short_max, dst, starts, summary);
 }
 int vxh_fill_decode(void* c, int n, int bucket, const int64_t* rids, const int* tokens, int vocab, int32_t* dst,
                     const int64_t* starts, int64_t* max_kv) {

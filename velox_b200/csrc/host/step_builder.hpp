@@ -2,12 +2,14 @@
 // buffer of 32-bit words whose sections start at the given offsets:
 //   0 token_ids [tokens]      1 positions [tokens]     2 seq_of_token [tokens]
 //   3 cu_seqlens [requests+1] 4 kv_offsets [requests]  5 state_slots [requests]
-//   6 wanted_rows [wanted]    7 single_rows [requests]  8 portion_seqs [requests]
+//   6 wanted_rows [wanted]    7 single_rows [tokens]    8 portion_seqs [requests]
 //   then per group: block_table [requests, max_blocks], slot_mapping [tokens] (page *
 //   page_size + offset of each new position).
-// single_rows lists the token rows of the requests that bring exactly one token,
-// portion_seqs the requests (rows of the step) that bring more: a mixed step hands
-// the first to the decode attention and the second to the prompt attention.
+// single_rows lists the token rows of the requests that bring at most `short_max`
+// tokens (1: exactly the decoded tokens), portion_seqs the requests (rows of the
+// step) that bring more: a mixed step hands the first, token by token, to the decode
+// attention (every token a query of its own over its request's keys, the range of keys
+// cut into pieces that many warps share) and the second to the prompt attention.
 // The reference rebuilds and uploads block tables and offsets inside every layer
 // (src/paged/qwen3.rs:584-627); here the description is built once per step and
 // shared by all layers.
@@ -21,11 +23,12 @@ namespace vxh {
 // A general step: request i brings lens[i] tokens (concatenated in `tokens`) and
 // asks for want_counts[i] places among them (concatenated in `wants`).  The pages
 // must have been reserved.  summary: total tokens, wanted rows, longest portion,
-// largest number of keys any request will have, requests that bring one token, the
-// largest number of keys among those, requests that bring more, (unused).
+// largest number of keys any request will have, token rows of short requests, the
+// largest number of keys among those requests, requests that bring more than
+// `short_max` tokens, the longest short request.
 inline int build_step(CacheBook& book, int n, const int64_t* rids, const int* lens, const int* tokens,
-                      const int* want_counts, const int* wants, int vocab, int32_t* dst, const int64_t* starts,
-                      int64_t* summary) {
+                      const int* want_counts, const int* wants, int vocab, int short_max, int32_t* dst,
+                      const int64_t* starts, int64_t* summary) {
     const int S = book.page_size(), MB = book.max_blocks(), G = book.num_groups();
     int32_t* token_ids = dst + starts[0];
     int32_t* positions = dst + starts[1];
@@ -36,7 +39,8 @@ inline int build_step(CacheBook& book, int n, const int64_t* rids, const int* le
     int32_t* wanted = dst + starts[6];
     int32_t* single_rows = dst + starts[7];
     int32_t* portion_seqs = dst + starts[8];
-    int64_t row = 0, nw = 0, max_new = 0, max_kv = 0, n_single = 0, n_portions = 0, max_kv_single = 0;
+    int64_t row = 0, nw = 0, max_new = 0, max_kv = 0, n_single = 0, n_portions = 0, max_kv_single = 0, max_short = 0;
+    if (short_max < 1) short_max = 1;
     const int* tok = tokens;
     const int* want = wants;
     cu[0] = 0;
@@ -77,9 +81,10 @@ inline int build_step(CacheBook& book, int n, const int64_t* rids, const int* le
                 sm[j] = (int32_t)(page * S + pos % S);
             }
         }
-        if (k == 1) {
-            single_rows[n_single++] = (int32_t)row;
-            max_kv_single = std::max<int64_t>(max_kv_single, rc->length + 1);
+        if (k <= short_max) {
+            for (int j = 0; j < k; ++j) single_rows[n_single++] = (int32_t)(row + j);
+            max_kv_single = std::max<int64_t>(max_kv_single, rc->length + k);
+            max_short = std::max<int64_t>(max_short, k);
         } else {
             portion_seqs[n_portions++] = i;
         }
@@ -96,7 +101,7 @@ inline int build_step(CacheBook& book, int n, const int64_t* rids, const int* le
     summary[4] = n_single;
     summary[5] = max_kv_single;
     summary[6] = n_portions;
-    summary[7] = 0;
+    summary[7] = max_short;
     return OK;
 }
 

@@ -76,7 +76,7 @@ def _declare(lib) -> None:
         "vx_gemm_skinny": [P, P, P, P, I, I, I, I, I, I, I, I, I, I, P],
         "vx_paged_prefill_attention_tc": [P, I, I, P, P, I, P, I, P, P, P, P, I, F, I, I, I, I, I, I, I, P, P],
         "vx_paged_prefill_attention": [P, I, P, P, P, I, P, P, P, P, I, F, I, I, I, I, I, I, I, P],
-        "vx_paged_decode_attention": [P, I, P, P, P, I, P, P, P, P, I, P, I, F, I, I, I, I, I, I, I, P],
+        "vx_paged_decode_attention": [P, I, P, P, P, I, P, P, P, P, I, P, I, F, I, I, I, I, I, I, I, I, P],
         "vx_sample": [P, I, I, I, P, P, P, P, P],
     }
     lib.vx_set_pdl_mask.argtypes = [I]
@@ -295,10 +295,14 @@ def decode_attention_supported(dtype, head_dim: int, page_size: int, group: int)
 def paged_decode_attention(q: torch.Tensor, q_row_stride: int, k_pool, v_pool, block_table: torch.Tensor,
                            seq_of_token, positions, scale: float, window: int, num_heads: int, num_kv_heads: int,
                            head_dim: int, requests: int, max_kv: int, token_rows=None,
-                           out: Optional[torch.Tensor] = None, out_rows: Optional[int] = None) -> torch.Tensor:
-    """Attention of one query token per request over its pages (bfloat16), the
+                           out: Optional[torch.Tensor] = None, out_rows: Optional[int] = None,
+                           single_tokens: bool = True) -> torch.Tensor:
+    """Attention of one query token per entry over its request's pages (bfloat16), the
     key range split over blocks of DECODE_CHUNK_TILES * 16 keys.  `max_kv` bounds
-    every request's number of keys (it sizes the grid and the scratch)."""
+    every entry's number of keys (it sizes the grid and the scratch).  `token_rows`
+    picks the entries' rows; `single_tokens=False` says that some of them are tokens of
+    one request's portion (the kernel then waits for the step's cache writes before it
+    reads any key)."""
     _dev(q, k_pool, v_pool, block_table, seq_of_token, positions, token_rows)
     _need(q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and v_pool.dtype == torch.bfloat16,
           "paged_decode_attention: bfloat16 only")
@@ -316,7 +320,7 @@ def paged_decode_attention(q: torch.Tensor, q_row_stride: int, k_pool, v_pool, b
         _ptr(q), q_row_stride, _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1],
         _ptr(token_rows), _ptr(seq_of_token), _ptr(positions), _ptr(scratch), max_splits, _ptr(out),
         num_heads * head_dim, float(scale), int(window), requests, num_heads, num_kv_heads, head_dim,
-        k_pool.shape[2], DECODE_CHUNK_TILES, _stream()), "paged_decode_attention")
+        k_pool.shape[2], DECODE_CHUNK_TILES, 1 if single_tokens else 0, _stream()), "paged_decode_attention")
     return out
 
 

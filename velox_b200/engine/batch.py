@@ -43,7 +43,7 @@ class StepContext:
     kv_offsets: torch.Tensor     # int32 [requests], positions already cached before the step
     state_slots: torch.Tensor    # int32 [requests], the request's state slot
     wanted_rows: torch.Tensor    # int32 [wanted], token rows whose logits are asked for
-    single_rows: torch.Tensor    # int32 [requests]: token rows of the requests that bring one token (first n_single)
+    single_rows: torch.Tensor    # int32 [tokens]: token rows of the requests that bring few tokens (first n_single)
     portion_seqs: torch.Tensor   # int32 [requests]: the requests that bring more than one (first n_portions)
     groups: List[GroupContext]
     # host copies for decisions that need no device round trip
@@ -52,9 +52,10 @@ class StepContext:
     slots: List[int] = field(default_factory=list)
     max_new: int = 0
     max_kv: int = 0
-    n_single: int = 0        # requests that bring exactly one token
-    max_kv_single: int = 0   # most keys of any of those after the step
+    n_single: int = 0        # token rows of the requests that bring at most `short_max` tokens (1: decoded tokens)
+    max_kv_single: int = 0   # most keys of any of those requests after the step
     n_portions: int = 0      # requests that bring more
+    max_short: int = 0       # the longest of the short requests (1: every row of `single_rows` is its request's only one)
 
     @property
     def decode_only(self) -> bool:
@@ -68,7 +69,7 @@ SECTION_NAMES = ["token_ids", "positions", "seq_of_token", "cu_seqlens", "kv_off
 def _sections(n: int, total: int, wanted: int, n_groups: int, max_blocks: int):
     """Sizes and starts (in 32-bit words, every section on a 16-byte boundary) of the
     sections of a step's description, in the host library's order."""
-    sizes = [total, total, total, n + 1, n, n, wanted, n, n]
+    sizes = [total, total, total, n + 1, n, n, wanted, total, n]
     for _ in range(n_groups):
         sizes += [n * max_blocks, total]
     starts, cur = [], 0
@@ -78,12 +79,14 @@ def _sections(n: int, total: int, wanted: int, n_groups: int, max_blocks: int):
     return sizes, starts, cur
 
 
-def build_step_arrays(entries: Sequence[StepEntry], cache, vocab_size: Optional[int] = None, out=None):
+def build_step_arrays(entries: Sequence[StepEntry], cache, vocab_size: Optional[int] = None, out=None,
+                      short_max: int = 1):
     """The step's description after the cache has reserved the pages, written by the
     host library into `out` (a writable int32 numpy array, made if not given).
     Returns (out, sizes, starts, summary) with summary = (tokens, wanted rows,
-    longest portion, most keys of any request after the step, requests that bring
-    one token, most keys among those, requests that bring more, unused)."""
+    longest portion, most keys of any request after the step, token rows of the
+    requests that bring at most `short_max` tokens, most keys among those requests,
+    requests that bring more, the longest short request)."""
     from .. import native
 
     n = len(entries)
@@ -109,18 +112,19 @@ def build_step_arrays(entries: Sequence[StepEntry], cache, vocab_size: Optional[
     native.check(cache._lib.vxh_build_step(
         cache._book, n, rids, native.int_array(lens), tokens.ctypes.data_as(ctypes.POINTER(ctypes.c_int)),
         native.int_array(len(e.want) for e in entries), native.int_array(w for e in entries for w in e.want),
-        -1 if vocab_size is None else int(vocab_size), out.ctypes.data_as(ctypes.c_void_p),
+        -1 if vocab_size is None else int(vocab_size), int(short_max), out.ctypes.data_as(ctypes.c_void_p),
         native.int64_array(starts), summary))
     return out, sizes, starts, [int(x) for x in summary]
 
 
-def build_step_context(entries: Sequence[StepEntry], cache, device, vocab_size: Optional[int] = None) -> StepContext:
+def build_step_context(entries: Sequence[StepEntry], cache, device, vocab_size: Optional[int] = None,
+                       short_max: int = 1) -> StepContext:
     """Has the step's description written into one pinned buffer and copies it once."""
     n = len(entries)
     lens = [len(e.tokens) for e in entries]
     _, _, words = _sections(n, sum(lens), sum(len(e.want) for e in entries), len(cache.groups), cache.max_blocks)
     host = torch.empty(max(words, 4), dtype=torch.int32, pin_memory=(torch.device(device).type == "cuda"))
-    hv, sizes, starts, summary = build_step_arrays(entries, cache, vocab_size, out=host.numpy())
+    hv, sizes, starts, summary = build_step_arrays(entries, cache, vocab_size, out=host.numpy(), short_max=short_max)
     dev = host.to(device, non_blocking=True)
     views = [dev[st:st + s] for st, s in zip(starts, sizes)]
     named = dict(zip(SECTION_NAMES, views[:len(SECTION_NAMES)]))
@@ -131,4 +135,4 @@ def build_step_context(entries: Sequence[StepEntry], cache, device, vocab_size: 
     return StepContext(
         n_tokens=summary[0], n_seqs=n, groups=gctx, new_lens=lens, offsets=offs,
         slots=[int(x) for x in hv[starts[5]:starts[5] + n]], max_new=summary[2], max_kv=summary[3],
-        n_single=summary[4], max_kv_single=summary[5], n_portions=summary[6], **named)
+        n_single=summary[4], max_kv_single=summary[5], n_portions=summary[6], max_short=summary[7], **named)

@@ -7,6 +7,13 @@ description (token ids, positions, block tables, slot mapping, sampling
 parameters), copies it into the graph's fixed device buffer, and launches the
 graph; embedding, all layers, the head and the sampling kernel run from there.
 
+Small mixed steps (a short prompt portion beside decoded tokens, as a fixed chunk size
+and continuous batching produce them) are bound by the host, not the device: some ten
+launches a layer from Python take longer than their kernels run.  A step whose shape
+(tokens, requests, wanted rows, how many rows go to which attention kernel, longest
+portion, key-range buckets) has come up a few times is therefore captured too, at its
+exact shape, and replayed when that shape comes again (`MIXED_*` below).
+
 Padding: a batch is padded up to its bucket with rows that read page 0 at
 position 0 and write nothing (slot -1); their tokens are dropped.  Models with
 per-request state are never padded (a padded row would touch a real slot) and
@@ -26,7 +33,7 @@ import torch
 
 from .. import native
 from ..csrc import ops
-from .batch import SECTION_NAMES, GroupContext, StepContext, StepEntry
+from .batch import SECTION_NAMES, GroupContext, StepContext, StepEntry, _sections, build_step_arrays
 
 SPLIT_KEYS = ops.DECODE_CHUNK_TILES * 16
 
@@ -91,7 +98,7 @@ class _Graph:
         self.d_temp, self.d_top_p, self.d_uniform = f
         self.ctx = StepContext(n_tokens=B, n_seqs=B, groups=groups, new_lens=[1] * B, offsets=[0] * B,
                                slots=[0] * B, max_new=1, max_kv=max_kv, n_single=B, max_kv_single=max_kv,
-                               n_portions=0, **dict(zip(names, v[:F])))
+                               n_portions=0, max_short=1, **dict(zip(names, v[:F])))
         # constant sections
         self.h["seq_of_token"][:] = np.arange(B)
         self.h["cu_seqlens"][:] = np.arange(B + 1)
@@ -129,6 +136,52 @@ class _Graph:
         self.ids = ops.sample(self.logits, self.d_temp, self.d_top_p, self.d_uniform)
 
 
+MIXED_MAX_TOKENS = 256   # larger steps keep the device busy longer than the host needs to launch them
+MIXED_SEEN_BEFORE = 2    # a shape is captured when it comes up for the third time
+MIXED_MAX_GRAPHS = 64    # (each holds its activations: tens of MB at the real widths)
+
+
+class _MixedGraph:
+    """A captured step of one exact shape.  Its description lives in a fixed device buffer
+    that every replay fills; sampling stays outside (it takes host-made parameters)."""
+
+    def __init__(self, runner, sig):
+        cache, device = runner.cache, runner.device
+        (total, n, wanted, n_single, n_portions, max_new, max_short, max_kv, max_kv_single) = sig
+        self.sig = sig
+        MB, G = cache.max_blocks, len(cache.groups)
+        self.sizes, self.starts, words = _sections(n, total, wanted, G, MB)
+        self.host = torch.zeros(max(words, 4), dtype=torch.int32, pin_memory=True)
+        self.dev = torch.zeros(max(words, 4), dtype=torch.int32, device=device)
+        v = [self.dev[st:st + sz] for st, sz in zip(self.starts, self.sizes)]
+        F = len(SECTION_NAMES)
+        groups = [GroupContext(v[F + 2 * g].view(n, MB), v[F + 1 + 2 * g]) for g in range(G)]
+        # (the host-side lists are left empty: parts that read them are not graph-safe and never get here)
+        self.ctx = StepContext(n_tokens=total, n_seqs=n, groups=groups, max_new=max_new, max_kv=max_kv,
+                               n_single=n_single, max_kv_single=max_kv_single, n_portions=n_portions,
+                               max_short=max_short, **dict(zip(SECTION_NAMES, v[:F])))
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits = self.ids = None
+        self.launches = self.bounded_wait_launches = 0
+        self.copied: Optional[torch.cuda.Event] = None
+
+    def fill(self, entries, cache, vocab_size, short_max) -> List[int]:
+        if self.copied is not None:
+            self.copied.synchronize()
+        _, _, _, summary = build_step_arrays(entries, cache, vocab_size, out=self.host.numpy(), short_max=short_max)
+        self.dev.copy_(self.host, non_blocking=True)
+        if self.copied is None:
+            self.copied = torch.cuda.Event()
+        self.copied.record()
+        return summary
+
+    def run_model(self, runner) -> None:
+        self.logits = runner.run(self.ctx)
+        if self.logits is None:   # (nothing wanted: the capture still needs a tensor to hand around)
+            self.logits = torch.empty((0, runner.vocab_size), dtype=torch.float32, device=runner.device)
+        self.ids = self.logits   # (no sampling inside; `_capture` copies both)
+
+
 class DecodeGraphs:
     def __init__(self, runner):
         self.runner = weakref.proxy(runner)  # (the runner holds these graphs: no cycle, they end with it)
@@ -139,6 +192,8 @@ class DecodeGraphs:
         self.usable = all(getattr(p, "cuda_graph_safe", False) for p in runner.model.parts())
         self.cap = cache.slots.num_slots
         self._collected = False
+        self.mixed: Dict[Tuple, _MixedGraph] = {}
+        self._mixed_seen: Dict[Tuple, int] = {}
 
     def capture_all(self, max_batch: int, max_kv: int) -> int:
         """Captures, ahead of the first request, the graph of every (batch bucket,
@@ -189,7 +244,50 @@ class DecodeGraphs:
             ops.note_bounded_wait(g.bounded_wait_launches)
         return g.logits, g.ids
 
-    def _capture(self, g: _Graph) -> None:
+    # -- small mixed steps ---------------------------------------------------------
+    def mixed_signature(self, entries: Sequence[StepEntry], rids, short_max: int) -> Optional[Tuple]:
+        """The shape of a step that is no pure decode step, if it is small enough to be worth a graph
+        (else None): everything a part's choice of kernels and their grids may depend on."""
+        if not self.usable or self.has_state:
+            return None
+        lens = [len(e.tokens) for e in entries]
+        total = sum(lens)
+        if total > MIXED_MAX_TOKENS or not entries:
+            return None
+        cache, n = self.runner.cache, len(entries)
+        short = [i for i, k in enumerate(lens) if k <= short_max]
+        max_new = max(lens)
+        longest = int(native.check(cache._lib.vxh_cache_max_length(cache._book, n, rids)))
+        max_kv = keys_bucket(longest + max_new)
+        max_kv_single = 0
+        if short:
+            sub = native.int64_array(rids[i] for i in short)
+            max_kv_single = keys_bucket(int(native.check(cache._lib.vxh_cache_max_length(cache._book, len(short), sub)))
+                                        + max(lens[i] for i in short))
+        return (total, n, sum(len(e.want) for e in entries), sum(lens[i] for i in short), n - len(short), max_new,
+                max(lens[i] for i in short) if short else 0, max_kv, max_kv_single)
+
+    def mixed_step(self, sig: Tuple, entries: Sequence[StepEntry], short_max: int):
+        """Runs a step of shape `sig` from its graph if it has one; captures one if the shape has come up
+        often enough; returns the logits at the wanted rows, or NotImplemented for the eager path."""
+        g = self.mixed.get(sig)
+        if g is None:
+            seen = self._mixed_seen.get(sig, 0)
+            if seen < MIXED_SEEN_BEFORE or len(self.mixed) >= MIXED_MAX_GRAPHS:
+                self._mixed_seen[sig] = seen + 1
+                return NotImplemented
+            g = self.mixed[sig] = _MixedGraph(self.runner, sig)
+        g.fill(entries, self.runner.cache, self.runner.vocab_size, short_max)
+        if g.graph is None:
+            self._capture(g)   # (its eager run is this step)
+        else:
+            g.graph.replay()
+            ops.add_launches(g.launches)
+            if g.bounded_wait_launches:
+                ops.note_bounded_wait(g.bounded_wait_launches)
+        return g.logits if sig[2] else None
+
+    def _capture(self, g) -> None:
         # once eagerly (first-use set-up of kernels and libraries happens outside the capture) ...
         torch.cuda.synchronize()
         side = torch.cuda.Stream()

@@ -27,6 +27,9 @@ class ModelRunner:
     def __init__(self, model, cache: CacheManager, device, vocab_size: int, cuda_graphs: bool = False):
         self.model, self.cache, self.device, self.vocab_size = model, cache, torch.device(device), int(vocab_size)
         self.steps = 0
+        # requests that bring at most so many tokens are listed token by token for the mixers (a mixer
+        # may then treat each token as a decoded one): the largest wish among the model's parts
+        self.short_max = max([1] + [int(getattr(p, "short_rows_up_to", 1)) for p in model.parts()])
         self.graphs = None
         if cuda_graphs:
             from .graphs import DecodeGraphs
@@ -100,8 +103,16 @@ class ModelRunner:
                 idx = torch.tensor(rows, dtype=torch.long, device=self.device)
                 logits, ids = all_logits[idx], all_ids[idx]
         else:
-            ctx = build_step_context(entries, self.cache, self.device, self.vocab_size)
-            logits = self.run(ctx)
+            logits, sig = NotImplemented, None
+            if self.graphs is not None:
+                sig = self.graphs.mixed_signature(entries, rids, self.short_max)
+            if sig is not None:
+                # a small mixed step: from its graph, if this shape has one by now (the step's
+                # description is checked by the host library as it is written, as in the eager path)
+                logits = self.graphs.mixed_step(sig, entries, self.short_max)
+            if logits is NotImplemented:
+                ctx = build_step_context(entries, self.cache, self.device, self.vocab_size, self.short_max)
+                logits = self.run(ctx)
             if sample and logits is not None:
                 t = torch.tensor([sampling[0], sampling[1], sampling[2]], dtype=torch.float32).to(self.device, non_blocking=True)
                 ids = ops.sample(logits, t[0], t[1], t[2]) if any(x > 0 for x in sampling[0]) else ops.sample(logits)

@@ -78,7 +78,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "vxh_cache_commit": (I, [P, c_int64, L]), "vxh_cache_release": (I, [P, c_int64]),
         "vxh_cache_check": (I, [P]), "vxh_cache_reserve_many": (I, [P, I, PI64, PI]),
         "vxh_cache_commit_many": (I, [P, I, PI64, PI]),
-        "vxh_build_step": (I, [P, I, PI64, PI, PI, PI, PI, I, c_void_p, PI64, PI64]),
+        "vxh_build_step": (I, [P, I, PI64, PI, PI, PI, PI, I, I, c_void_p, PI64, PI64]),
         "vxh_fill_decode": (I, [P, I, I, PI64, PI, I, c_void_p, PI64, PI64]),
         "vxh_sched_create": (P, [P, I, L, L, L]), "vxh_sched_destroy": (None, [P]),
         "vxh_sched_max_model_len": (L, [P]), "vxh_sched_submit": (L, [P, PI, L, L, I, PI, I, PI, PI, I]),

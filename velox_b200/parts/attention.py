@@ -31,6 +31,13 @@ TC_PREFILL_MIN_TOKENS = 32   # longest portion of a step from which the tcgen05 
 
 
 class PagedAttention(Mixer):
+    # Requests that bring fewer tokens than the tcgen05 kernel's shortest portion are listed token by
+    # token in the step's description (`single_rows`): every token goes to the decode kernel as a query
+    # of its own, its request's keys cut into pieces of 256 that many warps share.  A prompt kernel gives
+    # such a portion one block per kv head that walks ALL the request's keys alone: 16 tokens on top of
+    # 4,000 cached keys took 300 us a layer that way.
+    short_rows_up_to = TC_PREFILL_MIN_TOKENS - 1
+
     @property
     def cuda_graph_safe(self) -> bool:
         # reads nothing of a step but device tensors and sizes fixed per graph; a position
@@ -136,14 +143,17 @@ class PagedAttention(Mixer):
             prefill = ops.paged_prefill_attention_tc if use_tc else ops.paged_prefill_attention  # tcgen05 | mma.sync
             out, seqs, n = None, None, ctx.n_seqs
             if ctx.n_single and ops.decode_attention_supported(qkv.dtype, D, page, H // Hk):
-                # A mixed step: the requests that bring one token go to the decode kernel (a
-                # warp per 256 keys, every key read once), not into a query tile of their own;
-                # the kernels write disjoint rows.  A decoded token's result is then the same
-                # bits whether or not prompt portions ride in its step.
+                # A mixed step: the tokens of requests that bring one token, or a few, go to the
+                # decode kernel (a warp per 256 keys), not into a query tile of their own; the
+                # kernels write disjoint rows.  A decoded token's result is then the same bits
+                # whether or not prompt portions ride in its step.
                 out = torch.empty((qkv.shape[0], H * D), dtype=qkv.dtype, device=qkv.device)
                 ops.paged_decode_attention(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
                                            ctx.seq_of_token, ctx.positions, self.scale, self.window, H, Hk, D,
-                                           ctx.n_single, ctx.max_kv_single, token_rows=ctx.single_rows, out=out)
+                                           ctx.n_single, ctx.max_kv_single, token_rows=ctx.single_rows, out=out,
+                                           single_tokens=ctx.max_short <= 1)
+                if ctx.n_portions == 0:
+                    return out
                 seqs, n = ctx.portion_seqs, ctx.n_portions
             return prefill(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table, ctx.cu_seqlens,
                            ctx.kv_offsets, self.scale, self.window, H, Hk, D, n, ctx.max_new, qkv.shape[0],
