@@ -607,3 +607,54 @@ def test_a_window_ends_where_it_should(kernel, window, length):
         near = torch.allclose(out[-1, :D].float(), value, atol=2e-2)
         assert near == inside, "%s: the key at %d (query at %d, window %d) %s" % (
             kernel, j, p, window, "was not seen" if inside else "was seen")
+
+
+# ----------------------------------------------------------------------------
+TC_SPLIT_CASES = [
+    ([(3000, 64)], 8, 2, 128, 16, 0),                              # two query tiles on 24 key tiles: cut into 6 runs
+    ([(1500, 40), (20, 33), (2500, 35), (0, 70)], 8, 2, 128, 16, 0),  # cut (3 runs), whole, cut (5 runs), whole, in one launch
+    ([(2000, 100)], 32, 8, 128, 16, 0),                            # the flagship's head layout: 4 query tiles x 8 kv heads
+    ([(4000, 50), (900, 60)], 4, 1, 128, 32, 600),                 # a window: the runs' tiles start far from key 0
+    ([(1021, 130)], 4, 4, 128, 16, 0),                             # no sharing; the last tokens see one key tile more than the first
+]
+
+
+@pytest.mark.parametrize("case", range(len(TC_SPLIT_CASES)))
+def test_paged_prefill_attention_tc_cut_into_runs(case):
+    """A short portion on top of many cached keys: its key tiles are cut into runs that several blocks take,
+    and a second kernel adds the runs."""
+    seqs, H, Hk, D, S, window = TC_SPLIT_CASES[case]
+    q, kp, vp, bt, sot, pos, want = paged_case(torch.bfloat16, seqs, H, Hk, D, S, window, seed=120 + case)
+    cu, offs = prefill_inputs(seqs)
+    max_kv = max(o + n for o, n in seqs)
+    out = ops().paged_prefill_attention_tc(q, H * D, kp, vp, bt, cu, offs, 1 / math.sqrt(D), window, H, Hk, D,
+                                           len(seqs), max(n for _, n in seqs), q.shape[0], max_kv=max_kv)
+    ops().check_device_errors()
+    close(out, want, torch.bfloat16, what="tcgen05 prefill attention in runs, case %d" % case)
+    whole = ops().paged_prefill_attention_tc(q, H * D, kp, vp, bt, cu, offs, 1 / math.sqrt(D), window, H, Hk, D,
+                                             len(seqs), max(n for _, n in seqs), q.shape[0])
+    assert not torch.equal(out, whole), "nothing was cut: the case lost its point"
+    assert (out.float() - whole.float()).abs().max() < 2e-2
+    # a request's result does not depend on what else is in the launch
+    if len(seqs) > 1:
+        alone_q, kp1, vp1, bt1, _, _, _ = paged_case(torch.bfloat16, seqs[:1], H, Hk, D, S, window, seed=120 + case)
+        cu1, offs1 = prefill_inputs(seqs[:1])
+        alone = ops().paged_prefill_attention_tc(alone_q, H * D, kp1, vp1, bt1, cu1, offs1, 1 / math.sqrt(D), window, H, Hk,
+                                                 D, 1, seqs[0][1], alone_q.shape[0], max_kv=max_kv)
+        assert torch.equal(alone, out[:seqs[0][1]])
+
+
+@pytest.mark.parametrize("far", [0, 500, 1023, 1024, 2900])
+def test_prefill_attention_tc_in_runs_finds_one_far_key(far):
+    H, Hk, D, S = 8, 2, 128, 16
+    seqs = [(2960, 40)]
+    q, kp, vp, bt, sot, pos, want = paged_case(torch.bfloat16, seqs, H, Hk, D, S, 0, seed=18, spike=far)
+    cu, offs = prefill_inputs(seqs)
+    out = ops().paged_prefill_attention_tc(q, H * D, kp, vp, bt, cu, offs, 1 / math.sqrt(D), 0, H, Hk, D, 1, 40, 40, max_kv=3000)
+    ops().check_device_errors()
+    close(out, want, torch.bfloat16)
+    page, off = int(bt[0, far // S]), far % S
+    value = vp[page, 0, off].float().cpu().numpy()
+    scale = np.abs(value).max()
+    assert np.abs(want[-1, :D] - value).max() < 0.03 * scale, "the far key does not decide the plain answer: the case lost its point"
+    assert np.abs(f64(out)[-1, :D] - value).max() < 0.04 * scale

@@ -165,16 +165,19 @@ def test_a_long_prompt_in_one_step_and_in_two(model_folders, tmp_path, dtype):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_a_context_of_4000_tokens(model_folders, tmp_path, dtype):
-    """A prompt of 3,950 tokens in portions of 2,048 and 1,902 (the second on top of
-    2,048 cached positions), then 50 tokens one by one beside a short request:
-    sixteen pieces of keys per decoded token, a window of 200 far from the start."""
+    """A prompt of 3,950 tokens in portions of 2,048, 1,802 (on top of 2,048 cached
+    positions) and 100 (on top of 3,850: few query tiles and thirty key tiles, which
+    the prefill attention cuts into runs, in the windowed layers runs without keys
+    among them), then 50 tokens one by one beside a short request: sixteen pieces of
+    keys per decoded token, a window of 200 far from the start."""
     folder = model_folders["tiny_d"]
     cfg, w = P.load_model_folder(folder)
     long_, short = random_tokens(cfg["vocab_size"], 4000, 41), random_tokens(cfg["vocab_size"], 60, 42)
     plain = {"L": Oracle(cfg, w, long_), "s": Oracle(cfg, w, short)}
     tr = Trace()
     tr.add([("L", long_[:2048], [0, 1000, 2047], 0)], plain=plain)
-    tr.add([("L", long_[2048:3950], [0, 1, 951, 1901], 2048), ("s", short[:10], [9], 0)], plain=plain)
+    tr.add([("L", long_[2048:3850], [0, 1, 951, 1801], 2048)], plain=plain)
+    tr.add([("L", long_[3850:3950], [0, 1, 31, 32, 64, 99], 3850), ("s", short[:10], [9], 0)], plain=plain)
     for k in range(50):
         tr.add([("L", [long_[3950 + k]], [0], 3950 + k), ("s", [short[10 + k]], [0], 10 + k)],
                end=["L", "s"] if k == 49 else [], plain=plain)

@@ -182,6 +182,22 @@ __device__ __forceinline__ bool pt_softmax_barrier_and(bool ok) {
     return all != 0;
 }
 
+// A short portion on top of many cached keys has few query tiles (a 64-token portion at 4 query heads
+// per kv head: two) but many key tiles for each to walk alone.  Its key tiles are then cut into `splits`
+// runs that as many blocks take; each writes its unnormalised output and (reference, sum) per row, and
+// the join kernel below adds the runs in order.  The number of runs depends on the request's own portion
+// and keys only, never on what else is in the step.
+__device__ __host__ __forceinline__ int pt_splits_of(int n_new, int kv_len, int toks_per_tile, int Hk, int max_splits,
+                                                     int sms) {
+    const int q_tiles = (n_new + toks_per_tile - 1) / toks_per_tile;
+    const int key_tiles = (kv_len + PT_KEYS - 1) / PT_KEYS;
+    const int fill = sms / (q_tiles * Hk);   // no more runs than give every SM one block: a second wave would wait for the first
+    if (fill < 2 || key_tiles < 8) return 1; // blocks enough for the SMs already, or nothing to cut
+    int s = key_tiles / 4;                   // four key tiles a run at least
+    s = s < fill ? s : fill;
+    return s < max_splits ? s : max_splits;
+}
+
 // barriers of a block
 struct PtBarriers {
     unsigned long long q_full;
@@ -196,6 +212,7 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
                                   const int* __restrict__ kv_offsets, const int* __restrict__ seq_list,
                                   bf16* __restrict__ out, int out_row_stride,
                                   float scale_log2, int window, int H, int Hk, int S, int share_log2,
+                                  float* __restrict__ part_o, float* __restrict__ part_ml, int max_splits, int sms,
                                   int* __restrict__ error) {
     extern __shared__ unsigned char pt_smem_raw[];
     __shared__ __align__(8) PtBarriers bars;
@@ -211,7 +228,8 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // the longest tiles (the last tokens of a prompt) are handed out first
-    const int qt = gridDim.x - 1 - blockIdx.x, hk = blockIdx.y;
+    const int split = (int)blockIdx.x % max_splits;
+    const int qt = (int)gridDim.x / max_splits - 1 - (int)blockIdx.x / max_splits, hk = blockIdx.y;
     const int seq = seq_list ? seq_list[blockIdx.z] : (int)blockIdx.z;
     const int share = 1 << share_log2;
     const int toks_per_tile = PT_ROWS >> share_log2;
@@ -220,12 +238,33 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
     const int t0 = qt * toks_per_tile;
     if (t0 >= n_new) return;   // (before anything is allocated)
     const int off = kv_offsets[seq];
+    const int splits = pt_splits_of(n_new, off + n_new, toks_per_tile, Hk, max_splits, sms);
+    if (split >= splits) return;
     const int* bt = block_table + (size_t)seq * max_blocks;
     const int toks_live = min(toks_per_tile, n_new - t0);
     const int kv_hi = off + t0 + toks_live;               // one past the last visible key of the tile
     const int kv_lo = window > 0 ? max(0, off + t0 + 1 - window) : 0;
-    const int tile_lo = kv_lo / PT_KEYS, tile_hi = (kv_hi + PT_KEYS - 1) / PT_KEYS;
-    const int ntiles = tile_hi - tile_lo;
+    int tile_lo = kv_lo / PT_KEYS;
+    const int tile_hi = (kv_hi + PT_KEYS - 1) / PT_KEYS;
+    int ntiles = tile_hi - tile_lo;
+    if (splits > 1) {
+        // this block's run of the tile's key tiles
+        const int per = (ntiles + splits - 1) / splits;
+        tile_lo += split * per;
+        ntiles = min(per, tile_hi - tile_lo);
+        if (ntiles <= 0) {
+            // nothing in this run for this query tile (early tokens of a portion see fewer keys): it weighs nothing
+            for (int r = threadIdx.x; r < PT_ROWS; r += PT_THREADS) {
+                const int tok = r & (toks_per_tile - 1), hi = r >> (7 - share_log2);
+                if (tok < toks_live) {
+                    const size_t p = ((size_t)(row_base + t0 + tok) * H + (hk * share + hi)) * max_splits + split;
+                    part_ml[2 * p] = -INFINITY;
+                    part_ml[2 * p + 1] = 0.f;
+                }
+            }
+            return;
+        }
+    }
 
     if (threadIdx.x == 0) {
         pt_mbar_init(pt_smem_u32(&bars.q_full), 1);
@@ -493,12 +532,25 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
             if (!ok && lane == 0) { failed = 1; atomicExch(error, 13); }
         } else {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            const float inv = 1.f / ((row_sum[0][r] + row_sum[1][r]) + (row_sum[2][r] + row_sum[3][r]));
+            const float total = (row_sum[0][r] + row_sum[1][r]) + (row_sum[2][r] + row_sum[3][r]);
+            const float inv = 1.f / total;
             const bool live = tok < toks_live;
             bf16* dst = out + (size_t)(row_base + t0 + tok) * out_row_stride + (size_t)(hk * share + hi) * PT_D + hc * PT_PART;
             unsigned acc[32];
             pt_ld32(tmem_o + lane_addr + (unsigned)(hc * PT_PART), acc);
-            if (live) {
+            if (live && splits > 1) {
+                // one run of several: the unnormalised output and what it is relative to, for the join
+                const size_t p = ((size_t)(row_base + t0 + tok) * H + (hk * share + hi)) * max_splits + split;
+                float* po = part_o + p * PT_D + hc * PT_PART;
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    *reinterpret_cast<float4*>(po + j) = make_float4(__uint_as_float(acc[j]), __uint_as_float(acc[j + 1]),
+                                                                     __uint_as_float(acc[j + 2]), __uint_as_float(acc[j + 3]));
+                if (hc == 0) {
+                    part_ml[2 * p] = m_used;
+                    part_ml[2 * p + 1] = total;
+                }
+            } else if (live) {
 #pragma unroll
                 for (int j = 0; j < 32; j += 8) {
                     uint4 pk;
@@ -517,6 +569,53 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+// Adds the runs of the query tiles that were cut (see pt_splits_of): grid (32 x query tiles, kv head,
+// request), a block for four rows of a query tile, a warp per row, the runs in order.
+__global__ void __launch_bounds__(128)
+paged_prefill_join_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int max_splits, int sms,
+                          const int* __restrict__ cu_seqlens, const int* __restrict__ kv_offsets,
+                          const int* __restrict__ seq_list, bf16* __restrict__ out, int out_row_stride, int H, int Hk,
+                          int share_log2) {
+    pdl_wait();
+    pdl_trigger();
+    const int qt = blockIdx.x >> 5, hk = blockIdx.y;
+    const int seq = seq_list ? seq_list[blockIdx.z] : (int)blockIdx.z;
+    const int share = 1 << share_log2, toks_per_tile = PT_ROWS >> share_log2;
+    const int row_base = cu_seqlens[seq];
+    const int n_new = cu_seqlens[seq + 1] - row_base;
+    const int t0 = qt * toks_per_tile;
+    if (t0 >= n_new) return;
+    const int splits = pt_splits_of(n_new, kv_offsets[seq] + n_new, toks_per_tile, Hk, max_splits, sms);
+    if (splits <= 1) return;   // written whole by the kernel above
+    const int toks_live = min(toks_per_tile, n_new - t0);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    {
+        const int r = ((int)(blockIdx.x & 31) << 2) + warp;
+        const int tok = r & (toks_per_tile - 1), hi = r >> (7 - share_log2);
+        if (tok >= toks_live) return;
+        const int row = row_base + t0 + tok, h = hk * share + hi;
+        const size_t p0 = ((size_t)row * H + h) * max_splits;
+        float M = -INFINITY;
+        for (int s2 = 0; s2 < splits; ++s2) M = fmaxf(M, part_ml[2 * (p0 + s2)]);
+        float L = 0.f;
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s2 = 0; s2 < splits; ++s2) {
+            const float m = part_ml[2 * (p0 + s2)];
+            if (m == -INFINITY) continue;   // (a run without a visible key: its output was not written)
+            const float wgt = exp2f(m - M);
+            L += wgt * part_ml[2 * (p0 + s2) + 1];
+            const float4 v = *reinterpret_cast<const float4*>(part_o + (p0 + s2) * PT_D + lane * 4);
+            o.x += wgt * v.x; o.y += wgt * v.y; o.z += wgt * v.z; o.w += wgt * v.w;
+        }
+        const float inv = 1.f / L;
+        __nv_bfloat162 a = __floats2bfloat162_rn(o.x * inv, o.y * inv), b = __floats2bfloat162_rn(o.z * inv, o.w * inv);
+        uint2 pk;
+        pk.x = *reinterpret_cast<const unsigned*>(&a);
+        pk.y = *reinterpret_cast<const unsigned*>(&b);
+        *reinterpret_cast<uint2*>(out + (size_t)row * out_row_stride + (size_t)h * PT_D + lane * 4) = pk;
     }
 }
 
@@ -554,12 +653,16 @@ static bool pt_make_map(CUtensorMap* map, const void* base, long long rows, int 
 // in all, row stride q_row_stride, query head h at columns h * 128) at positions
 // kv_offsets[i] onward; pools are [pages, Hk, S, 128].  `error`: a device int a block
 // sets if one of its bounded waits runs out.  With `seq_list` (device, `requests`
-// entries) only the requests it names are worked on.
+// entries) only the requests it names are worked on.  `max_splits` > 1 lets requests
+// with few query tiles and many keys cut their key tiles into up to so many runs
+// (pt_splits_of decides per request); `scratch` then holds tokens * H * max_splits *
+// (D + 2) floats.
 extern "C" int vx_paged_prefill_attention_tc(const void* q, int q_row_stride, int tokens, const void* k_pool,
                                              const void* v_pool, int pages, const int* block_table, int max_blocks,
                                              const int* cu_seqlens, const int* kv_offsets, const int* seq_list, void* out,
                                              int out_row_stride, float scale, int window, int requests, int max_new,
-                                             int H, int Hk, int D, int S, int* error, cudaStream_t stream) {
+                                             int H, int Hk, int D, int S, float* scratch, int max_splits, int* error,
+                                             cudaStream_t stream) {
     if (requests <= 0 || max_new <= 0 || tokens <= 0) return VX_OK;
     if (D != PT_D || H <= 0 || Hk <= 0 || H % Hk || S <= 0 || S % 16 || window < 0 || !error) return VX_ERR_SHAPE;
     const int G = H / Hk;
@@ -568,6 +671,7 @@ extern "C" int vx_paged_prefill_attention_tc(const void* q, int q_row_stride, in
         ((((uintptr_t)k_pool) | ((uintptr_t)v_pool)) & 15))
         return VX_ERR_ALIGN;
     if (Hk > 65535 || requests > 65535) return VX_ERR_LIMIT;
+    if (max_splits < 1 || max_splits > 64 || (max_splits > 1 && !scratch)) return VX_ERR_SHAPE;
     int share_log2 = 0;
     while ((1 << share_log2) < G) ++share_log2;
     const int toks_per_tile = PT_ROWS >> share_log2;
@@ -579,10 +683,22 @@ extern "C" int vx_paged_prefill_attention_tc(const void* q, int q_row_stride, in
     const size_t smem = 5 * (size_t)PT_TILE_BYTES + 1024;
     static bool configured[VX_MAX_DEVICES];
     if (int rc = vx_configure_smem(paged_prefill_attention_tc_kernel, smem, configured)) return rc;
-    dim3 grid((max_new + toks_per_tile - 1) / toks_per_tile, Hk, requests);
+    const int q_tiles = (max_new + toks_per_tile - 1) / toks_per_tile;
+    static int sm_counts[VX_MAX_DEVICES];
+    const int sms = vx_sm_count(sm_counts);
+    // scratch of the cut query tiles: outputs [tokens, H, max_splits, D], then (reference, sum) [tokens, H, max_splits, 2]
+    float* part_o = scratch;
+    float* part_ml = scratch ? scratch + (size_t)tokens * H * max_splits * D : nullptr;
+    dim3 grid(q_tiles * max_splits, Hk, requests);
     VX_LAUNCH_K(VX_K_ATTENTION, paged_prefill_attention_tc_kernel, grid, PT_THREADS, smem, stream, mq, mk, mv,
                 block_table, max_blocks, cu_seqlens, kv_offsets, seq_list, (bf16*)out, out_row_stride, scale * PT_LOG2E, window, H,
-                Hk, S, share_log2, error);
+                Hk, S, share_log2, part_o, part_ml, max_splits, sms, error);
     VX_LAUNCH_CHECK();
+    if (max_splits > 1) {
+        dim3 jgrid(q_tiles * 32, Hk, requests);
+        VX_LAUNCH_K(VX_K_JOIN, paged_prefill_join_kernel, jgrid, 128, 0, stream, (const float*)part_o, (const float*)part_ml,
+                    max_splits, sms, cu_seqlens, kv_offsets, seq_list, (bf16*)out, out_row_stride, H, Hk, share_log2);
+        VX_LAUNCH_CHECK();
+    }
     return VX_OK;
 }

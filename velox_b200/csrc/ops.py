@@ -74,7 +74,7 @@ def _declare(lib) -> None:
         "vx_gemm_nt_simt": [P, P, P, P, I, I, I, I, I, I, I, I, P],
         "vx_gemm_tcgen05": [P, P, P, P, I, I, I, I, I, I, I, I, I, P, P],
         "vx_gemm_skinny": [P, P, P, P, I, I, I, I, I, I, I, I, I, I, P],
-        "vx_paged_prefill_attention_tc": [P, I, I, P, P, I, P, I, P, P, P, P, I, F, I, I, I, I, I, I, I, P, P],
+        "vx_paged_prefill_attention_tc": [P, I, I, P, P, I, P, I, P, P, P, P, I, F, I, I, I, I, I, I, I, P, I, P, P],
         "vx_paged_prefill_attention": [P, I, P, P, P, I, P, P, P, P, I, F, I, I, I, I, I, I, I, P],
         "vx_paged_decode_attention": [P, I, P, P, P, I, P, P, P, P, I, P, I, F, I, I, I, I, I, I, I, I, P],
         "vx_sample": [P, I, I, I, P, P, P, P, P],
@@ -275,12 +275,13 @@ DECODE_CHUNK_TILES = 16  # keys per piece of the split decode kernel: 16 tiles o
 _WORKSPACE = {}
 
 
-def workspace(device, nfloats: int) -> torch.Tensor:
-    """A float32 scratch buffer of at least `nfloats` on `device`, kept between calls.
-    While a CUDA graph is being captured the buffer is the graph's own."""
+def workspace(device, nfloats: int, which: str = "decode") -> torch.Tensor:
+    """A float32 scratch buffer of at least `nfloats` on `device`, kept between calls
+    (one per use: `which`).  While a CUDA graph is being captured the buffer is the
+    graph's own."""
     if torch.cuda.is_current_stream_capturing():
         return torch.empty(max(nfloats, 1), dtype=torch.float32, device=device)
-    key = str(device)
+    key = (str(device), which)
     buf = _WORKSPACE.get(key)
     if buf is None or buf.numel() < nfloats:
         buf = torch.empty(max(nfloats, 1 << 16), dtype=torch.float32, device=device)
@@ -351,6 +352,9 @@ def paged_prefill_attention(q: torch.Tensor, q_row_stride: int, k_pool, v_pool, 
     return out
 
 
+PREFILL_MAX_SPLITS = 16
+
+
 def prefill_attention_tc_supported(dtype, head_dim: int, page_size: int, group: int) -> bool:
     return dtype == torch.bfloat16 and head_dim == 128 and page_size % 16 == 0 and group in (1, 2, 4, 8)
 
@@ -358,9 +362,11 @@ def prefill_attention_tc_supported(dtype, head_dim: int, page_size: int, group: 
 def paged_prefill_attention_tc(q: torch.Tensor, q_row_stride: int, k_pool, v_pool, block_table: torch.Tensor,
                                cu_seqlens, kv_offsets, scale: float, window: int, num_heads: int, num_kv_heads: int,
                                head_dim: int, requests: int, max_new: int, tokens: int, seq_list=None,
-                               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                               out: Optional[torch.Tensor] = None, max_kv: int = 0) -> torch.Tensor:
     """The same as `paged_prefill_attention` on the tcgen05 tensor cores (head size
-    128, accumulators in tensor memory, operands by TMA)."""
+    128, accumulators in tensor memory, operands by TMA).  `max_kv` (a bound on any
+    request's keys after the step) lets short portions on top of many keys be cut into
+    runs of key tiles that several blocks share; 0: never."""
     _dev(q, k_pool, v_pool, block_table, cu_seqlens, kv_offsets, seq_list, out)
     _need(q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and v_pool.dtype == torch.bfloat16,
           "paged_prefill_attention_tc: bfloat16 only")
@@ -369,11 +375,19 @@ def paged_prefill_attention_tc(q: torch.Tensor, q_row_stride: int, k_pool, v_poo
     _need(k_pool.is_contiguous() and v_pool.is_contiguous(), "paged_prefill_attention_tc: contiguous pools")
     if out is None:
         out = torch.empty((tokens, num_heads * head_dim), dtype=q.dtype, device=q.device)
+    # runs of key tiles: up to a quarter of the longest request's key tiles, 16 at most; only a step whose
+    # portions are short can have a request that is cut (a long portion has query tiles enough)
+    max_splits, scratch = 1, None
+    toks_per_tile = 128 // (num_heads // num_kv_heads)
+    sms = _sm_count(q.device)
+    if max_kv >= 8 * 128 and 2 * -(-max_new // toks_per_tile) * num_kv_heads <= sms:
+        max_splits = max(1, min(PREFILL_MAX_SPLITS, -(-max_kv // 128) // 4, sms // num_kv_heads))
+        scratch = workspace(q.device, tokens * num_heads * max_splits * (head_dim + 2), which="prefill")
     _check(library().vx_paged_prefill_attention_tc(
         _ptr(q), q_row_stride, tokens, _ptr(k_pool), _ptr(v_pool), k_pool.shape[0], _ptr(block_table),
         block_table.shape[1], _ptr(cu_seqlens), _ptr(kv_offsets), _ptr(seq_list), _ptr(out), num_heads * head_dim, float(scale),
         int(window), requests, int(max_new), num_heads, num_kv_heads, head_dim, k_pool.shape[2],
-        _ptr(_error_word(q.device)), _stream()), "paged_prefill_attention_tc")
+        _ptr(scratch), max_splits, _ptr(_error_word(q.device)), _stream()), "paged_prefill_attention_tc")
     note_bounded_wait()
     return out
 
@@ -392,6 +406,16 @@ def gemm_nt_simt(a: torch.Tensor, w: torch.Tensor, bias=None, out_dtype: Optiona
     _check(library().vx_gemm_nt_simt(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), m, n, k, a.stride(0), w.stride(0), n,
                                      dtype_code(a.dtype), dtype_code(out_dtype), _stream()), "gemm_nt_simt")
     return out
+
+
+_SM_COUNTS = {}
+
+
+def _sm_count(device) -> int:
+    key = str(device)
+    if key not in _SM_COUNTS:
+        _SM_COUNTS[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _SM_COUNTS[key]
 
 
 _ERROR_WORDS = {}

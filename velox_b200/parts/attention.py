@@ -155,9 +155,10 @@ class PagedAttention(Mixer):
                 if ctx.n_portions == 0:
                     return out
                 seqs, n = ctx.portion_seqs, ctx.n_portions
+            more = dict(max_kv=ctx.max_kv) if use_tc else {}   # (short portions on many keys: cut into runs of key tiles)
             return prefill(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table, ctx.cu_seqlens,
                            ctx.kv_offsets, self.scale, self.window, H, Hk, D, n, ctx.max_new, qkv.shape[0],
-                           seq_list=seqs, out=out)
+                           seq_list=seqs, out=out, **more)
         return ops.paged_attention_generic(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
                                            ctx.seq_of_token, ctx.positions, self.scale, self.window, H, Hk, D,
                                            qkv.shape[0])
