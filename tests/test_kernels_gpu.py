@@ -503,11 +503,15 @@ TC_SHAPES = [(128, 256, 64), (128, 128, 128), (256, 512, 4096), (200, 384, 96), 
              (2048, 4096, 12288)]
 
 
-@pytest.mark.parametrize("wide", [True, False])
+TC_TILES = {"128x256": dict(wide=True), "128x128": dict(wide=False), "256x256 by a pair of blocks": dict(pair=True)}
+
+
+@pytest.mark.parametrize("tiles", list(TC_TILES))
 @pytest.mark.parametrize("M,N,K", TC_SHAPES)
-def test_gemm_tcgen05(M, N, K, wide):
+def test_gemm_tcgen05(M, N, K, tiles):
+    how = TC_TILES[tiles]
     a, w = rnd((M, K), torch.bfloat16, 30), rnd((N, K), torch.bfloat16, 31, 0.05)
-    got = ops().gemm_tcgen05(a, w, None, wide=wide)
+    got = ops().gemm_tcgen05(a, w, None, **how)
     ops().check_device_errors()
     if M * N * K <= 1 << 28:
         close(got, f64(a) @ f64(w).T, torch.bfloat16, what="tcgen05")
@@ -516,17 +520,17 @@ def test_gemm_tcgen05(M, N, K, wide):
     scale = max(1.0, float(ref.float().abs().max()))
     assert (got.float() - ref.float()).abs().max() <= 2e-2 * scale
     bias = rnd((N,), torch.float32, 32)
-    got_b = ops().gemm_tcgen05(a, w, bias, wide=wide)
+    got_b = ops().gemm_tcgen05(a, w, bias, **how)
     assert (got_b.float() - (ref.float() + bias)).abs().max() <= 2e-2 * scale + 2e-2
 
 
-@pytest.mark.parametrize("wide", [True, False])
+@pytest.mark.parametrize("tiles", list(TC_TILES))
 @pytest.mark.parametrize("M,I,K", [(128, 128, 64), (300, 200, 96), (2048, 12288, 4096)])
-def test_gemm_tcgen05_gated(M, I, K, wide):
+def test_gemm_tcgen05_gated(M, I, K, tiles):
     a = rnd((M, K), torch.bfloat16, 33)
     wg, wu = rnd((I, K), torch.bfloat16, 34, 0.05), rnd((I, K), torch.bfloat16, 35, 0.05)
     w = torch.stack([wg.view(I // 8, 8, K), wu.view(I // 8, 8, K)], 1).reshape(2 * I, K).contiguous()
-    got = ops().gemm_tcgen05(a, w, None, gated_activation="silu", wide=wide)
+    got = ops().gemm_tcgen05(a, w, None, gated_activation="silu", **TC_TILES[tiles])
     ops().check_device_errors()
     g, u = torch.mm(a, wg.t()).float(), torch.mm(a, wu.t()).float()
     want = torch.nn.functional.silu(g) * u

@@ -73,6 +73,7 @@ def _declare(lib) -> None:
         "vx_paged_attention_generic": [P, I, P, P, P, I, P, P, P, I, F, I, I, I, I, I, I, I, P],
         "vx_gemm_nt_simt": [P, P, P, P, I, I, I, I, I, I, I, I, P],
         "vx_gemm_tcgen05": [P, P, P, P, I, I, I, I, I, I, I, I, I, P, P],
+        "vx_gemm_tcgen05_pair": [P, P, P, P, I, I, I, I, I, I, I, I, P, P],
         "vx_gemm_skinny": [P, P, P, P, I, I, I, I, I, I, I, I, I, I, P],
         "vx_paged_prefill_attention_tc": [P, I, I, P, P, I, P, I, P, P, P, P, I, F, I, I, I, I, I, I, I, P, I, P, P],
         "vx_paged_prefill_attention": [P, I, P, P, P, I, P, P, P, P, I, F, I, I, I, I, I, I, I, P],
@@ -477,13 +478,25 @@ def tcgen05_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
+def tcgen05_pair_better(m: int, n: int, device) -> bool:
+    """Whether 256 x 256 tiles by pairs of blocks beat 128 x 256 tiles by single blocks for
+    an [m, n] result: both kinds of block spend the same time on a tile (a pair a little
+    less: each SM reads half of W's tile from its shared memory), so the kind that needs
+    fewer rounds of the GPU's SMs wins; padding rows count as work."""
+    sms = _sm_count(device)
+    cols = -(-n // 256)
+    single = -(-(-(-m // 128) * cols) // sms)
+    paired = -(-(-(-m // 256) * cols) // max(1, sms // 2))
+    return paired * 0.97 < single
+
+
 def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias=None, gated_activation: Optional[str] = None,
-                 wide: bool = True) -> torch.Tensor:
+                 wide: bool = True, pair: bool = False) -> torch.Tensor:
     """a [M,K] times w [N,K] transposed on the tcgen05 tensor cores (bfloat16 in and
     out, float32 accumulation in tensor memory, operands by TMA).  With
     `gated_activation`, w's rows come in tiles of 8 gate rows followed by their 8 up
     rows and the result is act(gate) * up, [M, N/2].  `wide`: 128 x 256 tiles, else
-    128 x 128."""
+    128 x 128; `pair`: 256 x 256 tiles, each formed by a pair of blocks."""
     _dev(a, w, bias)
     _need(a.dim() == 2 and w.dim() == 2 and a.shape[1] == w.shape[1], "gemm_tcgen05: a [M,K], w [N,K]")
     _need(tcgen05_supported(a, w), "gemm_tcgen05: bfloat16, K a multiple of 8, N a multiple of 16, 16-byte aligned rows")
@@ -496,9 +509,14 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias=None, gated_activation: 
         _need(bias.dtype == torch.float32 and bias.numel() == n, "gemm_tcgen05: float32 bias of N elements")
     out = torch.empty((m, cols), dtype=torch.bfloat16, device=a.device)
     _need(cols % 8 == 0, "gemm_tcgen05: output rows must be 16-byte aligned")
-    _check(library().vx_gemm_tcgen05(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), m, n, k, a.stride(0), w.stride(0), cols,
-                                     1 if gated_activation else 0, ACTIVATIONS.get(gated_activation, 0),
-                                     1 if wide else 0, _ptr(_error_word(a.device)), _stream()), "gemm_tcgen05")
+    if pair:
+        _check(library().vx_gemm_tcgen05_pair(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), m, n, k, a.stride(0), w.stride(0),
+                                              cols, 1 if gated_activation else 0, ACTIVATIONS.get(gated_activation, 0),
+                                              _ptr(_error_word(a.device)), _stream()), "gemm_tcgen05_pair")
+    else:
+        _check(library().vx_gemm_tcgen05(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), m, n, k, a.stride(0), w.stride(0), cols,
+                                         1 if gated_activation else 0, ACTIVATIONS.get(gated_activation, 0),
+                                         1 if wide else 0, _ptr(_error_word(a.device)), _stream()), "gemm_tcgen05")
     note_bounded_wait()
     return out
 

@@ -19,7 +19,7 @@ from .linear import Linear
 
 
 GATE_TILE = 8
-FUSED_TCGEN05_MIN_ROWS = 1024
+FUSED_TCGEN05_MIN_ROWS = 128
 
 
 class GatedMLP(FeedForward):
@@ -61,9 +61,10 @@ class GatedMLP(FeedForward):
             # a decode step: W streamed once, act(gate) * up taken on the accumulators
             a = ops.gemm_skinny(h, w, None, h.dtype, gated_activation=self.activation)
         elif fused and h.shape[0] >= FUSED_TCGEN05_MIN_ROWS and ops.tcgen05_supported(h, w):
-            # a prompt portion: tcgen05 product with the same epilogue (measured faster than
-            # the library product followed by the activation kernel from about a thousand rows)
-            a = ops.gemm_tcgen05(h, w, None, gated_activation=self.activation)
+            # a prompt portion: tcgen05 product with the same epilogue (measured no slower than
+            # the library product followed by the activation kernel from 128 rows, faster from 512)
+            a = ops.gemm_tcgen05(h, w, None, gated_activation=self.activation,
+                                 pair=ops.tcgen05_pair_better(h.shape[0], w.shape[0], h.device))
         elif h.dtype == torch.bfloat16:
             # the library product hands over its float32 sums: gate and up are not rounded
             # before the activation, as in the fused kernels
