@@ -48,10 +48,9 @@
 #define PT_ROWS 128
 #define PT_KEYS 128
 #define PT_D 128
-#define PT_THREADS 672
-#define PT_SOFTMAX_THREADS 512
-#define PT_SPLIT 4                   // threads that share a row
-#define PT_PART (PT_KEYS / PT_SPLIT)  // keys of a tile, and columns of O, per thread
+#define PT_QTILES 2                  // query tiles a block works on
+#define PT_THREADS 384
+#define PT_MMA_WARP 8                // warps 0-3: softmax of query tile 0, 4-7: of tile 1, 8: tensor core, 9-11: producers
 #define PT_SPIN_LIMIT (1 << 24)
 #define PT_LOG2E 1.4426950408889634f
 #define PT_HALF_BYTES (128 * 128)   // 128 rows x 64 columns of bf16: one swizzled half of a tile
@@ -173,25 +172,16 @@ __device__ __forceinline__ void pt_st16(unsigned taddr, const unsigned (&r)[16])
         : "memory");
 }
 
-// Named barrier 1 over the softmax threads, with the AND of `ok` returned to all.
-__device__ __forceinline__ bool pt_softmax_barrier_and(bool ok) {
-    unsigned all;
-    asm volatile(
-        "{\n .reg .pred p, q;\n setp.ne.u32 p, %1, 0;\n barrier.red.and.pred q, 1, %2, p;\n selp.u32 %0, 1, 0, q;\n}\n"
-        : "=r"(all) : "r"((unsigned)ok), "n"(PT_SOFTMAX_THREADS) : "memory");
-    return all != 0;
-}
-
-// A short portion on top of many cached keys has few query tiles (a 64-token portion at 4 query heads
-// per kv head: two) but many key tiles for each to walk alone.  Its key tiles are then cut into `splits`
+// A short portion on top of many cached keys has few query blocks (a 64-token portion at 4 query heads
+// per kv head: one) but many key tiles for each to walk alone.  Its key tiles are then cut into `splits`
 // runs that as many blocks take; each writes its unnormalised output and (reference, sum) per row, and
 // the join kernel below adds the runs in order.  The number of runs depends on the request's own portion
 // and keys only, never on what else is in the step.
 __device__ __host__ __forceinline__ int pt_splits_of(int n_new, int kv_len, int toks_per_tile, int Hk, int max_splits,
                                                      int sms) {
-    const int q_tiles = (n_new + toks_per_tile - 1) / toks_per_tile;
+    const int q_blocks = (n_new + PT_QTILES * toks_per_tile - 1) / (PT_QTILES * toks_per_tile);
     const int key_tiles = (kv_len + PT_KEYS - 1) / PT_KEYS;
-    const int fill = sms / (q_tiles * Hk);   // no more runs than give every SM one block: a second wave would wait for the first
+    const int fill = sms / (q_blocks * Hk);  // no more runs than give every SM one block: a second wave would wait for the first
     if (fill < 2 || key_tiles < 8) return 1; // blocks enough for the SMs already, or nothing to cut
     int s = key_tiles / 4;                   // four key tiles a run at least
     s = s < fill ? s : fill;
@@ -200,12 +190,12 @@ __device__ __host__ __forceinline__ int pt_splits_of(int n_new, int kv_len, int 
 
 // barriers of a block
 struct PtBarriers {
-    unsigned long long q_full;
+    unsigned long long q_full[PT_QTILES];
     unsigned long long k_full[2], k_empty[2], v_full[2], v_empty[2];
-    unsigned long long s_full[2], p_ready[2], pv_done[2];
+    unsigned long long s_full[PT_QTILES], p_ready[PT_QTILES], pv_done[PT_QTILES];
 };
 
-__global__ void __launch_bounds__(PT_THREADS)
+__global__ void __launch_bounds__(PT_THREADS, 1)
 paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                   const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
                                   int max_blocks, const int* __restrict__ cu_seqlens,
@@ -218,69 +208,104 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
     __shared__ __align__(8) PtBarriers bars;
     __shared__ unsigned tmem_base_s;
     __shared__ int failed;
-    __shared__ float row_max[2][PT_SPLIT][PT_ROWS];   // [tile parity][part of the keys][row]: the parts' maxima
-    __shared__ float row_sum[PT_SPLIT][PT_ROWS];      // [part of the keys][row]: the parts' sums, at the end
     unsigned char* smem = (unsigned char*)(((uintptr_t)pt_smem_raw + 1023) & ~(uintptr_t)1023);
-    unsigned char* q_s = smem;                                   // 32 KB
-    unsigned char* k_s = smem + PT_TILE_BYTES;                   // 2 x 32 KB
-    unsigned char* v_s = smem + 3 * PT_TILE_BYTES;               // 2 x 32 KB
+    unsigned char* q_s = smem;                                   // 2 x 32 KB
+    unsigned char* k_s = smem + 2 * PT_TILE_BYTES;               // 2 x 32 KB
+    unsigned char* v_s = smem + 4 * PT_TILE_BYTES;               // 2 x 32 KB
     pdl_wait();
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // the longest tiles (the last tokens of a prompt) are handed out first
+    // the longest blocks (the last tokens of a prompt) are handed out first
     const int split = (int)blockIdx.x % max_splits;
-    const int qt = (int)gridDim.x / max_splits - 1 - (int)blockIdx.x / max_splits, hk = blockIdx.y;
+    const int qb = (int)gridDim.x / max_splits - 1 - (int)blockIdx.x / max_splits, hk = blockIdx.y;
     const int seq = seq_list ? seq_list[blockIdx.z] : (int)blockIdx.z;
     const int share = 1 << share_log2;
     const int toks_per_tile = PT_ROWS >> share_log2;
     const int row_base = cu_seqlens[seq];
     const int n_new = cu_seqlens[seq + 1] - row_base;
-    const int t0 = qt * toks_per_tile;
-    if (t0 >= n_new) return;   // (before anything is allocated)
+    const int t_base = qb * PT_QTILES * toks_per_tile;
+    if (t_base >= n_new) return;   // (before anything is allocated)
     const int off = kv_offsets[seq];
-    const int splits = pt_splits_of(n_new, off + n_new, toks_per_tile, Hk, max_splits, sms);
+    const int kv_total = off + n_new;
+    const int splits = pt_splits_of(n_new, kv_total, toks_per_tile, Hk, max_splits, sms);
     if (split >= splits) return;
     const int* bt = block_table + (size_t)seq * max_blocks;
-    const int toks_live = min(toks_per_tile, n_new - t0);
-    const int kv_hi = off + t0 + toks_live;               // one past the last visible key of the tile
-    const int kv_lo = window > 0 ? max(0, off + t0 + 1 - window) : 0;
-    int tile_lo = kv_lo / PT_KEYS;
-    const int tile_hi = (kv_hi + PT_KEYS - 1) / PT_KEYS;
-    int ntiles = tile_hi - tile_lo;
+    // The two query tiles of the block: their tokens, the keys they see, the key tiles of those.
+    int t0[PT_QTILES], live[PT_QTILES], tile_a[PT_QTILES], tile_b[PT_QTILES];
+    int kv_lo_all = 0, kv_hi_all = 0, lo = 0, hi = 0;
+#pragma unroll
+    for (int q = 0; q < PT_QTILES; ++q) {
+        t0[q] = t_base + q * toks_per_tile;
+        live[q] = max(0, min(toks_per_tile, n_new - t0[q]));
+        tile_a[q] = tile_b[q] = 0;
+        if (live[q] > 0) {
+            const int kv_hi = off + t0[q] + live[q];   // one past the last visible key of the tile
+            const int kv_lo = window > 0 ? max(0, off + t0[q] + 1 - window) : 0;
+            tile_a[q] = kv_lo / PT_KEYS;
+            tile_b[q] = (kv_hi + PT_KEYS - 1) / PT_KEYS;
+            if (q == 0) kv_lo_all = kv_lo;
+            kv_hi_all = kv_hi;
+        }
+    }
+    lo = tile_a[0];
+    hi = live[1] > 0 ? tile_b[1] : tile_b[0];
     if (splits > 1) {
-        // this block's run of the tile's key tiles
-        const int per = (ntiles + splits - 1) / splits;
-        tile_lo += split * per;
-        ntiles = min(per, tile_hi - tile_lo);
-        if (ntiles <= 0) {
-            // nothing in this run for this query tile (early tokens of a portion see fewer keys): it weighs nothing
-            for (int r = threadIdx.x; r < PT_ROWS; r += PT_THREADS) {
-                const int tok = r & (toks_per_tile - 1), hi = r >> (7 - share_log2);
-                if (tok < toks_live) {
-                    const size_t p = ((size_t)(row_base + t0 + tok) * H + (hk * share + hi)) * max_splits + split;
+        // this block's run of the block's key tiles
+        const int per = (hi - lo + splits - 1) / splits;
+        lo += split * per;
+        hi = min(lo + per, hi);
+    }
+    bool any = false;
+#pragma unroll
+    for (int q = 0; q < PT_QTILES; ++q) {
+        tile_a[q] = max(tile_a[q], lo);
+        tile_b[q] = live[q] > 0 ? min(tile_b[q], hi) : tile_a[q];
+        if (tile_b[q] <= tile_a[q]) tile_a[q] = tile_b[q] = 0;   // nothing of this run for this query tile
+        any = any || tile_b[q] > tile_a[q];
+    }
+    if (splits > 1) {
+        // a query tile without a key in this run (early tokens of a portion see fewer keys) weighs nothing
+#pragma unroll
+        for (int q = 0; q < PT_QTILES; ++q) {
+            if (live[q] > 0 && tile_b[q] == tile_a[q] && threadIdx.x < PT_ROWS) {
+                const int r = threadIdx.x;
+                const int tok = r & (toks_per_tile - 1), hi_ = r >> (7 - share_log2);
+                if (tok < live[q]) {
+                    const size_t p = ((size_t)(row_base + t0[q] + tok) * H + (hk * share + hi_)) * max_splits + split;
                     part_ml[2 * p] = -INFINITY;
                     part_ml[2 * p + 1] = 0.f;
                 }
             }
-            return;
         }
     }
+    if (!any) return;
+    {   // the tiles that are loaded: from the first tile any query tile wants to the last
+        int first = hi, last = lo;
+#pragma unroll
+        for (int q = 0; q < PT_QTILES; ++q)
+            if (tile_b[q] > tile_a[q]) { first = min(first, tile_a[q]); last = max(last, tile_b[q]); }
+        lo = first;
+        hi = last;
+    }
+    const int ntiles = hi - lo;
 
     if (threadIdx.x == 0) {
-        pt_mbar_init(pt_smem_u32(&bars.q_full), 1);
         for (int i = 0; i < 2; ++i) {
             pt_mbar_init(pt_smem_u32(&bars.k_full[i]), 1);
             pt_mbar_init(pt_smem_u32(&bars.k_empty[i]), 1);
             pt_mbar_init(pt_smem_u32(&bars.v_full[i]), 1);
             pt_mbar_init(pt_smem_u32(&bars.v_empty[i]), 1);
-            pt_mbar_init(pt_smem_u32(&bars.s_full[i]), 1);
-            pt_mbar_init(pt_smem_u32(&bars.p_ready[i]), PT_SOFTMAX_THREADS / 32);   // one arrival per softmax warp
-            pt_mbar_init(pt_smem_u32(&bars.pv_done[i]), 1);
+        }
+        for (int q = 0; q < PT_QTILES; ++q) {
+            pt_mbar_init(pt_smem_u32(&bars.q_full[q]), 1);
+            pt_mbar_init(pt_smem_u32(&bars.s_full[q]), 1);
+            pt_mbar_init(pt_smem_u32(&bars.p_ready[q]), 4);   // one arrival per softmax warp of the tile
+            pt_mbar_init(pt_smem_u32(&bars.pv_done[q]), 1);
         }
         failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (warp == 1) {  // tensor memory: scores/probabilities 0 and 1 (128 columns each), output (128)
+    if (warp == PT_MMA_WARP) {  // tensor memory: scores/probabilities of tiles 0 and 1, outputs of tiles 0 and 1 (128 columns each)
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
                      ::"r"(pt_smem_u32(&tmem_base_s)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
@@ -289,35 +314,26 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const unsigned tmem_base = tmem_base_s;
-    const unsigned tmem_o = tmem_base + 256;
-
-    if (warp == 0 || warp >= 18) {
-        // ---------------- producers: warps 0 and 18 the keys, 19 and 20 the values ----------------
-        // A tiled TMA load takes some 70 cycles to issue, and a tile of keys and values is 32
-        // boxes of 16 keys x 64 columns (a page holds 16 keys), so the boxes are spread over four
-        // warps of eight lanes; keys and values wait for their own buffers (a key buffer is free
-        // as soon as its scores are formed, long before the value buffer of the same tile).
-        const int pw = warp == 0 ? 0 : warp - 17;           // 0..3
-        const int which = pw >> 1, part = pw & 1;           // keys / values; groups 0-3 / 4-7 of the tile
-        if (pw == 0) {
-            // queries: for each shared head, its tokens' two 64-column halves
-            if (lane == 0) pt_mbar_expect_tx(pt_smem_u32(&bars.q_full), PT_TILE_BYTES);
-            __syncwarp();
-            if (lane < 2 * share) {
-                const int hi = lane >> 1, half = lane & 1;
-                pt_tma_load_2d(pt_smem_u32(q_s + half * PT_HALF_BYTES + hi * toks_per_tile * 128), &map_q,
-                               (hk * share + hi) * PT_D + half * 64, row_base + t0, pt_smem_u32(&bars.q_full));
-            }
-        }
-        const int g = part * 4 + ((lane & 7) >> 1), half = lane & 1;
+    // Registers go from the group of the tensor-core and producer warps to the two groups of softmax warps,
+    // whose threads hold a row of 128 scores each.  The block's pool is what it was launched with, 384 x 168
+    // registers, and 256 x 208 + 128 x 88 is exactly that: a request beyond the pool would wait for ever.
+    if (warp >= PT_MMA_WARP) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;\n");
+    if (warp == PT_MMA_WARP + 1 || warp == PT_MMA_WARP + 2) {
+        // ---------------- producers of keys (one warp) and values (the other) ----------------
+        // A tile is 16 boxes of 16 keys x 64 columns (a page holds 16 keys or a multiple), one box
+        // per lane; keys and values wait for their own buffers (a key buffer is free as soon as
+        // the scores of both query tiles are formed, long before the value buffer of the same tile).
+        const int which = warp - (PT_MMA_WARP + 1);           // keys / values
+        const int g = (lane & 15) >> 1, half = lane & 1;
         const CUtensorMap* map = which ? &map_v : &map_k;
-        for (int i = 0; i < ntiles; ++i) {
+        for (int i = 0; i < ntiles && !failed; ++i) {
             const int b = i & 1;
-            const int key_base = (tile_lo + i) * PT_KEYS;
+            const int key_base = (lo + i) * PT_KEYS;
             // Groups of 16 keys outside [kv_lo, kv_hi) repeat the nearest group inside: they
             // are masked anyway, and their pages may not be this request's.
             int key = key_base + g * 16;
-            key = max(min(key, (kv_hi - 1) & ~15), kv_lo & ~15);
+            key = max(min(key, (kv_hi_all - 1) & ~15), kv_lo_all & ~15);
             const int page = bt[key / S];   // (asked for before the wait below)
             const unsigned full = pt_smem_u32(which ? &bars.v_full[b] : &bars.k_full[b]);
             bool ok = true;
@@ -328,21 +344,32 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
                 if (!ok) {
                     failed = 1;
                     atomicExch(error, 11);
-                } else if (part == 0) {
-                    // (the other warp's boxes may land before this is posted: the barrier's phase
-                    // cannot end before this arrival)
+                } else {
                     pt_mbar_expect_tx(full, PT_TILE_BYTES);
                 }
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
-            if (lane < 8) {
+            if (lane < 16) {
                 const int y = (page * Hk + hk) * S + (key % S);
                 unsigned char* dst = (which ? v_s : k_s) + b * PT_TILE_BYTES;
                 pt_tma_load_2d(pt_smem_u32(dst + half * PT_HALF_BYTES + g * 16 * 128), map, half * 64, y, full);
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == PT_MMA_WARP + 3) {
+        // ---------------- producer of the queries: for each shared head, its tokens' two 64-column halves ----------------
+#pragma unroll
+        for (int q = 0; q < PT_QTILES; ++q) {
+            if (tile_b[q] == tile_a[q]) continue;
+            if (lane == 0) pt_mbar_expect_tx(pt_smem_u32(&bars.q_full[q]), PT_TILE_BYTES);
+            __syncwarp();
+            if (lane < 2 * share) {
+                const int hi_ = lane >> 1, half = lane & 1;
+                pt_tma_load_2d(pt_smem_u32(q_s + q * PT_TILE_BYTES + half * PT_HALF_BYTES + hi_ * toks_per_tile * 128), &map_q,
+                               (hk * share + hi_) * PT_D + half * 64, row_base + t0[q], pt_smem_u32(&bars.q_full[q]));
+            }
+        }
+    } else {
         // ---------------- tensor core ----------------
         if (lane == 0) {
             // S = Q K^T: float32 out, bf16 A and B, both K-major, N = 128 keys, M = 128 rows
@@ -351,222 +378,229 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
             // O += P V: A from tensor memory, B = V MN-major (bit 16), N = 128 (head size)
             const unsigned idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(PT_D >> 3) << 17) |
                                      ((unsigned)(PT_ROWS >> 4) << 24);
-            auto issue_s = [&](int i) {   // scores of tile i into buffer i & 1
-                const int b = i & 1;
-                const unsigned qa = pt_smem_u32(q_s), ka = pt_smem_u32(k_s + b * PT_TILE_BYTES);
+            auto issue_s = [&](int q, int t) {   // scores of query tile q on key tile t, over the tile's scores/probabilities
+                const unsigned qa = pt_smem_u32(q_s + q * PT_TILE_BYTES), ka = pt_smem_u32(k_s + ((t - lo) & 1) * PT_TILE_BYTES);
 #pragma unroll
                 for (int k = 0; k < PT_D / 16; ++k) {
                     const unsigned o = (unsigned)((k >> 2) * PT_HALF_BYTES + (k & 3) * 32);
-                    pt_mma_ss(tmem_base + (unsigned)(b * 128), pt_desc_kmajor(qa + o), pt_desc_kmajor(ka + o), idesc_s,
+                    pt_mma_ss(tmem_base + (unsigned)(q * 128), pt_desc_kmajor(qa + o), pt_desc_kmajor(ka + o), idesc_s,
                               k > 0 ? 1u : 0u);
                 }
-                pt_commit(pt_smem_u32(&bars.s_full[b]));
-                pt_commit(pt_smem_u32(&bars.k_empty[b]));
+                pt_commit(pt_smem_u32(&bars.s_full[q]));
             };
-            bool ok = pt_mbar_wait(pt_smem_u32(&bars.q_full), 0) && pt_mbar_wait(pt_smem_u32(&bars.k_full[0]), 0);
-            if (ok) {
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                issue_s(0);
-            }
-            for (int i = 0; i < ntiles && ok; ++i) {
-                const int b = i & 1;
-                if (i + 1 < ntiles) {
-                    // the next scores go into the other buffer, which P V of tile i - 1 must have left
-                    ok = pt_mbar_wait(pt_smem_u32(&bars.k_full[b ^ 1]), (unsigned)(((i + 1) >> 1) & 1));
-                    if (ok && i >= 1) ok = pt_mbar_wait(pt_smem_u32(&bars.pv_done[b ^ 1]), (unsigned)(((i - 1) >> 1) & 1));
-                    if (!ok) break;
-                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                    issue_s(i + 1);
-                }
-                ok = pt_mbar_wait(pt_smem_u32(&bars.v_full[b]), (unsigned)((i >> 1) & 1)) &&
-                     pt_mbar_wait(pt_smem_u32(&bars.p_ready[b]), (unsigned)((i >> 1) & 1));
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const unsigned va = pt_smem_u32(v_s + b * PT_TILE_BYTES);
+            bool ok = true;
+            // the first key tile's scores
+            ok = pt_mbar_wait(pt_smem_u32(&bars.k_full[0]), 0);
 #pragma unroll
-                for (int k = 0; k < PT_KEYS / 16; ++k)   // 16 keys a step: 8 columns of packed P, 2 KB of V
-                    pt_mma_ts(tmem_o, tmem_base + (unsigned)(b * 128 + k * 8), pt_desc_mnmajor(va + (unsigned)(k * 2048)),
-                              idesc_o, (i > 0 || k > 0) ? 1u : 0u);
-                pt_commit(pt_smem_u32(&bars.pv_done[b]));
+            for (int q = 0; q < PT_QTILES; ++q) {
+                if (tile_b[q] > tile_a[q]) {
+                    ok = ok && pt_mbar_wait(pt_smem_u32(&bars.q_full[q]), 0);   // (once: the queries stay)
+                    if (ok && tile_a[q] == lo) {
+                        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                        issue_s(q, lo);
+                    }
+                }
+            }
+            if (ok) pt_commit(pt_smem_u32(&bars.k_empty[0]));
+            for (int t = lo; t < hi && ok; ++t) {
+                const int u = t - lo, b = u & 1;
+                bool have_v = false, have_k = false;
+#pragma unroll
+                for (int q = 0; q < PT_QTILES; ++q) {
+                    if (t >= tile_a[q] && t < tile_b[q]) {
+                        // O_q += P_q V: the probabilities of this tile, the values
+                        if (!have_v) { ok = ok && pt_mbar_wait(pt_smem_u32(&bars.v_full[b]), (unsigned)((u >> 1) & 1)); have_v = true; }
+                        const int n = t - tile_a[q];
+                        ok = ok && pt_mbar_wait(pt_smem_u32(&bars.p_ready[q]), (unsigned)(n & 1));
+                        if (!ok) break;
+                        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                        const unsigned va = pt_smem_u32(v_s + b * PT_TILE_BYTES);
+#pragma unroll
+                        for (int k = 0; k < PT_KEYS / 16; ++k)   // 16 keys a step: 8 columns of packed P, 2 KB of V
+                            pt_mma_ts(tmem_base + (unsigned)(256 + q * 128), tmem_base + (unsigned)(q * 128 + k * 8),
+                                      pt_desc_mnmajor(va + (unsigned)(k * 2048)), idesc_o, (n > 0 || k > 0) ? 1u : 0u);
+                        pt_commit(pt_smem_u32(&bars.pv_done[q]));
+                    }
+                    if (t + 1 >= tile_a[q] && t + 1 < tile_b[q]) {
+                        // the next scores of this query tile go where its probabilities were: the tensor core
+                        // takes its instructions in order, so P V above has read them before
+                        if (!have_k) { ok = ok && pt_mbar_wait(pt_smem_u32(&bars.k_full[b ^ 1]), (unsigned)(((u + 1) >> 1) & 1)); have_k = true; }
+                        if (!ok) break;
+                        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                        issue_s(q, t + 1);
+                    }
+                }
+                if (!ok) break;
                 pt_commit(pt_smem_u32(&bars.v_empty[b]));
+                if (t + 1 < hi) pt_commit(pt_smem_u32(&bars.k_empty[b ^ 1]));
             }
             if (!ok) { failed = 1; atomicExch(error, 12); }
         }
+    }
     } else {
-        // ---------------- softmax and epilogue: four threads own one row ----------------
-        const int sw = warp - 2;                                 // 0..15
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 208;\n");
+        // ---------------- softmax and epilogue: warps 0-3 query tile 0, warps 4-7 query tile 1; a thread owns a row ----------------
+        const int q = warp >> 2;
+        const int my_t0 = q ? t0[1] : t0[0], my_live = q ? live[1] : live[0];
+        const int my_a = q ? tile_a[1] : tile_a[0], my_b = q ? tile_b[1] : tile_b[0];
         const int quarter = warp & 3;                            // the warp's quarter of tensor memory's lanes
-        const int hc = sw >> 2;                                  // which 32 keys of a tile, which 32 columns of O
         const int r = quarter * 32 + lane;                       // row of the tile = lane of tensor memory
-        const int tok = r & (toks_per_tile - 1), hi = r >> (7 - share_log2);
-        const int pos = off + t0 + tok;
-        const int lo = window > 0 ? pos + 1 - window : 0;
+        const int tok = r & (toks_per_tile - 1), hi_ = r >> (7 - share_log2);
+        const int pos = off + my_t0 + tok;
+        const int lo_key = window > 0 ? pos + 1 - window : 0;
         const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
+        const unsigned s_addr = tmem_base + (unsigned)(q * 128) + lane_addr;
+        const unsigned o_addr = tmem_base + (unsigned)(256 + q * 128) + lane_addr;
+        const int my_tiles = my_b - my_a;
         float m_used = -INFINITY, l = 0.f;
-        const int warp_min_pos = __reduce_min_sync(0xffffffffu, pos), warp_max_lo = __reduce_max_sync(0xffffffffu, lo);
-        // All softmax threads pass the same named barriers in the same order whatever
-        // happens: a thread whose bounded wait ran out skips its work, and the
-        // barrier's AND tells everybody to stop at the same place.
+        const int warp_min_pos = __reduce_min_sync(0xffffffffu, pos), warp_max_lo = __reduce_max_sync(0xffffffffu, lo_key);
         bool ok = true;
-        int i = 0;
-        for (; i < ntiles; ++i) {
-            const int b = i & 1;
-            const int key_base = (tile_lo + i) * PT_KEYS + hc * PT_PART;   // of this thread's 32 keys
-            if (ok) ok = pt_mbar_wait(pt_smem_u32(&bars.s_full[b]), (unsigned)((i >> 1) & 1));
+        for (int n = 0; n < my_tiles; ++n) {
+            const int t = my_a + n;
+            const int key_base = t * PT_KEYS;
+            ok = pt_mbar_wait(pt_smem_u32(&bars.s_full[q]), (unsigned)(n & 1));
             ok = __all_sync(0xffffffffu, ok);
-            const unsigned s_addr = tmem_base + (unsigned)(b * 128) + lane_addr;
-            // A stretch of keys that every row of the warp sees whole needs no masking at all.
-            const bool whole = key_base + PT_PART - 1 <= warp_min_pos && key_base >= warp_max_lo;
-            unsigned v[32];
-            float mx = -INFINITY;
-            if (ok) {
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                // the 32 scores are read once and stay in registers for both passes
-                pt_ld32(s_addr + (unsigned)(hc * PT_PART), v);
-                // pass 1: the maximum over the visible keys, in four chains so that no
-                // instruction waits for the one before it
-                float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-                if (whole) {
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            // the row's 128 scores are read once and stay in registers for both passes
+            unsigned v[PT_KEYS];
 #pragma unroll
-                    for (int j = 0; j < 32; j += 2)   // (the three-input maximum: one instruction for two scores)
-                        asm("max.f32 %0, %0, %1, %2;\n" : "+f"(m4[(j >> 1) & 3]) : "f"(__uint_as_float(v[j])), "f"(__uint_as_float(v[j + 1])));
-                } else {
+            for (int c = 0; c < 4; ++c) pt_ld32_issue(s_addr + (unsigned)(c * 32), *reinterpret_cast<unsigned(*)[32]>(&v[c * 32]));
+            pt_wait_ld();
+            // A tile that every row of the warp sees whole needs no masking at all.
+            const bool whole = key_base + PT_KEYS - 1 <= warp_min_pos && key_base >= warp_max_lo;
+            if (!whole) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int key = key_base + j;
-                        if (key <= pos && key >= lo) m4[j & 3] = fmaxf(m4[j & 3], __uint_as_float(v[j]));
-                    }
+                for (int j = 0; j < PT_KEYS; ++j) {
+                    const int key = key_base + j;
+                    if (!(key <= pos && key >= lo_key)) v[j] = 0xff800000u;   // -inf
                 }
-                mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
             }
-            row_max[b][hc][r] = mx;
-            // (also orders every thread's reads of the scores before anybody's writes of probabilities)
-            if (!pt_softmax_barrier_and(ok)) { ok = false; break; }
-            mx = fmaxf(fmaxf(row_max[b][0][r], row_max[b][1][r]), fmaxf(row_max[b][2][r], row_max[b][3][r])) * scale_log2;
-            // (the scale is positive)  The reference maximum moves only when it has grown by more than the
-            // threshold; the four threads of a row see the same maxima and decide alike.
+            // pass 1: the maximum, in eight chains of three-input maxima
+            float m8[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) m8[c] = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < PT_KEYS; j += 2)
+                asm("max.f32 %0, %0, %1, %2;\n" : "+f"(m8[(j >> 1) & 7]) : "f"(__uint_as_float(v[j])), "f"(__uint_as_float(v[j + 1])));
+            float mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
+            mx *= scale_log2;   // (the scale is positive)
+            // The reference maximum moves only when it has grown by more than the threshold.
             float alpha = 1.f;
-            bool move = mx > m_used + PT_RESCALE_THRESHOLD;
+            const bool move = mx > m_used + PT_RESCALE_THRESHOLD;
             if (move) {
                 alpha = (m_used == -INFINITY) ? 0.f : exp2f(m_used - mx);
                 m_used = mx;
                 l *= alpha;
             }
-            if (i > 0 && __any_sync(0xffffffffu, move)) {
-                // this part of O is rescaled in the rows that moved; P V of the previous tile must be complete
-                ok = pt_mbar_wait(pt_smem_u32(&bars.pv_done[b ^ 1]), (unsigned)(((i - 1) >> 1) & 1));
+            if (n > 0 && __any_sync(0xffffffffu, move)) {
+                // O is rescaled in the rows that moved; P V of the previous tile must be complete
+                ok = pt_mbar_wait(pt_smem_u32(&bars.pv_done[q]), (unsigned)((n - 1) & 1));
                 ok = __all_sync(0xffffffffu, ok);
-                if (ok) {
-                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
                     unsigned acc[32];
-                    pt_ld32(tmem_o + lane_addr + (unsigned)(hc * PT_PART), acc);
+                    pt_ld32(o_addr + (unsigned)(c * 32), acc);
 #pragma unroll
                     for (int j = 0; j < 32; ++j) acc[j] = __float_as_uint(__uint_as_float(acc[j]) * alpha);
-                    pt_st32(tmem_o + lane_addr + (unsigned)(hc * PT_PART), acc);
+                    pt_st32(o_addr + (unsigned)(c * 32), acc);
                 }
             }
-            if (ok) {
-                // pass 2: probabilities, written back over the scores as packed bfloat16
-                float ps0 = 0.f, ps1 = 0.f;
-                const float neg_m = -m_used;   // (-inf only if the row has seen no key yet; then nothing is visible)
-                unsigned pk[16];
-                if (whole) {
+            // pass 2: probabilities, written back over the scores as packed bfloat16
+            {
+                // (m_used is -inf only while the row has seen no key; every score is -inf then and 2^-inf = 0)
+                const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
+                const float2 sc2 = make_float2(scale_log2, scale_log2), nm2 = make_float2(neg_m, neg_m);
+                float2 sum2[4];
 #pragma unroll
-                    for (int j = 0; j < 32; j += 2) {
-                        const float x0 = fmaf(__uint_as_float(v[j]), scale_log2, neg_m);
-                        const float x1 = fmaf(__uint_as_float(v[j + 1]), scale_log2, neg_m);
-                        const float p0 = (j % PT_POLY_EVERY == PT_POLY_EVERY - 1) ? pt_ex2_poly(x0) : pt_ex2(x0);
-                        const float p1 = ((j + 1) % PT_POLY_EVERY == PT_POLY_EVERY - 1) ? pt_ex2_poly(x1) : pt_ex2(x1);
-                        ps0 += p0;
-                        ps1 += p1;
-                        const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                for (int c = 0; c < 4; ++c) sum2[c] = make_float2(0.f, 0.f);
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    unsigned pk[32];
+#pragma unroll
+                    for (int j = 0; j < 64; j += 2) {
+                        const int jj = c * 64 + j;
+                        const float2 x = __ffma2_rn(make_float2(__uint_as_float(v[jj]), __uint_as_float(v[jj + 1])), sc2, nm2);
+                        float2 p;
+                        p.x = (jj % PT_POLY_EVERY == PT_POLY_EVERY - 1) ? pt_ex2_poly(x.x) : pt_ex2(x.x);
+                        p.y = ((jj + 1) % PT_POLY_EVERY == PT_POLY_EVERY - 1) ? pt_ex2_poly(x.y) : pt_ex2(x.y);
+                        sum2[(j >> 1) & 3] = __fadd2_rn(sum2[(j >> 1) & 3], p);
+                        const __nv_bfloat162 h = __floats2bfloat162_rn(p.x, p.y);
                         pk[j >> 1] = *reinterpret_cast<const unsigned*>(&h);
                     }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; j += 2) {
-                        const int key = key_base + j;
-                        float p0 = 0.f, p1 = 0.f;
-                        if (key <= pos && key >= lo) p0 = pt_ex2(fmaf(__uint_as_float(v[j]), scale_log2, neg_m));
-                        if (key + 1 <= pos && key + 1 >= lo) p1 = pt_ex2(fmaf(__uint_as_float(v[j + 1]), scale_log2, neg_m));
-                        ps0 += p0;
-                        ps1 += p1;
-                        const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                        pk[j >> 1] = *reinterpret_cast<const unsigned*>(&h);
-                    }
+                    pt_st32(s_addr + (unsigned)(c * 32), pk);
                 }
-                pt_st16(s_addr + (unsigned)(hc * (PT_PART / 2)), pk);
-                l += ps0 + ps1;
+                const float2 s01 = __fadd2_rn(sum2[0], sum2[1]), s23 = __fadd2_rn(sum2[2], sum2[3]);
+                l += (s01.x + s01.y) + (s23.x + s23.y);
             }
-            if (ok && (tile_lo + i + 1) * PT_KEYS > kv_hi) {
-                // the tile reaches past the last key: clear those value rows (both halves)
-                ok = pt_mbar_wait(pt_smem_u32(&bars.v_full[b]), (unsigned)((i >> 1) & 1));
+            if ((t + 1) * PT_KEYS > kv_total && (q == 0 || !(t >= tile_a[0] && t < tile_b[0]))) {
+                // the tile reaches past the request's last key: the lowest query tile that works on it clears
+                // those value rows (both halves); the tensor core takes the tiles' products in this order
+                const int u = t - lo, b = u & 1;
+                ok = pt_mbar_wait(pt_smem_u32(&bars.v_full[b]), (unsigned)((u >> 1) & 1));
                 ok = __all_sync(0xffffffffu, ok);
-                if (ok) {
-                    unsigned char* vt = v_s + b * PT_TILE_BYTES;
-                    const int first = max(kv_hi - (tile_lo + i) * PT_KEYS, 0);
-                    for (int idx = sw * 32 + lane; idx < (PT_KEYS - first) * 16; idx += PT_SOFTMAX_THREADS) {
-                        const int row = first + (idx >> 4), c16 = idx & 15;
-                        *reinterpret_cast<uint4*>(vt + (c16 >> 3) * PT_HALF_BYTES + row * 128 + (c16 & 7) * 16) =
-                            make_uint4(0, 0, 0, 0);
-                    }
-                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                if (!ok) break;
+                unsigned char* vt = v_s + b * PT_TILE_BYTES;
+                const int first = max(kv_total - t * PT_KEYS, 0);
+                for (int idx = quarter * 32 + lane; idx < (PT_KEYS - first) * 16; idx += PT_ROWS) {
+                    const int row = first + (idx >> 4), c16 = idx & 15;
+                    *reinterpret_cast<uint4*>(vt + (c16 >> 3) * PT_HALF_BYTES + row * 128 + (c16 & 7) * 16) =
+                        make_uint4(0, 0, 0, 0);
                 }
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             }
-            if (ok) {
-                asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
-                asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-                __syncwarp();
-                if (lane == 0) pt_mbar_arrive(pt_smem_u32(&bars.p_ready[b]));
-            }
+            asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) pt_mbar_arrive(pt_smem_u32(&bars.p_ready[q]));
         }
-        if (ok && ntiles > 0) {
-            const int last = ntiles - 1;
-            ok = pt_mbar_wait(pt_smem_u32(&bars.pv_done[last & 1]), (unsigned)((last >> 1) & 1));
+        if (ok && my_tiles > 0) {
+            ok = pt_mbar_wait(pt_smem_u32(&bars.pv_done[q]), (unsigned)((my_tiles - 1) & 1));
             ok = __all_sync(0xffffffffu, ok);
         }
-        // the parts of a row's sum meet here (every thread arrives, failed or not)
-        row_sum[hc][r] = l;
-        const bool all_ok = pt_softmax_barrier_and(ok);
-        if (!all_ok) {
-            if (!ok && lane == 0) { failed = 1; atomicExch(error, 13); }
-        } else {
+        if (!ok) {
+            if (lane == 0) { failed = 1; atomicExch(error, 13); }
+        } else if (my_tiles > 0) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            const float total = (row_sum[0][r] + row_sum[1][r]) + (row_sum[2][r] + row_sum[3][r]);
-            const float inv = 1.f / total;
-            const bool live = tok < toks_live;
-            bf16* dst = out + (size_t)(row_base + t0 + tok) * out_row_stride + (size_t)(hk * share + hi) * PT_D + hc * PT_PART;
-            unsigned acc[32];
-            pt_ld32(tmem_o + lane_addr + (unsigned)(hc * PT_PART), acc);
-            if (live && splits > 1) {
-                // one run of several: the unnormalised output and what it is relative to, for the join
-                const size_t p = ((size_t)(row_base + t0 + tok) * H + (hk * share + hi)) * max_splits + split;
-                float* po = part_o + p * PT_D + hc * PT_PART;
+            const float inv = 1.f / l;
+            const bool is_live = tok < my_live;
+            bf16* dst = out + (size_t)(row_base + my_t0 + tok) * out_row_stride + (size_t)(hk * share + hi_) * PT_D;
+            const size_t p = ((size_t)(row_base + my_t0 + tok) * H + (hk * share + hi_)) * max_splits + split;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                unsigned acc[32];
+                pt_ld32(o_addr + (unsigned)(c * 32), acc);
+                if (is_live && splits > 1) {
+                    // one run of several: the unnormalised output and what it is relative to, for the join
+                    float* po = part_o + p * PT_D + c * 32;
 #pragma unroll
-                for (int j = 0; j < 32; j += 4)
-                    *reinterpret_cast<float4*>(po + j) = make_float4(__uint_as_float(acc[j]), __uint_as_float(acc[j + 1]),
-                                                                     __uint_as_float(acc[j + 2]), __uint_as_float(acc[j + 3]));
-                if (hc == 0) {
-                    part_ml[2 * p] = m_used;
-                    part_ml[2 * p + 1] = total;
+                    for (int j = 0; j < 32; j += 4)
+                        *reinterpret_cast<float4*>(po + j) = make_float4(__uint_as_float(acc[j]), __uint_as_float(acc[j + 1]),
+                                                                         __uint_as_float(acc[j + 2]), __uint_as_float(acc[j + 3]));
+                } else if (is_live) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        uint4 pk;
+                        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                        for (int q2 = 0; q2 < 4; ++q2)
+                            h[q2] = __floats2bfloat162_rn(__uint_as_float(acc[j + 2 * q2]) * inv,
+                                                          __uint_as_float(acc[j + 2 * q2 + 1]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c * 32 + j) = pk;
+                    }
                 }
-            } else if (live) {
-#pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                    uint4 pk;
-                    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-                    for (int q2 = 0; q2 < 4; ++q2)
-                        h[q2] = __floats2bfloat162_rn(__uint_as_float(acc[j + 2 * q2]) * inv,
-                                                      __uint_as_float(acc[j + 2 * q2 + 1]) * inv);
-                    *reinterpret_cast<uint4*>(dst + j) = pk;
-                }
+            }
+            if (is_live && splits > 1) {
+                part_ml[2 * p] = m_used;
+                part_ml[2 * p + 1] = l;
             }
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
-    if (warp == 1) {
+    if (warp == PT_MMA_WARP) {
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
     }
@@ -680,7 +714,7 @@ extern "C" int vx_paged_prefill_attention_tc(const void* q, int q_row_stride, in
         !pt_make_map(&mk, k_pool, (long long)pages * Hk * S, D, D, 16) ||
         !pt_make_map(&mv, v_pool, (long long)pages * Hk * S, D, D, 16))
         return VX_ERR_DRIVER;
-    const size_t smem = 5 * (size_t)PT_TILE_BYTES + 1024;
+    const size_t smem = 6 * (size_t)PT_TILE_BYTES + 1024;
     static bool configured[VX_MAX_DEVICES];
     if (int rc = vx_configure_smem(paged_prefill_attention_tc_kernel, smem, configured)) return rc;
     const int q_tiles = (max_new + toks_per_tile - 1) / toks_per_tile;
@@ -689,7 +723,8 @@ extern "C" int vx_paged_prefill_attention_tc(const void* q, int q_row_stride, in
     // scratch of the cut query tiles: outputs [tokens, H, max_splits, D], then (reference, sum) [tokens, H, max_splits, 2]
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)tokens * H * max_splits * D : nullptr;
-    dim3 grid(q_tiles * max_splits, Hk, requests);
+    const int q_blocks = (q_tiles + PT_QTILES - 1) / PT_QTILES;
+    dim3 grid(q_blocks * max_splits, Hk, requests);
     VX_LAUNCH_K(VX_K_ATTENTION, paged_prefill_attention_tc_kernel, grid, PT_THREADS, smem, stream, mq, mk, mv,
                 block_table, max_blocks, cu_seqlens, kv_offsets, seq_list, (bf16*)out, out_row_stride, scale * PT_LOG2E, window, H,
                 Hk, S, share_log2, part_o, part_ml, max_splits, sms, error);

@@ -381,7 +381,7 @@ def paged_prefill_attention_tc(q: torch.Tensor, q_row_stride: int, k_pool, v_poo
     max_splits, scratch = 1, None
     toks_per_tile = 128 // (num_heads // num_kv_heads)
     sms = _sm_count(q.device)
-    if max_kv >= 8 * 128 and 2 * -(-max_new // toks_per_tile) * num_kv_heads <= sms:
+    if max_kv >= 8 * 128 and 2 * -(-max_new // (2 * toks_per_tile)) * num_kv_heads <= sms:   # (a block takes two query tiles)
         max_splits = max(1, min(PREFILL_MAX_SPLITS, -(-max_kv // 128) // 4, sms // num_kv_heads))
         scratch = workspace(q.device, tokens * num_heads * max_splits * (head_dim + 2), which="prefill")
     _check(library().vx_paged_prefill_attention_tc(
