@@ -56,6 +56,7 @@
 #define PT_HALF_BYTES (128 * 128)   // 128 rows x 64 columns of bf16: one swizzled half of a tile
 #define PT_TILE_BYTES (2 * PT_HALF_BYTES)
 #define PT_RESCALE_THRESHOLD 8.0f
+#define PT_SUM_LIMIT 16777216.f    // 2^24: a tile's sum of probabilities beyond which its own maximum is taken
 
 __device__ __forceinline__ unsigned pt_smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void pt_mbar_init(unsigned bar, unsigned count) {
@@ -215,9 +216,13 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
     pdl_wait();
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // the longest blocks (the last tokens of a prompt) are handed out first
+    // Blocks are handed out in the order of blockIdx.x: the longest first (the last tokens of a prompt), over
+    // all kv heads, so that the short ones fill the gaps at the end (with the kv head in blockIdx.y a head's
+    // short blocks would come before the next head's long ones: 2,048 tokens took 50 instead of 34 us by the
+    // same arithmetic).
     const int split = (int)blockIdx.x % max_splits;
-    const int qb = (int)gridDim.x / max_splits - 1 - (int)blockIdx.x / max_splits, hk = blockIdx.y;
+    const int hk = ((int)blockIdx.x / max_splits) % Hk;
+    const int qb = (int)gridDim.x / (max_splits * Hk) - 1 - (int)blockIdx.x / (max_splits * Hk);
     const int seq = seq_list ? seq_list[blockIdx.z] : (int)blockIdx.z;
     const int share = 1 << share_log2;
     const int toks_per_tile = PT_ROWS >> share_log2;
@@ -446,7 +451,8 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
         const int quarter = warp & 3;                            // the warp's quarter of tensor memory's lanes
         const int r = quarter * 32 + lane;                       // row of the tile = lane of tensor memory
         const int tok = r & (toks_per_tile - 1), hi_ = r >> (7 - share_log2);
-        const int pos = off + my_t0 + tok;
+        // (rows beyond the portion's last token act as the last token: they are computed and not stored)
+        const int pos = min(off + my_t0 + tok, kv_total - 1);
         const int lo_key = window > 0 ? pos + 1 - window : 0;
         const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
         const unsigned s_addr = tmem_base + (unsigned)(q * 128) + lane_addr;
@@ -476,40 +482,50 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
                     if (!(key <= pos && key >= lo_key)) v[j] = 0xff800000u;   // -inf
                 }
             }
-            // pass 1: the maximum, in eight chains of three-input maxima
-            float m8[8];
-#pragma unroll
-            for (int c = 0; c < 8; ++c) m8[c] = -INFINITY;
-#pragma unroll
-            for (int j = 0; j < PT_KEYS; j += 2)
-                asm("max.f32 %0, %0, %1, %2;\n" : "+f"(m8[(j >> 1) & 7]) : "f"(__uint_as_float(v[j])), "f"(__uint_as_float(v[j + 1])));
-            float mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
-            mx *= scale_log2;   // (the scale is positive)
-            // The reference maximum moves only when it has grown by more than the threshold.
-            float alpha = 1.f;
-            const bool move = mx > m_used + PT_RESCALE_THRESHOLD;
-            if (move) {
-                alpha = (m_used == -INFINITY) ? 0.f : exp2f(m_used - mx);
-                m_used = mx;
-                l *= alpha;
-            }
-            if (n > 0 && __any_sync(0xffffffffu, move)) {
-                // O is rescaled in the rows that moved; P V of the previous tile must be complete
-                ok = pt_mbar_wait(pt_smem_u32(&bars.pv_done[q]), (unsigned)((n - 1) & 1));
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            // The reference of the exponentials comes from the row's earlier tiles whenever it can: softmax does
+            // not care what it is relative to, and bfloat16 probabilities and float32 sums are as exact at 2^20
+            // as at 1.  The tile's own maximum (a pass over the 128 scores) is taken only for a row's first keys,
+            // for a masked tile, or when the tile's sum shows that its scores have outgrown the reference
+            // (a sum of 2^24 or more, infinity included); then the reference moves and O is rescaled, as it is
+            // when the maximum has grown by more than the threshold 2^8.
+            bool with_max = __any_sync(0xffffffffu, !whole || m_used == -INFINITY);
+            float tile_sum = 0.f;
 #pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    unsigned acc[32];
-                    pt_ld32(o_addr + (unsigned)(c * 32), acc);
+            for (int attempt = 0; attempt < 2 && ok; ++attempt) {
+                if (with_max) {
+                    // the maximum, in eight chains of three-input maxima
+                    float m8[8];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) acc[j] = __float_as_uint(__uint_as_float(acc[j]) * alpha);
-                    pt_st32(o_addr + (unsigned)(c * 32), acc);
+                    for (int c = 0; c < 8; ++c) m8[c] = -INFINITY;
+#pragma unroll
+                    for (int j = 0; j < PT_KEYS; j += 2)
+                        asm("max.f32 %0, %0, %1, %2;\n" : "+f"(m8[(j >> 1) & 7]) : "f"(__uint_as_float(v[j])), "f"(__uint_as_float(v[j + 1])));
+                    float mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
+                    mx *= scale_log2;   // (the scale is positive)
+                    float alpha = 1.f;
+                    const bool move = mx > m_used + PT_RESCALE_THRESHOLD;
+                    if (move) {
+                        alpha = (m_used == -INFINITY) ? 0.f : exp2f(m_used - mx);
+                        m_used = mx;
+                        l *= alpha;
+                    }
+                    if (n > 0 && __any_sync(0xffffffffu, move)) {
+                        // O is rescaled in the rows that moved; P V of the previous tile must be complete
+                        ok = pt_mbar_wait(pt_smem_u32(&bars.pv_done[q]), (unsigned)((n - 1) & 1));
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (!ok) break;
+                        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll 1
+                        for (int c = 0; c < 4; ++c) {
+                            unsigned acc[32];
+                            pt_ld32(o_addr + (unsigned)(c * 32), acc);
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) acc[j] = __float_as_uint(__uint_as_float(acc[j]) * alpha);
+                            pt_st32(o_addr + (unsigned)(c * 32), acc);
+                        }
+                    }
                 }
-            }
-            // pass 2: probabilities, written back over the scores as packed bfloat16
-            {
+                // probabilities, written back over the scores as packed bfloat16
                 // (m_used is -inf only while the row has seen no key; every score is -inf then and 2^-inf = 0)
                 const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
                 const float2 sc2 = make_float2(scale_log2, scale_log2), nm2 = make_float2(neg_m, neg_m);
@@ -533,8 +549,13 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
                     pt_st32(s_addr + (unsigned)(c * 32), pk);
                 }
                 const float2 s01 = __fadd2_rn(sum2[0], sum2[1]), s23 = __fadd2_rn(sum2[2], sum2[3]);
-                l += (s01.x + s01.y) + (s23.x + s23.y);
+                tile_sum = (s01.x + s01.y) + (s23.x + s23.y);
+                if (with_max || !__any_sync(0xffffffffu, !(tile_sum < PT_SUM_LIMIT))) break;
+                with_max = true;   // once more, relative to this tile's maximum
+                asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             }
+            if (!ok) break;
+            l += tile_sum;
             if ((t + 1) * PT_KEYS > kv_total && (q == 0 || !(t >= tile_a[0] && t < tile_b[0]))) {
                 // the tile reaches past the request's last key: the lowest query tile that works on it clears
                 // those value rows (both halves); the tensor core takes the tiles' products in this order
@@ -724,7 +745,7 @@ extern "C" int vx_paged_prefill_attention_tc(const void* q, int q_row_stride, in
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)tokens * H * max_splits * D : nullptr;
     const int q_blocks = (q_tiles + PT_QTILES - 1) / PT_QTILES;
-    dim3 grid(q_blocks * max_splits, Hk, requests);
+    dim3 grid(q_blocks * Hk * max_splits, 1, requests);
     VX_LAUNCH_K(VX_K_ATTENTION, paged_prefill_attention_tc_kernel, grid, PT_THREADS, smem, stream, mq, mk, mv,
                 block_table, max_blocks, cu_seqlens, kv_offsets, seq_list, (bf16*)out, out_row_stride, scale * PT_LOG2E, window, H,
                 Hk, S, share_log2, part_o, part_ml, max_splits, sms, error);
