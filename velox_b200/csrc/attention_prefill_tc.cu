@@ -2,37 +2,36 @@
 // (tcgen05.mma, accumulators in tensor memory, operands by TMA), bfloat16, head
 // size 128.
 //
-// grid (query tile, kv head, request), one block per SM at a time.  A block takes
-// 128 query rows of one request: 128 / G consecutive new tokens for each of the G
-// query heads of one kv head (G in {1, 2, 4, 8}), so the heads of a group share
-// every key/value tile.  It walks over the request's keys in tiles of 128.
+// grid (pairs of query tiles x kv heads x runs, 1, request), one block per SM at a
+// time, numbered longest first.  A block takes TWO query tiles of 128 rows of one
+// request, each 128 / G consecutive new tokens for each of the G query heads of one
+// kv head (G in {1, 2, 4, 8}), so the heads of a group and both tiles share every
+// key/value tile.  It walks over the request's keys in tiles of 128.
 //
-//   warps 0, 18-20  producers: warp 0 loads the query tile once; then, tile by tile,
-//               warps 0 and 18 load the keys and warps 19 and 20 the values, page by
-//               page with tiled TMA loads (128-byte swizzle), one 16-key x 64-column
-//               box per lane (eight lanes a warp), into two shared-memory buffers each;
-//   warp 1      tensor core: one thread issues S = Q K^T (128 x 128, 8 instructions
-//               of K 16) into one of two score buffers in tensor memory, and, when
-//               the softmax warps have turned a score buffer into probabilities,
-//               O += P V (A operand straight from tensor memory, V as the
-//               MN-major B operand).  S of tile i + 1 is issued before P V of tile i,
-//               so the tensor core works while the softmax of tile i runs;
-//   warps 2-17  softmax: four threads own one query row (one lane of tensor memory),
-//               warps 2-5 its keys 0-31 of the tile, warps 6-9 its keys 32-63, and so
-//               on.  A thread reads its 32 scores, masks by select (causal: key <=
-//               the row's position; window: key >= position + 1 - W), exchanges the
-//               maximum with its partners through shared memory (one named barrier a
-//               tile), keeps the running maximum and its quarter of the sum in
-//               float32 (base 2), writes the probabilities back over the scores as
-//               packed bfloat16, and rescales its quarter of the row of O only when
-//               the maximum has grown by more than 2^8 (the probabilities are then
-//               bounded by 256 instead of 1, which float32 and bfloat16 hold
-//               without loss of accuracy).  At the end the same warps add the four
-//               partial sums, divide O by the sum and store it.  The softmax, not the
-//               tensor core, sets the pace of this kernel, and what sets the pace of
-//               the softmax is the latency of each thread's chain of instructions,
-//               not the exponentials' throughput: with one thread per row a tile took
-//               about 4,300 cycles against 1,024 of tensor-core work, with two 2,050.
+//   warps 0-3, 4-7  softmax of query tile 0 and of query tile 1: a thread owns one
+//               row (one lane of tensor memory) and holds its 128 scores in
+//               registers.  It masks by select (causal: key <= the row's position;
+//               window: key >= position + 1 - W), takes 2^(s - m) against a
+//               reference m that comes from the row's earlier tiles (its own
+//               maximum only for a row's first keys, a masked tile, or when the
+//               tile's sum shows that the scores have outgrown the reference),
+//               keeps m and the row's sum in float32 (base 2), writes the
+//               probabilities back over the scores as packed bfloat16, and rescales
+//               its row of O when the reference moves (by more than 2^8).  At the end
+//               it divides O by the sum and stores its row.
+//   warp 8      tensor core: one thread issues, for each key tile and each query
+//               tile q, O_q += P_q V (A operand straight from tensor memory, V as the
+//               MN-major B operand) and then S_q = Q_q K^T of the NEXT key tile over
+//               the probabilities just used (the tensor core takes its instructions
+//               in order), so that one query tile's softmax runs under the other's
+//               products;
+//   warps 9-11  producers: keys (warp 9) and values (warp 10), page by page with
+//               tiled TMA loads (128-byte swizzle), one 16-key x 64-column box per
+//               lane, into two shared-memory buffers each; the two query tiles once
+//               (warp 11).
+// Registers move from warps 8-11 to the softmax warps (setmaxnreg).  In the steady
+// state the tensor core sets the pace: 32 products of 128 x 128 x 16 per key tile
+// take about 3,450 cycles, of which a softmax thread is busy for 1,830.
 //
 // Keys past the request's last key and below its window are masked; the values of a
 // tile that reaches past the last key are cleared in shared memory first, because a
