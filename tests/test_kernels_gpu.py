@@ -648,6 +648,31 @@ def test_paged_prefill_attention_tc_cut_into_runs(case):
         assert torch.equal(alone, out[:seqs[0][1]])
 
 
+@pytest.mark.parametrize("seed", range(10))
+def test_paged_prefill_attention_tc_drawn_shapes(seed):
+    """Drawn cases: one to four requests with portions of 1 to 400 tokens on 0 to 3,000 cached keys, every group size
+    and page size the kernel takes, with and without a window (of any length, so that the two query tiles of a block
+    want different key tiles), cut into runs or not.  Never-written slots of the pools hold NaN."""
+    rng = np.random.default_rng(900 + seed)
+    G = int(rng.choice([1, 2, 4, 8]))
+    Hk = int(rng.choice([1, 2, 3]))
+    H, D = G * Hk, 128
+    S = int(rng.choice([16, 32, 64]))
+    window = int(rng.choice([0, 0, int(rng.integers(1, 700))]))
+    seqs = []
+    for _ in range(int(rng.integers(1, 5))):
+        n = int(rng.choice([1, int(rng.integers(2, 40)), int(rng.integers(40, 400))]))
+        off = int(rng.choice([0, int(rng.integers(1, 300)), int(rng.integers(300, 3000))]))
+        seqs.append((off, n))
+    q, kp, vp, bt, sot, pos, want = paged_case(torch.bfloat16, seqs, H, Hk, D, S, window, seed=950 + seed)
+    cu, offs = prefill_inputs(seqs)
+    max_kv = max(o + n for o, n in seqs) if seed % 2 == 0 else 0
+    out = ops().paged_prefill_attention_tc(q, H * D, kp, vp, bt, cu, offs, 1 / math.sqrt(D), window, H, Hk, D,
+                                           len(seqs), max(n for _, n in seqs), q.shape[0], max_kv=max_kv)
+    ops().check_device_errors()
+    close(out, want, torch.bfloat16, what="drawn case %d: %r, %d/%d heads, pages of %d, window %d" % (seed, seqs, H, Hk, S, window))
+
+
 @pytest.mark.parametrize("far", [0, 500, 1023, 1024, 2900])
 def test_prefill_attention_tc_in_runs_finds_one_far_key(far):
     H, Hk, D, S = 8, 2, 128, 16
