@@ -212,6 +212,11 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
     unsigned char* q_s = smem;                                   // 2 x 32 KB
     unsigned char* k_s = smem + 2 * PT_TILE_BYTES;               // 2 x 32 KB
     unsigned char* v_s = smem + 4 * PT_TILE_BYTES;               // 2 x 32 KB
+    if (threadIdx.x == 0) {   // (the maps' first use would otherwise wait for them: 1 % at 2,048 tokens)
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_q) : "memory");
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_k) : "memory");
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_v) : "memory");
+    }
     pdl_wait();
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
