@@ -546,6 +546,10 @@ TC_PREFILL_CASES = [
     ([(100, 200), (63, 2), (64, 1), (300, 1)], 8, 2, 128, 16, 0),  # portions on top of cached keys, decodes beside them
     ([(0, 300)], 16, 2, 128, 32, 0),                               # 8 heads share, pages of 32
     ([(0, 400), (350, 90), (600, 1)], 4, 1, 128, 16, 170),         # a window that is no multiple of the tile
+    ([(0, 300), (77, 41)], 10, 2, 128, 16, 0),                     # 5 heads a kv head (24 tokens of each in a tile, 8 rows idle)
+    ([(130, 100), (0, 50)], 3, 1, 128, 32, 90),                    # 3 heads: 40 tokens each; a window
+    ([(0, 200)], 14, 2, 128, 16, 0),                               # 7 heads: 16 tokens each, 16 rows idle
+    ([(500, 64)], 6, 1, 128, 16, 0),                               # 6 heads
     ([(7, 333)], 32, 8, 128, 16, 0),                               # the flagship's head layout
     ([(0, 700)], 2, 1, 128, 16, 0),                                # two heads share: several tiles deep
 ]
@@ -620,6 +624,7 @@ TC_SPLIT_CASES = [
     ([(2000, 100)], 32, 8, 128, 16, 0),                            # the flagship's head layout: 4 query tiles x 8 kv heads
     ([(4000, 50), (900, 60)], 4, 1, 128, 32, 600),                 # a window: the runs' tiles start far from key 0
     ([(1021, 130)], 4, 4, 128, 16, 0),                             # no sharing; the last tokens see one key tile more than the first
+    ([(2100, 70), (1300, 33)], 10, 2, 128, 16, 0),                 # 5 heads a kv head, cut
 ]
 
 
@@ -650,11 +655,11 @@ def test_paged_prefill_attention_tc_cut_into_runs(case):
 
 @pytest.mark.parametrize("seed", range(10))
 def test_paged_prefill_attention_tc_drawn_shapes(seed):
-    """Drawn cases: one to four requests with portions of 1 to 400 tokens on 0 to 3,000 cached keys, every group size
+    """Drawn cases: one to four requests with portions of 1 to 400 tokens on 0 to 3,000 cached keys, every group size (1 to 8)
     and page size the kernel takes, with and without a window (of any length, so that the two query tiles of a block
     want different key tiles), cut into runs or not.  Never-written slots of the pools hold NaN."""
     rng = np.random.default_rng(900 + seed)
-    G = int(rng.choice([1, 2, 4, 8]))
+    G = int(rng.choice([1, 2, 3, 4, 5, 6, 7, 8]))
     Hk = int(rng.choice([1, 2, 3]))
     H, D = G * Hk, 128
     S = int(rng.choice([16, 32, 64]))

@@ -211,14 +211,23 @@ ODD = {
                               max_position_embeddings=512, tie_word_embeddings=True, rope_theta=10000.0,
                               rms_norm_eps=1e-6, hidden_act="silu", use_sliding_window=True, sliding_window=50,
                               max_window_layers=1)),
+    # heads of 128 with five query heads per kv head (the tensor-core prompt attention gives each head 24 rows of a
+    # tile and leaves 8 idle), a window, prompts long enough for two query tiles and several key tiles
+    "odd_d": dict(seed=14, page_size=16, lens=[300, 45, 150, 70, 1, 2, 33, 64],
+                  config=dict(vocab_size=300, hidden_size=160, intermediate_size=208, num_hidden_layers=2,
+                              num_attention_heads=10, head_dim=128, attention_bias=False, num_key_value_heads=2,
+                              max_position_embeddings=1024, tie_word_embeddings=True, rope_theta=10000.0,
+                              rms_norm_eps=1e-6, hidden_act="silu", use_sliding_window=True, sliding_window=170,
+                              max_window_layers=1)),
 }
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", sorted(ODD))
 def test_sizes_that_no_fast_kernel_takes(tmp_path, name, dtype):
-    """Head sizes, group sizes and widths outside what the tensor-core kernels take:
-    the engine has to find another kernel for each, or refuse; never a wrong result."""
+    """Head sizes, group sizes and widths outside what the tensor-core kernels take, or at
+    the edge of it: the engine has to find another kernel for each, or refuse; never a wrong
+    result."""
     from velox_b200.config import Qwen3Config
     from velox_b200.weights import write_random_model
 

@@ -5,7 +5,8 @@
 // grid (pairs of query tiles x kv heads x runs, 1, request), one block per SM at a
 // time, numbered longest first.  A block takes TWO query tiles of 128 rows of one
 // request, each 128 / G consecutive new tokens for each of the G query heads of one
-// kv head (G in {1, 2, 4, 8}), so the heads of a group and both tiles share every
+// kv head (G from 1 to 8; 128 / G rounded down to a multiple of 8, so that every head's rows
+// start on a boundary of the shared-memory swizzle), so the heads of a group and both tiles share every
 // key/value tile.  It walks over the request's keys in tiles of 128.
 //
 //   warps 0-3, 4-7  softmax of query tile 0 and of query tile 1: a thread owns one
@@ -172,6 +173,9 @@ __device__ __forceinline__ void pt_st16(unsigned taddr, const unsigned (&r)[16])
         : "memory");
 }
 
+// Tokens of a query tile: each of the G query heads of a kv head has as many rows of the tile's 128, a multiple of 8.
+__device__ __host__ __forceinline__ int pt_toks_per_tile(int share) { return (PT_ROWS / share) & ~7; }
+
 // A short portion on top of many cached keys has few query blocks (a 64-token portion at 4 query heads
 // per kv head: one) but many key tiles for each to walk alone.  Its key tiles are then cut into `splits`
 // runs that as many blocks take; each writes its unnormalised output and (reference, sum) per row, and
@@ -201,7 +205,7 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
                                   int max_blocks, const int* __restrict__ cu_seqlens,
                                   const int* __restrict__ kv_offsets, const int* __restrict__ seq_list,
                                   bf16* __restrict__ out, int out_row_stride,
-                                  float scale_log2, int window, int H, int Hk, int S, int share_log2,
+                                  float scale_log2, int window, int H, int Hk, int S, int share,
                                   float* __restrict__ part_o, float* __restrict__ part_ml, int max_splits, int sms,
                                   int* __restrict__ error) {
     extern __shared__ unsigned char pt_smem_raw[];
@@ -228,8 +232,7 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
     const int hk = ((int)blockIdx.x / max_splits) % Hk;
     const int qb = (int)gridDim.x / (max_splits * Hk) - 1 - (int)blockIdx.x / (max_splits * Hk);
     const int seq = seq_list ? seq_list[blockIdx.z] : (int)blockIdx.z;
-    const int share = 1 << share_log2;
-    const int toks_per_tile = PT_ROWS >> share_log2;
+    const int toks_per_tile = pt_toks_per_tile(share);
     const int row_base = cu_seqlens[seq];
     const int n_new = cu_seqlens[seq + 1] - row_base;
     const int t_base = qb * PT_QTILES * toks_per_tile;
@@ -278,8 +281,8 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
         for (int q = 0; q < PT_QTILES; ++q) {
             if (live[q] > 0 && tile_b[q] == tile_a[q] && threadIdx.x < PT_ROWS) {
                 const int r = threadIdx.x;
-                const int tok = r & (toks_per_tile - 1), hi_ = r >> (7 - share_log2);
-                if (tok < live[q]) {
+                const int hi_ = r / toks_per_tile, tok = r - hi_ * toks_per_tile;
+                if (hi_ < share && tok < live[q]) {
                     const size_t p = ((size_t)(row_base + t0[q] + tok) * H + (hk * share + hi_)) * max_splits + split;
                     part_ml[2 * p] = -INFINITY;
                     part_ml[2 * p + 1] = 0.f;
@@ -318,6 +321,17 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
                      ::"r"(pt_smem_u32(&tmem_base_s)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    if (share * toks_per_tile < PT_ROWS && threadIdx.x < PT_QTILES * PT_ROWS) {
+        // rows of the query tiles that belong to no head are never loaded: cleared, so that their scores are finite
+        const int r = threadIdx.x & (PT_ROWS - 1), qq = threadIdx.x >> 7;
+        if (r >= share * toks_per_tile) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                *reinterpret_cast<uint4*>(q_s + qq * PT_TILE_BYTES + (i >> 3) * PT_HALF_BYTES + r * 128 + (i & 7) * 16) =
+                    make_uint4(0, 0, 0, 0);
+        }
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
@@ -371,7 +385,7 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
 #pragma unroll
         for (int q = 0; q < PT_QTILES; ++q) {
             if (tile_b[q] == tile_a[q]) continue;
-            if (lane == 0) pt_mbar_expect_tx(pt_smem_u32(&bars.q_full[q]), PT_TILE_BYTES);
+            if (lane == 0) pt_mbar_expect_tx(pt_smem_u32(&bars.q_full[q]), (unsigned)(2 * share * toks_per_tile * 128));   // (the heads' rows, two halves)
             __syncwarp();
             if (lane < 2 * share) {
                 const int hi_ = lane >> 1, half = lane & 1;
@@ -455,7 +469,9 @@ paged_prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, con
         const int my_a = q ? tile_a[1] : tile_a[0], my_b = q ? tile_b[1] : tile_b[0];
         const int quarter = warp & 3;                            // the warp's quarter of tensor memory's lanes
         const int r = quarter * 32 + lane;                       // row of the tile = lane of tensor memory
-        const int tok = r & (toks_per_tile - 1), hi_ = r >> (7 - share_log2);
+        // (with 3, 5, 6 or 7 heads a kv head the tile's last rows belong to no head: they act as rows beyond the portion)
+        const int hi_raw = r / toks_per_tile;
+        const int hi_ = hi_raw < share ? hi_raw : 0, tok = hi_raw < share ? r - hi_raw * toks_per_tile : toks_per_tile;
         // (rows beyond the portion's last token act as the last token: they are computed and not stored)
         const int pos = min(off + my_t0 + tok, kv_total - 1);
         const int lo_key = window > 0 ? pos + 1 - window : 0;
@@ -638,12 +654,12 @@ __global__ void __launch_bounds__(128)
 paged_prefill_join_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int max_splits, int sms,
                           const int* __restrict__ cu_seqlens, const int* __restrict__ kv_offsets,
                           const int* __restrict__ seq_list, bf16* __restrict__ out, int out_row_stride, int H, int Hk,
-                          int share_log2) {
+                          int share) {
     pdl_wait();
     pdl_trigger();
     const int qt = blockIdx.x >> 5, hk = blockIdx.y;
     const int seq = seq_list ? seq_list[blockIdx.z] : (int)blockIdx.z;
-    const int share = 1 << share_log2, toks_per_tile = PT_ROWS >> share_log2;
+    const int toks_per_tile = pt_toks_per_tile(share);
     const int row_base = cu_seqlens[seq];
     const int n_new = cu_seqlens[seq + 1] - row_base;
     const int t0 = qt * toks_per_tile;
@@ -654,8 +670,8 @@ paged_prefill_join_kernel(const float* __restrict__ part_o, const float* __restr
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     {
         const int r = ((int)(blockIdx.x & 31) << 2) + warp;
-        const int tok = r & (toks_per_tile - 1), hi = r >> (7 - share_log2);
-        if (tok >= toks_live) return;
+        const int hi = r / toks_per_tile, tok = r - hi * toks_per_tile;
+        if (hi >= share || tok >= toks_live) return;
         const int row = row_base + t0 + tok, h = hk * share + hi;
         const size_t p0 = ((size_t)row * H + h) * max_splits;
         float M = -INFINITY;
@@ -726,15 +742,13 @@ extern "C" int vx_paged_prefill_attention_tc(const void* q, int q_row_stride, in
     if (requests <= 0 || max_new <= 0 || tokens <= 0) return VX_OK;
     if (D != PT_D || H <= 0 || Hk <= 0 || H % Hk || S <= 0 || S % 16 || window < 0 || !error) return VX_ERR_SHAPE;
     const int G = H / Hk;
-    if (G != 1 && G != 2 && G != 4 && G != 8) return VX_ERR_SHAPE;
+    if (G > 8) return VX_ERR_SHAPE;
     if ((q_row_stride & 7) || (((uintptr_t)q) & 15) || (out_row_stride & 7) || (((uintptr_t)out) & 15) ||
         ((((uintptr_t)k_pool) | ((uintptr_t)v_pool)) & 15))
         return VX_ERR_ALIGN;
     if (Hk > 65535 || requests > 65535) return VX_ERR_LIMIT;
     if (max_splits < 1 || max_splits > 64 || (max_splits > 1 && !scratch)) return VX_ERR_SHAPE;
-    int share_log2 = 0;
-    while ((1 << share_log2) < G) ++share_log2;
-    const int toks_per_tile = PT_ROWS >> share_log2;
+    const int toks_per_tile = pt_toks_per_tile(G);
     CUtensorMap mq, mk, mv;
     if (!pt_make_map(&mq, q, tokens, H * D, q_row_stride, toks_per_tile) ||
         !pt_make_map(&mk, k_pool, (long long)pages * Hk * S, D, D, 16) ||
@@ -753,12 +767,12 @@ extern "C" int vx_paged_prefill_attention_tc(const void* q, int q_row_stride, in
     dim3 grid(q_blocks * Hk * max_splits, 1, requests);
     VX_LAUNCH_K(VX_K_ATTENTION, paged_prefill_attention_tc_kernel, grid, PT_THREADS, smem, stream, mq, mk, mv,
                 block_table, max_blocks, cu_seqlens, kv_offsets, seq_list, (bf16*)out, out_row_stride, scale * PT_LOG2E, window, H,
-                Hk, S, share_log2, part_o, part_ml, max_splits, sms, error);
+                Hk, S, G, part_o, part_ml, max_splits, sms, error);
     VX_LAUNCH_CHECK();
     if (max_splits > 1) {
         dim3 jgrid(q_tiles * 32, Hk, requests);
         VX_LAUNCH_K(VX_K_JOIN, paged_prefill_join_kernel, jgrid, 128, 0, stream, (const float*)part_o, (const float*)part_ml,
-                    max_splits, sms, cu_seqlens, kv_offsets, seq_list, (bf16*)out, out_row_stride, H, Hk, share_log2);
+                    max_splits, sms, cu_seqlens, kv_offsets, seq_list, (bf16*)out, out_row_stride, H, Hk, G);
         VX_LAUNCH_CHECK();
     }
     return VX_OK;

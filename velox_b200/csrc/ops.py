@@ -357,7 +357,7 @@ PREFILL_MAX_SPLITS = 16
 
 
 def prefill_attention_tc_supported(dtype, head_dim: int, page_size: int, group: int) -> bool:
-    return dtype == torch.bfloat16 and head_dim == 128 and page_size % 16 == 0 and group in (1, 2, 4, 8)
+    return dtype == torch.bfloat16 and head_dim == 128 and page_size % 16 == 0 and 1 <= group <= 8
 
 
 def paged_prefill_attention_tc(q: torch.Tensor, q_row_stride: int, k_pool, v_pool, block_table: torch.Tensor,
@@ -379,7 +379,7 @@ def paged_prefill_attention_tc(q: torch.Tensor, q_row_stride: int, k_pool, v_poo
     # runs of key tiles: up to a quarter of the longest request's key tiles, 16 at most; only a step whose
     # portions are short can have a request that is cut (a long portion has query tiles enough)
     max_splits, scratch = 1, None
-    toks_per_tile = 128 // (num_heads // num_kv_heads)
+    toks_per_tile = (128 // (num_heads // num_kv_heads)) & ~7   # (as pt_toks_per_tile in the kernel)
     sms = _sm_count(q.device)
     if max_kv >= 8 * 128 and 2 * -(-max_new // (2 * toks_per_tile)) * num_kv_heads <= sms:   # (a block takes two query tiles)
         max_splits = max(1, min(PREFILL_MAX_SPLITS, -(-max_kv // 128) // 4, sms // num_kv_heads))
