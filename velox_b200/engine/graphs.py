@@ -25,6 +25,7 @@ from __future__ import annotations
 
 import ctypes
 import gc
+import os
 import weakref
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -136,7 +137,11 @@ class _Graph:
         self.ids = ops.sample(self.logits, self.d_temp, self.d_top_p, self.d_uniform)
 
 
-MIXED_MAX_TOKENS = 256   # larger steps keep the device busy longer than the host needs to launch them
+# Larger steps keep the device busy longer than the host needs to launch them, and recording a graph costs tens of
+# milliseconds: with 256 here a stream under a budget of 256 tokens a step recorded its 64 graphs and lost a quarter
+# of its throughput (Qwen3-14B shape 1,282 against 1,793 tokens a second; with 96 1,781).
+# VELOX_B200_MIXED_GRAPH_TOKENS sets it; 0: never.
+MIXED_MAX_TOKENS = int(os.environ.get("VELOX_B200_MIXED_GRAPH_TOKENS", "96"))
 MIXED_SEEN_BEFORE = 2    # a shape is captured when it comes up for the third time
 MIXED_MAX_GRAPHS = 64    # (each holds its activations: tens of MB at the real widths)
 
