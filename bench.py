@@ -31,6 +31,9 @@ MODEL = dict(vocab_size=151936, hidden_size=4096, intermediate_size=12288, num_h
              rms_norm_eps=1e-6, hidden_act="silu")
 # Other shapes of the same architecture, for measurements beside the benchmark's (`--shape`).
 SHAPES = {
+    "0.6b": dict(hidden_size=1024, intermediate_size=3072, num_hidden_layers=28, num_attention_heads=16, tie_word_embeddings=True),
+    "1.7b": dict(hidden_size=2048, intermediate_size=6144, num_hidden_layers=28, num_attention_heads=16, tie_word_embeddings=True),
+    "4b": dict(hidden_size=2560, intermediate_size=9728, num_hidden_layers=36, num_attention_heads=32, tie_word_embeddings=True),
     "8b": {},
     "14b": dict(hidden_size=5120, intermediate_size=17408, num_hidden_layers=40, num_attention_heads=40),
     "32b": dict(hidden_size=5120, intermediate_size=25600, num_hidden_layers=64, num_attention_heads=64),
@@ -210,7 +213,7 @@ def main() -> int:
     ap.add_argument("--max-batch-tokens", type=int, default=2048,
                     help="stream: new tokens of one step (a decoded token that rides with a prompt portion waits for it)")
     ap.add_argument("--shape", default="8b", choices=sorted(SHAPES),
-                    help="layer sizes: 8b is the benchmark's; 14b and 32b are Qwen3-14B / 32B")
+                    help="layer sizes: 8b is the benchmark's; the others are Qwen3-0.6B / 1.7B / 4B / 14B / 32B")
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64 and prefill")
     ap.add_argument("--context", type=int, default=CONTEXT,
                     help="context length the decoding requests reach (the benchmark's is %d; others for measurements "
